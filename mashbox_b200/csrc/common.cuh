@@ -1,0 +1,54 @@
+// Shared helpers of the sm_100a kernels: storage types, warp/block reductions with a fixed shape, error codes.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#define MB_API extern "C" __attribute__((visibility("default")))
+
+// Codes a kernel leaves in the engine's error word (first one wins); the host reads the word after a step.
+enum MbDeviceError {
+    MB_ERR_NONE = 0,
+    MB_ERR_TOKEN_RANGE = 1,     // a token id outside [0, vocab)
+    MB_ERR_PAGE_MISSING = 2,    // a position whose page the block table does not hold
+    MB_ERR_PAGE_RANGE = 3,      // a page id outside the pool
+    MB_ERR_WAIT_TIMEOUT = 4,    // a bounded wait inside a kernel ran out
+};
+
+__device__ __forceinline__ void mb_set_error(int* err, int code) {
+    if (err) atomicCAS(err, 0, code);
+}
+
+template <typename T> __device__ __forceinline__ float mb_load(const T* p);
+template <> __device__ __forceinline__ float mb_load<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float mb_load<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+
+template <typename T> __device__ __forceinline__ void mb_store(T* p, float v);
+template <> __device__ __forceinline__ void mb_store<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void mb_store<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float mb_warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float mb_warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block whose size is a multiple of 32 (at most 1024): warp trees, then one tree over the warp sums.
+// The shape of the reduction depends on the block size only, so a row's result does not depend on the batch.
+__device__ __forceinline__ float mb_block_sum(float v, float* scratch /* 32 floats */) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    v = mb_warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float t = (lane < nwarp) ? scratch[lane] : 0.0f;
+    return mb_warp_sum(t);
+}
+
+#define MB_LAUNCH_CHECK() do { cudaError_t e__ = cudaGetLastError(); if (e__ != cudaSuccess) return (int)e__; } while (0)

@@ -1,0 +1,209 @@
+// Memory-bound kernels of the step: embedding gather, residual-add + RMSNorm, rotation + K/V page write, SwiGLU.
+// T is the activation / cache storage type (float on the 32-bit path, bf16 to serve); all arithmetic is float.
+#include "common.cuh"
+
+// ------------------------------------------------------------------------------------------------ embedding
+// x[n, :] = table[tok[n], :] into the float residual stream.
+template <typename T>
+__global__ void embed_kernel(const int* __restrict__ tok, const T* __restrict__ table, float* __restrict__ x,
+                             int D, int V, int* err) {
+    const int n = blockIdx.x;
+    int t = tok[n];
+    if (t < 0 || t >= V) {
+        if (threadIdx.x == 0) mb_set_error(err, MB_ERR_TOKEN_RANGE);
+        for (int d = threadIdx.x; d < D; d += blockDim.x) x[(size_t)n * D + d] = 0.0f;
+        return;
+    }
+    const T* row = table + (size_t)t * D;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) x[(size_t)n * D + d] = mb_load(row + d);
+}
+
+// ------------------------------------------------------------------------------------------------ add + RMSNorm
+// v = x[r] (+ delta[r] (+ dbias));  if rows == nullptr the sum is written back to x (the residual stream);
+// out[i] = v * rsqrt(mean(v^2) + eps) * w.  r = rows ? rows[i] : i.  One block per output row.
+template <typename T>
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ dbias,
+                                   const int* __restrict__ rows, const float* __restrict__ w, float eps,
+                                   T* __restrict__ out, int D) {
+    __shared__ float scratch[32];
+    const int i = blockIdx.x;
+    const size_t r = rows ? (size_t)rows[i] : (size_t)i;
+    float* xr = x + r * D;
+    const T* dr = delta ? delta + r * D : nullptr;
+    float ss = 0.0f;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float v = xr[d];
+        if (dr) {
+            float a = mb_load(dr + d);
+            if (dbias) a += dbias[d];
+            v += a;
+            if (!rows) xr[d] = v;
+        }
+        ss = fmaf(v, v, ss);
+    }
+    ss = mb_block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float)D + eps);
+    T* o = out + (size_t)i * D;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float v = xr[d];
+        if (dr && rows) {
+            float a = mb_load(dr + d);
+            if (dbias) a += dbias[d];
+            v += a;
+        }
+        mb_store(o + d, v * inv * w[d]);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ rotation + K/V write
+// qkv[n] = [q (H*HD) | k (KV*HD) | v (KV*HD)] (+ bias).  q is rotated in place; k is rotated and written to its page,
+// v is written to its page (when pools are given).  freqs[i] is the angle per position step of pair i (RD/2 values);
+// pairing 0 rotates (2i, 2i+1), pairing 1 rotates (i, i + RD/2); dims from RD on pass through.  freqs == nullptr
+// means no rotation.  Page of position p of sequence s: table[s * max_blocks + p / page].
+template <typename T>
+__global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float* __restrict__ bias,
+                                     const int* __restrict__ positions, const int* __restrict__ tok_seq,
+                                     const int* __restrict__ table, int max_blocks, T* __restrict__ kpool,
+                                     T* __restrict__ vpool, const float* __restrict__ freqs, int H, int KV, int HD,
+                                     int RD, int pairing, int page, int num_pages, int* err) {
+    const int n = blockIdx.x;
+    const int half = HD / 2, rhalf = RD / 2;
+    const int per = blockDim.x / half;               // heads handled at once
+    const int lane = threadIdx.x % half, sub = threadIdx.x / half;
+    const int pos = positions[n];
+    T* row = qkv + (size_t)n * (H + 2 * KV) * HD;
+    const float* brow = bias;
+    size_t slot = 0;
+    bool store = kpool != nullptr;
+    if (store) {
+        const int pg = table[(size_t)tok_seq[n] * max_blocks + pos / page];
+        if (pg < 0 || pg >= num_pages) {
+            if (threadIdx.x == 0) mb_set_error(err, pg < 0 ? MB_ERR_PAGE_MISSING : MB_ERR_PAGE_RANGE);
+            store = false;
+        } else {
+            slot = (size_t)pg * KV * page + (pos % page);       // + kvh * page, then * HD
+        }
+    }
+    if (sub >= per) return;
+    // the pair this thread owns inside every head: element indices e0, e1 and whether it is rotated
+    int e0, e1;
+    bool rot;
+    if (pairing == 0) {
+        e0 = 2 * lane; e1 = e0 + 1; rot = lane < rhalf;
+    } else if (lane < rhalf) {
+        e0 = lane; e1 = lane + rhalf; rot = true;
+    } else {                                          // the passthrough dims RD .. HD-1, two per thread
+        e0 = RD + 2 * (lane - rhalf); e1 = e0 + 1; rot = false;
+    }
+    float c = 1.0f, s = 0.0f;
+    if (rot && freqs) {
+        const float ang = (float)pos * freqs[lane];
+        sincosf(ang, &s, &c);
+    } else {
+        rot = false;
+    }
+    for (int h = sub; h < H + 2 * KV; h += per) {
+        T* p = row + (size_t)h * HD;
+        float a = mb_load(p + e0), b = mb_load(p + e1);
+        if (brow) { a += brow[(size_t)h * HD + e0]; b += brow[(size_t)h * HD + e1]; }
+        if (h < H + KV && rot) {
+            const float ra = a * c - b * s, rb = a * s + b * c;
+            a = ra; b = rb;
+        }
+        if (h < H) {
+            mb_store(p + e0, a); mb_store(p + e1, b);
+        } else if (store) {
+            const int kvh = (h - H) % KV;
+            T* pool = (h < H + KV) ? kpool : vpool;
+            T* dst = pool + (slot + (size_t)kvh * page) * HD;
+            mb_store(dst + e0, a); mb_store(dst + e1, b);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ SwiGLU
+// gu[n] = [gate (F) | up (F)] -> out[n, f] = silu(gate) * up
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int F, size_t total) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const size_t n = i / F, f = i % F;
+    const float g = mb_load(gu + n * 2 * F + f), u = mb_load(gu + n * 2 * F + F + f);
+    mb_store(out + i, (g / (1.0f + expf(-g))) * u);
+}
+
+// ------------------------------------------------------------------------------------------------ launchers
+template <typename T>
+static int embed_launch(const int* tok, const void* table, float* x, int N, int D, int V, int* err, cudaStream_t st) {
+    if (N == 0) return 0;
+    embed_kernel<T><<<N, 256, 0, st>>>(tok, (const T*)table, x, D, V, err);
+    MB_LAUNCH_CHECK();
+    return 0;
+}
+MB_API int mb_embed_f32(const int* tok, const void* table, float* x, int N, int D, int V, int* err, cudaStream_t st) {
+    return embed_launch<float>(tok, table, x, N, D, V, err, st);
+}
+MB_API int mb_embed_bf16(const int* tok, const void* table, float* x, int N, int D, int V, int* err, cudaStream_t st) {
+    return embed_launch<__nv_bfloat16>(tok, table, x, N, D, V, err, st);
+}
+
+template <typename T>
+static int add_rmsnorm_launch(float* x, const void* delta, const float* dbias, const int* rows, const float* w,
+                              float eps, void* out, int n_out, int D, cudaStream_t st) {
+    if (n_out == 0) return 0;
+    add_rmsnorm_kernel<T><<<n_out, 256, 0, st>>>(x, (const T*)delta, dbias, rows, w, eps, (T*)out, D);
+    MB_LAUNCH_CHECK();
+    return 0;
+}
+MB_API int mb_add_rmsnorm_f32(float* x, const void* delta, const float* dbias, const int* rows, const float* w,
+                              float eps, void* out, int n_out, int D, cudaStream_t st) {
+    return add_rmsnorm_launch<float>(x, delta, dbias, rows, w, eps, out, n_out, D, st);
+}
+MB_API int mb_add_rmsnorm_bf16(float* x, const void* delta, const float* dbias, const int* rows, const float* w,
+                               float eps, void* out, int n_out, int D, cudaStream_t st) {
+    return add_rmsnorm_launch<__nv_bfloat16>(x, delta, dbias, rows, w, eps, out, n_out, D, st);
+}
+
+template <typename T>
+static int rope_kv_write_launch(void* qkv, const float* bias, const int* positions, const int* tok_seq,
+                                const int* table, int max_blocks, void* kpool, void* vpool, const float* freqs, int N,
+                                int H, int KV, int HD, int RD, int pairing, int page, int num_pages, int* err,
+                                cudaStream_t st) {
+    if (N == 0) return 0;
+    if (HD % 2 || RD % 2 || RD > HD || HD / 2 > 1024) return -2;
+    int threads = 256;
+    if (HD / 2 > threads) threads = ((HD / 2 + 31) / 32) * 32;
+    rope_kv_write_kernel<T><<<N, threads, 0, st>>>((T*)qkv, bias, positions, tok_seq, table, max_blocks, (T*)kpool,
+                                                    (T*)vpool, freqs, H, KV, HD, RD, pairing, page, num_pages, err);
+    MB_LAUNCH_CHECK();
+    return 0;
+}
+MB_API int mb_rope_kv_write_f32(void* qkv, const float* bias, const int* positions, const int* tok_seq,
+                                const int* table, int max_blocks, void* kpool, void* vpool, const float* freqs, int N,
+                                int H, int KV, int HD, int RD, int pairing, int page, int num_pages, int* err,
+                                cudaStream_t st) {
+    return rope_kv_write_launch<float>(qkv, bias, positions, tok_seq, table, max_blocks, kpool, vpool, freqs, N, H, KV,
+                                       HD, RD, pairing, page, num_pages, err, st);
+}
+MB_API int mb_rope_kv_write_bf16(void* qkv, const float* bias, const int* positions, const int* tok_seq,
+                                 const int* table, int max_blocks, void* kpool, void* vpool, const float* freqs, int N,
+                                 int H, int KV, int HD, int RD, int pairing, int page, int num_pages, int* err,
+                                 cudaStream_t st) {
+    return rope_kv_write_launch<__nv_bfloat16>(qkv, bias, positions, tok_seq, table, max_blocks, kpool, vpool, freqs,
+                                               N, H, KV, HD, RD, pairing, page, num_pages, err, st);
+}
+
+template <typename T>
+static int swiglu_launch(const void* gu, void* out, int N, int F, cudaStream_t st) {
+    const size_t total = (size_t)N * F;
+    if (total == 0) return 0;
+    swiglu_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, st>>>((const T*)gu, (T*)out, F, total);
+    MB_LAUNCH_CHECK();
+    return 0;
+}
+MB_API int mb_swiglu_f32(const void* gu, void* out, int N, int F, cudaStream_t st) {
+    return swiglu_launch<float>(gu, out, N, F, st);
+}
+MB_API int mb_swiglu_bf16(const void* gu, void* out, int N, int F, cudaStream_t st) {
+    return swiglu_launch<__nv_bfloat16>(gu, out, N, F, st);
+}

@@ -1,0 +1,131 @@
+"""The step function: one batch of (request, its next tokens) through the model, from the cache, to logits.
+
+A step takes entries (request id, tokens, want): the request's next tokens -- a portion of its prompt of any length, or
+one decoded token -- and the places among them whose logits are asked for.  All entries run as ONE batch: the tokens
+are laid end to end, every kernel runs over all of them, and attention tells the sequences apart by the step's
+descriptors.  Pages are taken from the cache manager before the step and the request's length is committed after it.
+The scheduler, generate() and the trace replay all go through this one function.
+
+Decode-only steps (every entry one token, every token wanted) are captured in CUDA graphs, keyed by the lengths of the
+step's integer arrays, and replayed: the arrays live in one device buffer that is refilled before each replay.
+"""
+import numpy as np
+import torch
+
+from .. import ops as kernels
+from ..cache.manager import CacheManager
+from ..errors import CacheError, RequestError
+from ..parts import Env, StepContext, StepInputs, Workspace
+
+
+class ModelRunner:
+    def __init__(self, model, engine_config, options=None):
+        from .loading import torch_dtype
+        self.model, self.cfg = model, engine_config
+        self.options = dict(options or {})
+        self.device = torch.device(engine_config.device)
+        if self.device.type != "cuda" or not torch.cuda.is_available():
+            raise RequestError("mashbox_b200 runs on a CUDA device only; there is no CPU path")
+        self.dtype = torch_dtype(engine_config.dtype)
+        self.env = Env(self.dtype, self.device, kernels)
+        needs, states = model.cache_needs()
+        self.cache = CacheManager(needs, states, engine_config.page_size, engine_config.pages(),
+                                  engine_config.max_requests, engine_config.max_context, self.dtype, self.device)
+        self.options.setdefault("logit_rows", engine_config.max_requests)
+        self.ws = Workspace(self.device, engine_config.max_tokens_per_step + engine_config.max_requests)
+        self.inputs = StepInputs(self.device)
+        self.err = kernels.new_error_word(self.device)
+        self.graphs, self.seen_signatures = {}, {}
+        self.use_graphs = bool(engine_config.cuda_graphs) and not self.options.get("no_graphs", False)
+        self.stats = dict(steps=0, tokens=0, graph_replays=0, graph_captures=0)
+
+    # -------------------------------------------------------------------------------------------- the step
+    def step(self, entries):
+        """entries: [(request id, tokens, want)] -> float32 logits (sum of wants, vocab) on the device, in the order
+        of the entries and of each `want`; None when nothing is wanted.  The tensor is valid until the next step."""
+        cache = self.cache
+        if not entries:
+            return None
+        seen = set()
+        need = [0] * len(cache.groups)
+        for rid, tokens, want in entries:
+            if rid in seen:
+                raise RequestError(f"request {rid!r} is in the step twice")
+            seen.add(rid)
+            if len(tokens) < 1:
+                raise RequestError(f"request {rid!r} brings no tokens")
+            if any(not 0 <= int(w) < len(tokens) for w in want):
+                raise RequestError(f"request {rid!r} wants a place outside its {len(tokens)} tokens")
+            r = cache.get(rid)
+            if r.length + len(tokens) > cache.max_context:
+                raise CacheError(f"request {rid!r} would hold {r.length + len(tokens)} tokens, over the context of "
+                                 f"{cache.max_context}")
+            for gi, n in enumerate(cache.pages_needed(rid, len(tokens))):
+                need[gi] += n
+        if any(n > g.pool.n_free for n, g in zip(need, cache.groups)):
+            raise CacheError("no free page")
+        for rid, tokens, _ in entries:
+            cache.extend(rid, len(tokens))
+
+        S = len(entries)
+        q_len = [len(t) for _, t, _ in entries]
+        q_start = np.concatenate([[0], np.cumsum(q_len)[:-1]]).astype(np.int32)
+        N = int(sum(q_len))
+        reqs = [cache.get(rid) for rid, _, _ in entries]
+        pos0 = np.asarray([r.length for r in reqs], np.int32)
+        rows = np.asarray([r.row for r in reqs], np.int32)
+        token_ids = np.concatenate([np.asarray(t, np.int64) for _, t, _ in entries]).astype(np.int32)
+        positions = np.concatenate([p + np.arange(n, dtype=np.int32) for p, n in zip(pos0, q_len)])
+        tok_row = np.repeat(rows, q_len)
+        want = np.asarray([q_start[i] + int(w) for i, (_, _, ws) in enumerate(entries) for w in ws], np.int32)
+
+        ctx = StepContext(self.env, cache, self.ws, self.inputs, self.err, self.options)
+        ctx.N, ctx.S, ctx.n_out = N, S, len(want)
+        ctx.rows, ctx.q_start, ctx.q_len, ctx.pos0 = rows.tolist(), q_start.tolist(), q_len, pos0.tolist()
+        ctx.state_slots = [r.state_slot for r in reqs]
+        inp = self.inputs
+        inp.reset()
+        inp.add("token_ids", token_ids)
+        inp.add("positions", positions)
+        inp.add("tok_row", tok_row)
+        inp.add("want", want)
+        inp.add("q_start", q_start)
+        inp.add("q_len", q_len)
+        inp.add("pos0", pos0)
+        inp.add("seq_row", rows)
+        inp.add("state_slot", ctx.state_slots)
+        self.model.prepare(ctx)
+        inp.upload()
+        cache.flush_tables()
+
+        decode_only = self.use_graphs and N == S and len(want) == S
+        logits = self._run_graph(ctx) if decode_only else self.model.forward(ctx)
+        for rid, tokens, _ in entries:
+            cache.commit(rid, len(tokens))
+        self.stats["steps"] += 1
+        self.stats["tokens"] += N
+        return logits
+
+    def _run_graph(self, ctx):
+        sig = (self.inputs.signature(), getattr(self.ws, "generation", 0), getattr(self.inputs, "generation", 0))
+        g = self.graphs.get(sig)
+        if g is not None:
+            g[0].replay()
+            self.stats["graph_replays"] += 1
+            return g[1]
+        count = self.seen_signatures.get(sig, 0)
+        self.seen_signatures[sig] = count + 1
+        if count == 0:                      # first time: run eagerly (loads kernels, sizes buffers)
+            return self.model.forward(ctx)
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            logits = self.model.forward(ctx)
+        graph.replay()
+        self.graphs[sig] = (graph, logits)
+        self.stats["graph_captures"] += 1
+        return logits
+
+    def check(self):
+        """Reads the kernels' error word (synchronises)."""
+        kernels.check_error_word(self.err)

@@ -1,0 +1,211 @@
+"""The scheduler: admits requests, cuts prompts into portions under a token budget, decodes, finishes and frees.
+
+Every live request is a list of tokens (prompt + what it generated) of which the first `computed` are in the cache.
+A step feeds each chosen request its next tokens: ONE token when only the last is missing (decoding), else a portion of
+at most `chunk` tokens.  Decoding requests come first and always get their token; what is left of the step's token
+budget goes to prompt portions, first come first served, then to new admissions.  The logits of a request are wanted
+only at the step that feeds its last known token; the token sampled there is appended (mashbox-labs/mashbox schedules
+the same way, one decode call for all decoding rows and at most one prefill chunk per prefilling row inside a token
+budget, src/mashbox/runtime/engine.py:953-1074, on whole-context slots instead of pages).
+
+When pages run out: a decoding request that needs a page none is free for makes the scheduler PREEMPT the most recently
+admitted running request (possibly itself): its pages, row and state slot are given back, it returns to the FRONT of
+the waiting queue with prompt + generated as the tokens to recompute, and its sampling continues at the same token
+index, so its answer does not change.  A prompt portion never preempts anyone: it shrinks to the pages that are free or
+waits.  A waiting request is admitted only when the pages for all its known tokens plus one are free.  A request whose
+prompt + max_new can never fit the pool or the context is refused at check() and touches nothing.
+
+Finish reasons as the reference (engine.py:820-827, 1040-1050): "stop" (a stop token, not emitted), "length" (max_new
+reached; the first token counts), "cancel", "error".
+"""
+from collections import deque
+from dataclasses import dataclass, field
+
+from ..errors import RequestError
+from ..sampling.params import I32_MAX, SamplingParams, check_settings, make_params
+
+
+@dataclass
+class Request:
+    rid: object
+    prompt: list
+    max_new: int
+    sampling: SamplingParams = field(default_factory=SamplingParams)
+    stop_ids: frozenset = frozenset()
+    generated: list = field(default_factory=list)
+    computed: int = 0
+    finish: str = None
+    error: str = None
+    order: int = 0
+    preemptions: int = 0
+    needs_penalty_start: bool = True
+    t_admit: float = None
+    t_first: float = None
+    t_end: float = None
+
+    @property
+    def tokens(self):
+        return self.prompt + self.generated
+
+    @property
+    def remaining(self):
+        return len(self.prompt) + len(self.generated) - self.computed
+
+
+@dataclass
+class Planned:
+    request: Request
+    start: int
+    count: int
+    sample: bool            # the portion ends at the request's last known token: its logits are wanted
+
+
+class Scheduler:
+    def __init__(self, cache, vocab, max_tokens_per_step=2048, chunk=2048):
+        self.cache, self.vocab = cache, int(vocab)
+        self.budget, self.chunk = int(max_tokens_per_step), int(chunk)
+        self.waiting, self.running = deque(), []
+        self.counter = 0
+        self.stats = dict(preemptions=0, steps=0)
+
+    # -------------------------------------------------------------------------------------------- admission
+    def capacity(self):
+        return min(self.cache.max_context, self.cache.num_pages * self.cache.page_size)
+
+    def check(self, prompt, max_new, sampling=None):
+        """None when the request fits this engine, else the reason (the request is refused alone)."""
+        try:
+            ids = list(prompt)
+        except TypeError:
+            return "the prompt must be 1 or more integer token ids"
+        if not ids or any(isinstance(t, bool) or not isinstance(t, int) for t in ids):
+            return "the prompt must be 1 or more integer token ids"
+        if min(ids) < 0 or max(ids) >= self.vocab:
+            return f"token ids must be 0..{self.vocab - 1}"
+        if isinstance(max_new, bool) or not isinstance(max_new, int) or not 1 <= max_new <= I32_MAX:
+            return f"max_new must be an integer 1..{I32_MAX}"
+        if len(ids) + max_new > self.capacity():
+            return f"prompt ({len(ids)} tokens) + max_new ({max_new}) is over the context of {self.capacity()}"
+        return check_settings(sampling, self.vocab)
+
+    def add(self, rid, prompt, max_new, sampling=None, stop_ids=()):
+        why = self.check(prompt, max_new, sampling)
+        if why is not None:
+            raise RequestError(why)
+        r = Request(rid, [int(t) for t in prompt], int(max_new), make_params(sampling), frozenset(stop_ids))
+        self.counter += 1
+        r.order = self.counter
+        self.waiting.append(r)
+        return r
+
+    def busy(self):
+        return bool(self.waiting or self.running)
+
+    # -------------------------------------------------------------------------------------------- planning
+    def _preempt(self, r):
+        self.cache.release(r.rid)
+        self.running.remove(r)
+        r.computed = 0
+        r.preemptions += 1
+        r.needs_penalty_start = True
+        self.waiting.appendleft(r)
+        self.stats["preemptions"] += 1
+
+    def plan(self):
+        """-> list of Planned for the next step (empty when nothing can run).  Pages are not taken here: the step
+        function takes them; this only makes sure they are there."""
+        cache = self.cache
+        free = list(cache.free_pages())
+        plan, used = [], 0
+
+        def fits(r, n):
+            return all(a <= b for a, b in zip(cache.pages_needed(r.rid, n), free))
+
+        def take(r, n):
+            for gi, a in enumerate(cache.pages_needed(r.rid, n)):
+                free[gi] -= a
+
+        # 1. every decoding request gets its token; newest running requests give way when pages are short
+        decoding = [r for r in self.running if r.remaining == 1]
+        for r in list(decoding):
+            if r not in self.running:
+                continue
+            while not fits(r, 1):
+                victim = max(self.running, key=lambda q: q.order)
+                self._preempt(victim)
+                plan = [p for p in plan if p.request is not victim]
+                free = list(cache.free_pages())
+                for p in plan:
+                    take(p.request, p.count)
+                if victim is r:
+                    break
+            if r in self.running:
+                plan.append(Planned(r, r.computed, 1, True))
+                take(r, 1)
+        used = len(plan)
+        # 2. portions of prompts already running, first come first served
+        for r in self.running:
+            if r.remaining <= 1 or used >= self.budget:
+                continue
+            n = min(r.remaining, self.chunk, self.budget - used)
+            while n > 0 and not fits(r, n):
+                n = self._shrink(r, n, free)
+            if n > 0:
+                plan.append(Planned(r, r.computed, n, n == r.remaining))
+                take(r, n)
+                used += n
+        # 3. new admissions, in order, while the whole of their known tokens (+1) fits
+        while self.waiting and used < self.budget and cache.can_admit():
+            r = self.waiting[0]
+            whole = len(r.prompt) + len(r.generated) + 1
+            pages = -(-whole // cache.page_size)
+            if any(pages > f for f in free):
+                break
+            self.waiting.popleft()
+            cache.admit(r.rid)
+            self.running.append(r)
+            n = min(r.remaining, self.chunk, self.budget - used)
+            plan.append(Planned(r, r.computed, n, n == r.remaining))
+            take(r, n)
+            used += n
+        return plan
+
+    def _shrink(self, r, n, free):
+        """the largest portion under n that the free pages allow (0 when not even one token fits)"""
+        cache = self.cache
+        room = min(free) * cache.page_size + (-cache.get(r.rid).reserved) % cache.page_size
+        return max(0, min(n - 1, room))
+
+    # -------------------------------------------------------------------------------------------- results
+    def finish(self, r, reason, error=None):
+        r.finish, r.error = reason, error
+        if r in self.running:
+            self.running.remove(r)
+            self.cache.release(r.rid)
+        elif r in self.waiting:
+            self.waiting.remove(r)
+
+    def advance(self, plan, sampled):
+        """After the step: plan as returned by plan(), sampled = the token of each Planned with sample=True, in
+        order.  -> requests that ended."""
+        ended, it = [], iter(sampled)
+        for p in plan:
+            r = p.request
+            r.computed += p.count
+            if not p.sample:
+                continue
+            t = int(next(it))
+            if t in r.stop_ids:
+                self.finish(r, "stop")
+                ended.append(r)
+                continue
+            r.generated.append(t)
+            if len(r.generated) >= r.max_new:
+                self.finish(r, "length")
+                ended.append(r)
+        self.stats["steps"] += 1
+        return ended
+
+    def cancel(self, r):
+        if r.finish is None:
+            self.finish(r, "cancel")

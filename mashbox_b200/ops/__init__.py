@@ -1,0 +1,203 @@
+"""Python faces of the hand-written CUDA kernels (mashbox_b200/csrc) and of the one library routine the engine uses.
+
+Every function works on CUDA tensors, launches on torch's current stream and raises KernelError when the kernel
+refuses the sizes.  There is no CPU or library fallback for a kernel: if the extension cannot be built or no GPU is
+there, the call fails.  The only library call is the bf16 matrix product (cuBLAS through torch.mm), which stands where
+the reference engine, too, hands its contractions to a library (src/mashbox/ops/dense16.py:73-75).
+"""
+import ctypes
+
+import torch
+
+from ..errors import KernelError
+from .build import load_library
+
+c_int, c_float, c_void_p = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
+
+DEVICE_ERRORS = {1: "a token id outside the vocabulary", 2: "a position whose cache page the block table does not hold",
+                 3: "a page id outside the cache pool", 4: "a bounded wait inside a kernel ran out"}
+
+
+def _suffix(dtype):
+    if dtype == torch.float32:
+        return "f32"
+    if dtype == torch.bfloat16:
+        return "bf16"
+    raise KernelError(f"no kernel for dtype {dtype}")
+
+
+def _p(t):
+    return None if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("mashbox_b200 kernels run on CUDA tensors only; there is no CPU fallback")
+
+
+def _check(code, what):
+    if code == 0:
+        return
+    if code == -2:
+        raise KernelError(f"{what}: the kernel does not take these sizes")
+    raise KernelError(f"{what}: CUDA error {code} at launch")
+
+
+_fn_cache = {}
+
+
+def _fn(lib, name, argtypes):
+    key = (lib, name)
+    f = _fn_cache.get(key)
+    if f is None:
+        f = getattr(load_library(lib), name)
+        f.argtypes = argtypes
+        f.restype = c_int
+        _fn_cache[key] = f
+    return f
+
+
+def new_error_word(device):
+    return torch.zeros(1, dtype=torch.int32, device=device)
+
+
+def check_error_word(err):
+    """Reads the device error word (a synchronisation) and raises if a kernel left a code there."""
+    code = int(err.item())
+    if code:
+        err.zero_()
+        raise KernelError("a kernel reported: " + DEVICE_ERRORS.get(code, f"code {code}"))
+
+
+# ------------------------------------------------------------------------------------------------ elementwise
+def embed(tokens, table, x, err):
+    """x[n] = table[tokens[n]] into the float32 residual stream x (N, D)."""
+    _cuda(tokens, table, x)
+    N, D = x.shape
+    f = _fn("elementwise", "mb_embed_" + _suffix(table.dtype),
+            [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(f(_p(tokens), _p(table), _p(x), N, D, table.shape[0], _p(err), _stream()), "embed")
+
+
+def add_rmsnorm(x, delta, delta_bias, weight, eps, out, rows=None):
+    """v = x (+ delta (+ delta_bias)); written back to x unless rows is given; out = v * rsqrt(mean(v^2)+eps) * weight.
+    x (N, D) float32; delta (N, D) and out in the activation dtype; weight, delta_bias float32; rows int32 indexes."""
+    _cuda(x, delta, weight, out, rows)
+    D = x.shape[1]
+    n_out = out.shape[0]
+    f = _fn("elementwise", "mb_add_rmsnorm_" + _suffix(out.dtype),
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_void_p])
+    _check(f(_p(x), _p(delta), _p(delta_bias), _p(rows), _p(weight), float(eps), _p(out), n_out, D, _stream()),
+           "add_rmsnorm")
+
+
+def rope_kv_write(qkv, bias, positions, tok_seq, table, kpool, vpool, freqs, H, KV, HD, RD, pairing, page, num_pages,
+                  err):
+    """qkv (N, (H + 2 KV) HD): adds bias, rotates q in place, writes rotated k and v to their pages (kpool/vpool None:
+    q only).  freqs (RD/2,) float32 angle per position step, None = no rotation; pairing 0 adjacent, 1 halves."""
+    _cuda(qkv, positions, tok_seq, table, kpool, vpool, freqs)
+    N = qkv.shape[0]
+    f = _fn("elementwise", "mb_rope_kv_write_" + _suffix(qkv.dtype),
+            [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p] + [c_int] * 8
+            + [c_void_p, c_void_p])
+    _check(f(_p(qkv), _p(bias), _p(positions), _p(tok_seq), _p(table), table.shape[1], _p(kpool), _p(vpool), _p(freqs),
+             N, H, KV, HD, RD, pairing, page, num_pages, _p(err), _stream()), "rope_kv_write")
+
+
+def swiglu(gu, out):
+    """gu (N, 2F) = [gate | up] -> out (N, F) = silu(gate) * up"""
+    _cuda(gu, out)
+    N, F = out.shape
+    f = _fn("elementwise", "mb_swiglu_" + _suffix(out.dtype), [c_void_p, c_void_p, c_int, c_int, c_void_p])
+    _check(f(_p(gu), _p(out), N, F, _stream()), "swiglu")
+
+
+# ------------------------------------------------------------------------------------------------ contractions
+def linear(a, w, out=None, out_dtype=None):
+    """a (N, K) @ w (M, K)^T -> (N, M).  float32: the package's own fixed-order FFMA kernel (no TF32, no tensor
+    cores).  bfloat16: cuBLAS with float accumulation; out_dtype float32 keeps the accumulator's precision."""
+    _cuda(a, w)
+    N, K = a.shape
+    M = w.shape[0]
+    if a.dtype == torch.float32:
+        if out is None:
+            out = torch.empty((N, M), dtype=torch.float32, device=a.device)
+        f = _fn("gemm_f32", "mb_gemm_f32", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+        _check(f(_p(a), _p(w), _p(out), N, M, K, _stream()), "gemm_f32")
+        return out
+    if out_dtype is not None and out_dtype != a.dtype:
+        r = torch.mm(a, w.t(), out_dtype=out_dtype)
+        if out is not None:
+            out.copy_(r)
+            return out
+        return r
+    if out is not None:
+        return torch.mm(a, w.t(), out=out)
+    return torch.mm(a, w.t())
+
+
+# ------------------------------------------------------------------------------------------------ attention
+def attention_simple(q, q_stride, out, positions, tok_seq, table, kpool, vpool, H, KV, HD, page, num_pages, window,
+                     scale, err):
+    _cuda(q, out, positions, tok_seq, table, kpool, vpool)
+    N = out.shape[0]
+    f = _fn("attention_simple", "mb_attn_simple_" + _suffix(out.dtype),
+            [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p] + [c_int] * 7
+            + [c_float, c_void_p, c_void_p])
+    _check(f(_p(q), q_stride, _p(out), _p(positions), _p(tok_seq), _p(table), table.shape[1], _p(kpool), _p(vpool), N,
+             H, KV, HD, page, num_pages, window or 0, float(scale), _p(err), _stream()), "attention_simple")
+
+
+def attention_mma_supports(HD):
+    return HD in (16, 32, 64, 128)
+
+
+def attention_mma(q, q_stride, out, kpool, vpool, items, n_items, decode, q_start, q_len, pos0, part_base, seq_row,
+                  table,
+                  part_o, part_ml, max_splits, H, KV, HD, page, num_pages, window, scale, err):
+    _cuda(q, out, kpool, vpool, items, q_start, q_len, pos0, part_base, table, part_o, part_ml)
+    f = _fn("attention_mma", "mb_attn_mma_bf16",
+            [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
+             c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p] + [c_int] * 7 + [c_float, c_void_p, c_void_p])
+    _check(f(_p(q), q_stride, _p(out), _p(kpool), _p(vpool), _p(items), n_items, 1 if decode else 0, _p(q_start),
+             _p(q_len), _p(pos0), _p(part_base), _p(seq_row), _p(table), table.shape[1], _p(part_o), _p(part_ml), max_splits, H, KV,
+             HD, page, num_pages, window or 0, float(scale), _p(err), _stream()), "attention_mma")
+
+
+def attention_merge(part_o, part_ml, part_tok, n_part, out, H, HD, max_splits):
+    _cuda(part_o, part_ml, part_tok, out)
+    f = _fn("attention_mma", "mb_attn_merge_bf16",
+            [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_p(part_o), _p(part_ml), _p(part_tok), n_part, _p(out), H, HD, max_splits, _stream()), "attention_merge")
+
+
+# ------------------------------------------------------------------------------------------------ sampling
+def sample_params_size():
+    lib = load_library("sampling")
+    lib.mb_sample_params_size.restype = c_int
+    return lib.mb_sample_params_size()
+
+
+def sample(logits, work, params, cnt, seen, n_rows, out):
+    """logits (R, V) float32; work (n_rows, V) float32 scratch; params: uint8 tensor of n_rows packed RowParams;
+    cnt (slots, V) int32 / seen (slots, V) uint8 penalty state or None; out (n_rows,) int32."""
+    _cuda(logits, work, params, cnt, seen, out)
+    f = _fn("sampling", "mb_sample", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p])
+    _check(f(_p(logits), _p(work), _p(params), _p(cnt), _p(seen), n_rows, logits.shape[1], _p(out), _stream()), "sample")
+
+
+def argmax(logits, out):
+    _cuda(logits, out)
+    f = _fn("sampling", "mb_argmax", [c_void_p, c_int, c_int, c_void_p, c_void_p])
+    _check(f(_p(logits), logits.shape[0], logits.shape[1], _p(out), _stream()), "argmax")
+
+
+def penalty_fill(cnt_row, seen_row, tokens, n_prompt, n_total, V):
+    _cuda(cnt_row, seen_row, tokens)
+    f = _fn("sampling", "mb_penalty_fill", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_p(cnt_row), _p(seen_row), _p(tokens), n_prompt, n_total, V, _stream()), "penalty_fill")

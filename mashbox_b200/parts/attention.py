@@ -1,0 +1,165 @@
+"""The attention mixer: grouped-query attention over the paged cache.
+
+q = h Wq^T (+bq), k, v likewise from one fused product (the three weights are concatenated at load); q and k are
+rotated, k and v written to the layer's pages, then every query attends to the cached keys of its own sequence up to
+its own position -- the step's own tokens are read from the cache like the older ones, so a portion of a prompt, a
+single decoded token and a whole prompt all take the same path.  Query head h reads kv head h // (H / KV); scores are
+scaled by head_dim^-0.5 (or `scale`), softmax and the weighted sum are float32; `window` w limits a query to the last w
+positions.  Formulas: src/mashbox/gguf/archs/dense.py:339-348, src/mashbox/runtime/attention.py:54-93.
+
+Kernels: the float32 path, and head sizes the tensor-core kernel does not take, use the plain paged kernel (one warp
+per token and head, fixed order).  The bf16 path packs the G query heads of a kv head into the rows of an MMA tile and
+runs the flash kernel: row tiles of 64 for prompt portions, tiles of 16 with the keys split over warps (and over
+blocks, merged by a second kernel) for decode tokens.  `prepare` builds that work list on the host.
+"""
+import numpy as np
+
+from ..cache.manager import CacheNeed
+from ..errors import ConfigError
+from ..weights.loader import Want
+from .base import PartSpec, make, register
+
+DECODE_ROWS, PREFILL_ROWS, KEY_TILE = 16, 64, 64
+
+
+class Attention:
+    def __init__(self, hidden, heads, kv_heads, head_dim, bias=False, position=None, window=None, scale=None,
+                 prefix="", names=None):
+        self.D, self.H, self.KV, self.HD = int(hidden), int(heads), int(kv_heads), int(head_dim)
+        if self.H % self.KV:
+            raise ConfigError(f"{heads} heads do not divide into {kv_heads} kv heads")
+        self.bias, self.window = bool(bias), (int(window) if window else None)
+        self.scale = float(scale) if scale else self.HD ** -0.5
+        self.prefix = prefix
+        n = dict(q="attn_q", k="attn_k", v="attn_v", o="attn_output")
+        n.update(names or {})
+        self.names = {k: prefix + v for k, v in n.items()}
+        self.position = make("position", position) if isinstance(position, PartSpec) else position
+        self.wqkv = self.bqkv = self.wo = self.bo = None
+
+    # ------------------------------------------------------------------------------------------ weights
+    def wants(self):
+        H, KV, HD, D = self.H, self.KV, self.HD, self.D
+        shapes = dict(q=(H * HD, D), k=(KV * HD, D), v=(KV * HD, D), o=(D, H * HD))
+        w = [Want(self.names[r] + ".weight", shapes[r], "matrix") for r in "qkvo"]
+        if self.bias:
+            w += [Want(self.names[r] + ".bias", (shapes[r][0],), "vector") for r in "qkvo"]
+        return w + (self.position.wants() if self.position is not None else [])
+
+    def bind(self, tensors, env):
+        import torch
+        t = lambda r, s: tensors[self.names[r] + s]
+        self.wqkv = torch.cat([t("q", ".weight"), t("k", ".weight"), t("v", ".weight")], 0).contiguous()
+        self.wo = t("o", ".weight")
+        if self.bias:
+            self.bqkv = torch.cat([t("q", ".bias"), t("k", ".bias"), t("v", ".bias")], 0).contiguous()
+            self.bo = t("o", ".bias")
+        if self.position is not None:
+            self.position.bind(tensors, env)
+
+    def cache_need(self):
+        return CacheNeed("window" if self.window else "full", self.KV, self.HD, self.window)
+
+    def state_need(self):
+        return None
+
+    # ------------------------------------------------------------------------------------------ planning
+    def uses_mma(self, ctx):
+        import torch
+        return ctx.dtype == torch.bfloat16 and ctx.ops.attention_mma_supports(self.HD) and not ctx.options.get(
+            "plain_attention", False)
+
+    def plan_key(self):
+        return ("attention", self.H // self.KV, self.KV, self.window)
+
+    def prepare(self, ctx):
+        """Work list of the flash kernel for this step: (sequence, row tile, split, splits) per block, decode-form
+        sequences (at most 16 packed rows) and prompt-form ones apart; sequences cut into splits get a place in the
+        partial buffers."""
+        if not self.uses_mma(ctx):
+            return
+        key = self.plan_key()
+        if key in ctx.memo:
+            return
+        G, KV = self.H // self.KV, self.KV
+        target = int(ctx.options.get("attention_target_blocks", 296))
+        max_splits = int(ctx.options.get("attention_max_splits", 16))
+        S = ctx.S
+        tiles = [1 if ctx.q_len[s] * G <= DECODE_ROWS else -(-ctx.q_len[s] * G // PREFILL_ROWS) for s in range(S)]
+        base = max(1, sum(tiles) * KV)
+        dec, pre, part_base, part_tok = [], [], [-1] * S, []
+        for s in range(S):
+            hi = ctx.pos0[s] + ctx.q_len[s]
+            lo = max(0, ctx.pos0[s] - self.window + 1) if self.window else 0
+            kv_tiles = -(-(hi - lo // KEY_TILE * KEY_TILE) // KEY_TILE)
+            ns = 1
+            if ctx.q_len[s] <= DECODE_ROWS and base < target:
+                ns = max(1, min(max_splits, -(-target // base), kv_tiles // 2))
+                ns = 1 << (ns.bit_length() - 1)                    # a power of two: few distinct work-list shapes
+            if ns > 1:
+                part_base[s] = len(part_tok) // 2
+                for t in range(ctx.q_len[s]):
+                    part_tok += [ctx.q_start[s] + t, ns]
+            dst = dec if ctx.q_len[s] * G <= DECODE_ROWS else pre
+            for m in range(tiles[s]):
+                for sp in range(ns):
+                    dst.append((-(ctx.pos0[s] + (m + 1) * PREFILL_ROWS // G), s, m, sp, ns))
+        pre.sort()                                                  # the tiles with the most keys first
+        name = "attn%d_" % len([k for k in ctx.memo if k[0] == "attention"])
+        flat = lambda items: np.asarray([i[1:] for i in items], np.int32).reshape(-1)
+        ctx.inputs.add(name + "dec", flat(dec))
+        ctx.inputs.add(name + "pre", flat(pre))
+        ctx.inputs.add(name + "part_base", np.asarray(part_base, np.int32))
+        ctx.inputs.add(name + "part_tok", np.asarray(part_tok, np.int32))
+        ctx.memo[key] = dict(name=name, n_dec=len(dec), n_pre=len(pre), n_part=len(part_tok) // 2,
+                             max_splits=max_splits)
+
+    # ------------------------------------------------------------------------------------------ forward
+    def forward(self, ctx, h, run):
+        import torch
+        ops, N = ctx.ops, ctx.N
+        H, KV, HD = self.H, self.KV, self.HD
+        width = (H + 2 * KV) * HD
+        qkv = ctx.ws.get("qkv", N, (width,), ctx.dtype)
+        ops.linear(h, self.wqkv, out=qkv)
+        group, kpool, vpool = ctx.cache.layer_cache(run.cache)
+        table = group.device_table
+        page, pages = ctx.cache.page_size, ctx.cache.num_pages
+        freqs, rd, pairing = (None, HD, 0)
+        if self.position is not None:
+            rot = self.position.rotation()
+            if rot is None:
+                if self.bias:
+                    raise ConfigError("a position encoding with its own kernel cannot be combined with q/k/v biases")
+                self.position.apply(ctx, qkv, H, KV, HD)
+            else:
+                freqs, rd, pairing = rot
+        ops.rope_kv_write(qkv, self.bqkv, ctx.dev("positions"), ctx.dev("tok_row"), table,
+                          kpool if run.write else None, vpool if run.write else None, freqs, H, KV, HD, rd, pairing,
+                          page, pages, ctx.err)
+        out = ctx.ws.get("attn_out", N, (H * HD,), ctx.dtype)
+        if self.uses_mma(ctx):
+            plan = ctx.memo[self.plan_key()]
+            nm = plan["name"]
+            n_part, ms = plan["n_part"], plan["max_splits"]
+            part_o = part_ml = None
+            if n_part:
+                part_o = ctx.ws.get("attn_part_o", n_part * H * ms, (HD,), torch.float32, reserve=0)
+                part_ml = ctx.ws.get("attn_part_ml", n_part * H * ms, (2,), torch.float32, reserve=0)
+            for form, n_items, decode in ((nm + "pre", plan["n_pre"], False), (nm + "dec", plan["n_dec"], True)):
+                if n_items:
+                    ops.attention_mma(qkv, width, out, kpool, vpool, ctx.dev(form), n_items, decode, ctx.dev("q_start"),
+                                      ctx.dev("q_len"), ctx.dev("pos0"), ctx.dev(nm + "part_base"), ctx.dev("seq_row"),
+                                      table, part_o, part_ml, ms, H, KV, HD, page, pages, self.window, self.scale,
+                                      ctx.err)
+            if n_part:
+                ops.attention_merge(part_o, part_ml, ctx.dev(nm + "part_tok"), n_part, out, H, HD, ms)
+        else:
+            ops.attention_simple(qkv, width, out, ctx.dev("positions"), ctx.dev("tok_row"), table, kpool, vpool, H, KV,
+                                 HD, page, pages, self.window, self.scale, ctx.err)
+        y = ctx.ws.get("delta", N, (self.D,), ctx.dtype)
+        ops.linear(out, self.wo, out=y)
+        return y, self.bo
+
+
+register("mixer", "attention", Attention)

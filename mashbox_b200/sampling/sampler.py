@@ -1,0 +1,60 @@
+"""Picks the next token of each row on the device and brings the ids to the host once per step.
+
+Rows that are plainly greedy (temperature 0, no penalties) take the argmax kernel (lowest index of the maximum).  Any
+other row takes the sampling kernel: penalties -> temperature -> top_k -> top_p -> min_p -> one Gumbel-max draw, with
+random bits from Philox keyed by (seed, index of the token in the row's answer), so a row redraws the same tokens when
+it is batched differently or recomputed after a preemption.  Penalty state (counts of generated tokens, the set of
+prompt + generated tokens) lives per state slot and is made only when a request asks for a penalty.
+"""
+import numpy as np
+import torch
+
+from .. import ops as kernels
+
+ROW = np.dtype([("temperature", "<f4"), ("top_p", "<f4"), ("min_p", "<f4"), ("rep", "<f4"), ("freq", "<f4"),
+                ("pres", "<f4"), ("top_k", "<i4"), ("slot", "<i4"), ("seed_lo", "<u4"), ("seed_hi", "<u4"),
+                ("step", "<i4"), ("logits_row", "<i4")])
+
+
+class Sampler:
+    def __init__(self, vocab, max_slots, device):
+        self.V, self.max_slots, self.device = int(vocab), int(max_slots), device
+        self.cnt = self.seen = None
+        self.work = None
+
+    def _penalty_state(self):
+        if self.cnt is None:
+            self.cnt = torch.zeros((self.max_slots, self.V), dtype=torch.int32, device=self.device)
+            self.seen = torch.zeros((self.max_slots, self.V), dtype=torch.uint8, device=self.device)
+
+    def start_row(self, slot, prompt, generated):
+        """Rebuilds the penalty state of one slot from the request's tokens (at its first token, and again when a
+        preempted request has been recomputed)."""
+        self._penalty_state()
+        self.cnt[slot].zero_()
+        self.seen[slot].zero_()
+        toks = torch.tensor(list(prompt) + list(generated), dtype=torch.int32).to(self.device)
+        kernels.penalty_fill(self.cnt[slot], self.seen[slot], toks, len(prompt), len(prompt) + len(generated), self.V)
+
+    def sample(self, logits, rows):
+        """logits (R, V) float32 on the device; rows: [(SamplingParams, token index, state slot or -1)], one per row of
+        logits in order.  -> list of token ids (one device-to-host copy)."""
+        n = len(rows)
+        if n == 0:
+            return []
+        out = torch.empty(n, dtype=torch.int32, device=self.device)
+        if all(p.plain_greedy for p, _, _ in rows):
+            kernels.argmax(logits[:n], out)
+            return out.tolist()
+        packed = np.zeros(n, ROW)
+        for i, (p, step, slot) in enumerate(rows):
+            packed[i] = (p.temperature, p.top_p, p.min_p, p.repetition_penalty, p.frequency_penalty,
+                         p.presence_penalty, p.top_k, slot if p.penalised else -1, p.seed & 0xFFFFFFFF,
+                         (p.seed >> 32) & 0xFFFFFFFF, step, i)
+        if any(p.penalised for p, _, _ in rows):
+            self._penalty_state()
+        params = torch.from_numpy(packed.view(np.uint8).copy()).to(self.device)
+        if self.work is None or self.work.shape[0] < n:
+            self.work = torch.empty((max(n, self.max_slots), self.V), dtype=torch.float32, device=self.device)
+        kernels.sample(logits, self.work, params, self.cnt, self.seen, n, out)
+        return out.tolist()

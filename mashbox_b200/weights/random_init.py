@@ -1,0 +1,46 @@
+"""Random-weights mode: a model's tensors from a configuration and a seed, and a model folder written from them.
+
+Every tensor has its own generator, seeded from (seed, crc32 of the tensor's name), so a tensor's values depend on
+neither the order tensors are made in nor on which other tensors exist.  Matrices are N(0, std), norm weights
+1 + N(0, norm_std), biases N(0, std).  The architecture entry says which tensors a configuration has (Hugging Face
+names and shapes); nothing here knows a model.
+"""
+import json
+import os
+import zlib
+
+import torch
+
+from .safetensors_io import write_safetensors
+
+
+def tensor_seed(seed, name):
+    return (int(seed) * 1_000_003 + zlib.crc32(name.encode())) % (1 << 63)
+
+
+def random_tensors(shapes, seed, dtype=torch.float32, device="cpu", std=0.02, norm_std=0.01):
+    """shapes: {name: (shape, kind)} with kind "matrix" | "norm" | "bias" -> {name: tensor of dtype on device}."""
+    out = {}
+    for name, (shape, kind) in shapes.items():
+        g = torch.Generator(device=device)
+        g.manual_seed(tensor_seed(seed, name))
+        x = torch.randn(tuple(shape), generator=g, device=device, dtype=torch.float32)
+        if kind == "norm":
+            x = 1.0 + norm_std * x
+        else:
+            x = std * x
+        out[name] = x.to(dtype)
+    return out
+
+
+def write_model_folder(folder, config, seed, dtype=torch.float32, std=0.02, norm_std=0.01):
+    """Writes folder/config.json and folder/model.safetensors for `config` (an architecture's typed configuration)
+    with seeded random weights stored as `dtype`.  -> folder"""
+    from ..config.registry import architecture
+    entry = architecture(config.architecture)
+    os.makedirs(folder, exist_ok=True)
+    with open(os.path.join(folder, "config.json"), "w") as fh:
+        json.dump(config.to_hf(), fh, indent=1)
+    tensors = random_tensors(entry.stored_tensors(config), seed, dtype=dtype, std=std, norm_std=norm_std)
+    write_safetensors(os.path.join(folder, "model.safetensors"), tensors)
+    return folder

@@ -1,0 +1,52 @@
+"""Tiny configurations and shared plumbing of the tests.  Model folders are made in temporary folders."""
+import functools
+import json
+import os
+
+import numpy as np
+import torch
+
+from mashbox_b200.config.llama import LlamaConfig, RopeScaling
+from mashbox_b200.weights.random_init import write_model_folder
+from tests.plain import llama as plain
+
+# two tiny configurations that differ in every size and option
+TINY_A = LlamaConfig(architecture="LlamaForCausalLM", num_layers=2, hidden=64, num_heads=4, num_kv_heads=2, head_dim=16,
+                     intermediate=192, vocab=256, rms_eps=1e-5, rope_theta=10000.0, rope_scaling=None,
+                     tie_embeddings=True, attention_bias=False, max_position=256)
+TINY_B = LlamaConfig(architecture="LlamaForCausalLM", num_layers=3, hidden=96, num_heads=6, num_kv_heads=1, head_dim=32,
+                     intermediate=320, vocab=509, rms_eps=1e-6, rope_theta=500000.0,
+                     rope_scaling=RopeScaling("llama3", 8.0, 1.0, 4.0, 64), tie_embeddings=False, attention_bias=True,
+                     max_position=512)
+TINY = {"A": (TINY_A, 0, 16), "B": (TINY_B, 1, 8)}          # config, seed, page size
+STD = 0.1       # random weights wide enough that attention is not uniform and logits are of order one
+
+
+def make_folder(tmp, name, store="float32"):
+    cfg, seed, _ = TINY[name]
+    d = os.path.join(str(tmp), f"tiny_{name}_{store}")
+    if not os.path.isdir(d):
+        write_model_folder(d, cfg, seed, dtype=getattr(torch, store), std=STD, norm_std=0.1)
+    return d
+
+
+@functools.lru_cache(maxsize=None)
+def _plain_model(folder):
+    return plain.read_model(folder)
+
+
+def plain_logits(folder, tokens):
+    """float64 logits (T, V) of the plain implementation for one whole sequence"""
+    cfg, W = _plain_model(folder)
+    return plain.forward(cfg, W, tokens).numpy()
+
+
+def prompts_for(name, lengths, seed=0):
+    cfg = TINY[name][0]
+    rng = np.random.default_rng(seed)
+    return [rng.integers(0, cfg.vocab, n).tolist() for n in lengths]
+
+
+def store_for(dtype):
+    """weights are stored in the dtype the run computes in, so the plain implementation sees the same values"""
+    return "float32" if dtype == "float32" else "bfloat16"

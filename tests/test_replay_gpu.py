@@ -1,0 +1,116 @@
+"""-m gpu: the engine's step function (through the trace replay) against the plain implementation, in float32 and
+bfloat16: whole prompts; most of a prompt in one step and the last 32 tokens one by one; portions of changing size
+down to two tokens; mixed batches of up to four live requests with so few pages that they are used again."""
+import numpy as np
+import pytest
+import torch
+
+from tests import helpers as H
+from tests.tolerances import assert_logits
+
+pytestmark = pytest.mark.gpu
+CASES = [(n, d) for n in ("A", "B") for d in ("float32", "bfloat16")]
+
+
+def runner_for(tmp, name, dtype, max_tokens, options=None):
+    from mashbox_b200.engine.replay import make_runner
+    folder = H.make_folder(tmp, name, H.store_for(dtype))
+    return folder, make_runner(folder, dtype, max_tokens, page_size=H.TINY[name][2], options=options)
+
+
+def replay(runner, steps):
+    from mashbox_b200.engine.replay import run_step
+    out = {}
+    for i, s in enumerate(steps):
+        s = dict(s, step=i)
+        r = run_step(runner, s)
+        if r is not None:
+            out[i] = r.numpy()
+    return out
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_whole_prompts(tmp_path_factory, name, dtype):
+    tmp = tmp_path_factory.mktemp("m")
+    folder, runner = runner_for(tmp, name, dtype, 256)
+    for p in H.prompts_for(name, (7, 13, 70, 130)):
+        got = replay(runner, [dict(entries=[dict(id="a", tokens=p, want=list(range(len(p))))], end=["a"])])[0]
+        assert_logits(got, H.plain_logits(folder, p), dtype, f"whole prompt of {len(p)}")
+    runner.cache.check()
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_last_32_one_by_one(tmp_path_factory, name, dtype):
+    tmp = tmp_path_factory.mktemp("m")
+    folder, runner = runner_for(tmp, name, dtype, 192)
+    for p in H.prompts_for(name, (40, 150), seed=1):
+        cut = len(p) - 32
+        steps = [dict(entries=[dict(id="a", tokens=p[:cut], want=[cut - 1])], end=[])]
+        steps += [dict(entries=[dict(id="a", tokens=[p[i]], want=[0])], end=["a"] if i == len(p) - 1 else [])
+                  for i in range(cut, len(p))]
+        out = replay(runner, steps)
+        got = np.concatenate([out[i] for i in range(len(steps))])
+        want = H.plain_logits(folder, p)[cut - 1:]
+        assert_logits(got, want, dtype, f"prompt of {len(p)}, last 32 decoded")
+    runner.cache.check()
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_portions_of_changing_size(tmp_path_factory, name, dtype):
+    tmp = tmp_path_factory.mktemp("m")
+    folder, runner = runner_for(tmp, name, dtype, 192)
+    p = H.prompts_for(name, (171,), seed=2)[0]
+    sizes, at, steps = [2, 17, 3, 64, 2, 31, 16, 8, 5, 2, 21], 0, []
+    for s in sizes:
+        s = min(s, len(p) - at)
+        if s <= 0:
+            break
+        steps.append(dict(entries=[dict(id="a", tokens=p[at:at + s], want=list(range(s)))], end=[]))
+        at += s
+    assert at == len(p)
+    out = replay(runner, steps)
+    got = np.concatenate([out[i] for i in range(len(steps))])
+    assert_logits(got, H.plain_logits(folder, p), dtype, "portions")
+
+
+def mixed_trace(prompts, rng, max_live=4):
+    """Random schedule: up to max_live live requests, each step feeds some of them a portion (2..24 tokens) or, near
+    their end, single tokens; a finished request ends and a new one starts on the pages it gave back."""
+    todo = list(enumerate(prompts))
+    live, steps, where = {}, [], {}
+    while todo or live:
+        while todo and len(live) < max_live:
+            i, p = todo.pop(0)
+            live[i] = 0
+        entries, end = [], []
+        for i in list(live):
+            if rng.random() < 0.25 and len(live) > 1:
+                continue                                   # left out of this step, goes on later
+            p, at = prompts[i], live[i]
+            left = len(p) - at
+            n = 1 if left <= 6 else int(min(left, rng.integers(2, 25)))
+            want = list(range(n))
+            entries.append(dict(id=f"r{i}", tokens=p[at:at + n], want=want))
+            where.setdefault(i, []).append((len(steps), len([w for e in entries[:-1] for w in e["want"]]), n))
+            live[i] += n
+            if live[i] == len(p):
+                end.append(f"r{i}")
+                del live[i]
+        if entries:
+            steps.append(dict(entries=entries, end=end))
+    return steps, where
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_mixed_batches_with_page_reuse(tmp_path_factory, name, dtype):
+    tmp = tmp_path_factory.mktemp("m")
+    lengths = (50, 33, 64, 20, 61, 47, 9, 58)
+    prompts = H.prompts_for(name, lengths, seed=3)
+    folder, runner = runner_for(tmp, name, dtype, 4 * 64)         # four live requests of at most 64 tokens
+    steps, where = mixed_trace(prompts, np.random.default_rng(5))
+    out = replay(runner, steps)
+    for i, p in enumerate(prompts):
+        got = np.concatenate([out[s][o:o + n] for s, o, n in where[i]])
+        assert_logits(got, H.plain_logits(folder, p), dtype, f"mixed, request {i}")
+    runner.cache.check()
+    assert all(f == runner.cache.num_pages for f in runner.cache.free_pages())
