@@ -43,9 +43,18 @@ class ModelRunner:
     def step(self, entries):
         """entries: [(request id, tokens, want)] -> float32 logits (sum of wants, vocab) on the device, in the order
         of the entries and of each `want`; None when nothing is wanted.  The tensor is valid until the next step."""
-        cache = self.cache
         if not entries:
             return None
+        ctx = self.begin(entries)
+        decode_only = self.use_graphs and ctx.N == ctx.S and ctx.n_out == ctx.S
+        logits = self._run_graph(ctx) if decode_only else self.model.forward(ctx)
+        self.commit(entries)
+        return logits
+
+    def begin(self, entries):
+        """Takes the pages the entries need, lays the step's integer arrays out, lets the mixers plan, sends the
+        arrays and the changed block-table entries to the device.  -> StepContext ready for model.forward"""
+        cache = self.cache
         seen = set()
         need = [0] * len(cache.groups)
         for rid, tokens, want in entries:
@@ -97,14 +106,14 @@ class ModelRunner:
         self.model.prepare(ctx)
         inp.upload()
         cache.flush_tables()
+        return ctx
 
-        decode_only = self.use_graphs and N == S and len(want) == S
-        logits = self._run_graph(ctx) if decode_only else self.model.forward(ctx)
+    def commit(self, entries):
+        """The step's tokens are in the cache: the requests grow (and windows give pages back)."""
         for rid, tokens, _ in entries:
-            cache.commit(rid, len(tokens))
+            self.cache.commit(rid, len(tokens))
+            self.stats["tokens"] += len(tokens)
         self.stats["steps"] += 1
-        self.stats["tokens"] += N
-        return logits
 
     def _run_graph(self, ctx):
         sig = (self.inputs.signature(), getattr(self.ws, "generation", 0), getattr(self.inputs, "generation", 0))

@@ -14,6 +14,10 @@ from .build import load_library
 
 c_int, c_float, c_void_p = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
 
+# bf16 products accumulate in float32 all the way: no reduced-precision reduction inside the library
+torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+torch.backends.cuda.matmul.allow_tf32 = False
+
 DEVICE_ERRORS = {1: "a token id outside the vocabulary", 2: "a position whose cache page the block table does not hold",
                  3: "a page id outside the cache pool", 4: "a bounded wait inside a kernel ran out"}
 

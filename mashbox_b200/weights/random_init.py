@@ -18,8 +18,9 @@ def tensor_seed(seed, name):
     return (int(seed) * 1_000_003 + zlib.crc32(name.encode())) % (1 << 63)
 
 
-def random_tensors(shapes, seed, dtype=torch.float32, device="cpu", std=0.02, norm_std=0.01):
-    """shapes: {name: (shape, kind)} with kind "matrix" | "norm" | "bias" -> {name: tensor of dtype on device}."""
+def random_tensors(shapes, seed, dtype=torch.float32, device="cpu", std=0.02, norm_std=0.01, std_by_name=()):
+    """shapes: {name: (shape, kind)} with kind "matrix" | "norm" | "bias" -> {name: tensor of dtype on device}.
+    std_by_name: (substring, std) pairs; the first whose substring is in a matrix's or bias's name replaces std."""
     out = {}
     for name, (shape, kind) in shapes.items():
         g = torch.Generator(device=device)
@@ -28,12 +29,12 @@ def random_tensors(shapes, seed, dtype=torch.float32, device="cpu", std=0.02, no
         if kind == "norm":
             x = 1.0 + norm_std * x
         else:
-            x = std * x
+            x = next((s for sub, s in std_by_name if sub in name), std) * x
         out[name] = x.to(dtype)
     return out
 
 
-def write_model_folder(folder, config, seed, dtype=torch.float32, std=0.02, norm_std=0.01):
+def write_model_folder(folder, config, seed, dtype=torch.float32, std=0.02, norm_std=0.01, std_by_name=()):
     """Writes folder/config.json and folder/model.safetensors for `config` (an architecture's typed configuration)
     with seeded random weights stored as `dtype`.  -> folder"""
     from ..config.registry import architecture
@@ -41,6 +42,7 @@ def write_model_folder(folder, config, seed, dtype=torch.float32, std=0.02, norm
     os.makedirs(folder, exist_ok=True)
     with open(os.path.join(folder, "config.json"), "w") as fh:
         json.dump(config.to_hf(), fh, indent=1)
-    tensors = random_tensors(entry.stored_tensors(config), seed, dtype=dtype, std=std, norm_std=norm_std)
+    tensors = random_tensors(entry.stored_tensors(config), seed, dtype=dtype, std=std, norm_std=norm_std,
+                             std_by_name=std_by_name)
     write_safetensors(os.path.join(folder, "model.safetensors"), tensors)
     return folder

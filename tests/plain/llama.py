@@ -175,37 +175,54 @@ def linear(x, w, b=None):
     return y if b is None else y + b
 
 
-def block(x, W, l, c, freqs, positions):
+def _same(t):
+    return t
+
+
+def round_bf16(t):
+    """round to bfloat16 and widen again: what holding a tensor in bfloat16 does to its values"""
+    return t.to(torch.float32).to(torch.bfloat16).to(F64)
+
+
+def block(x, W, l, c, freqs, positions, held=_same):
     """One pre-norm residual block: x += attn(ln1(x)); x += ffn(ln2(x)).  src/mashbox/gguf/archs/dense.py:339-357.
-    W holds Hugging Face names; q/k rows are permuted here as the loader of the reference does."""
+    W holds Hugging Face names; q/k rows are permuted here as the loader of the reference does.  `held` is applied to
+    every tensor the reference holds in its activation dtype (dense.py:335-357: the results of rms, of every matmul,
+    of the rotation and of silu*up are cast to `act`; biases are added in float32 before the cast of q, k, v and
+    after it for the output); the identity gives the exact model, round_bf16 a model of bfloat16 storage."""
     p = f"model.layers.{l}."
     T = x.shape[0]
     H, KV, HD = c["H"], c["KV"], c["HD"]
     bias = lambda n: W.get(p + n)
-    h = rms_norm(x, W[p + "input_layernorm.weight"], c["eps"])
+    plus = lambda y, b: y if b is None else y + b
+    h = held(rms_norm(x, W[p + "input_layernorm.weight"], c["eps"]))
     wq, wk = permute_rows(W[p + "self_attn.q_proj.weight"], H), permute_rows(W[p + "self_attn.k_proj.weight"], KV)
     bq, bk = bias("self_attn.q_proj.bias"), bias("self_attn.k_proj.bias")
     bq = None if bq is None else permute_rows(bq, H)
     bk = None if bk is None else permute_rows(bk, KV)
-    q = linear(h, wq, bq).reshape(T, H, HD)
-    k = linear(h, wk, bk).reshape(T, KV, HD)
-    v = linear(h, W[p + "self_attn.v_proj.weight"], bias("self_attn.v_proj.bias")).reshape(T, KV, HD)
-    q, k = rope_adjacent(q, positions, freqs), rope_adjacent(k, positions, freqs)
-    o = attention(q, k, v, HD ** -0.5, window=c.get("window"), positions=positions)
-    x = x + linear(o, W[p + "self_attn.o_proj.weight"], bias("self_attn.o_proj.bias"))
-    h = rms_norm(x, W[p + "post_attention_layernorm.weight"], c["eps"])
-    return x + swiglu(h, W[p + "mlp.gate_proj.weight"], W[p + "mlp.up_proj.weight"], W[p + "mlp.down_proj.weight"])
+    q = plus(held(linear(h, wq)), bq).reshape(T, H, HD)
+    k = plus(held(linear(h, wk)), bk).reshape(T, KV, HD)
+    v = held(plus(held(linear(h, W[p + "self_attn.v_proj.weight"])), bias("self_attn.v_proj.bias"))).reshape(T, KV, HD)
+    q, k = held(rope_adjacent(q, positions, freqs)), held(rope_adjacent(k, positions, freqs))
+    o = held(attention(q, k, v, HD ** -0.5, window=c.get("window"), positions=positions))
+    x = x + plus(held(linear(o, W[p + "self_attn.o_proj.weight"])), bias("self_attn.o_proj.bias"))
+    h = held(rms_norm(x, W[p + "post_attention_layernorm.weight"], c["eps"]))
+    g = held(linear(h, W[p + "mlp.gate_proj.weight"]))
+    u = held(linear(h, W[p + "mlp.up_proj.weight"]))
+    a = held(g * torch.sigmoid(g) * u)                                  # dense.py:356
+    return x + held(linear(a, W[p + "mlp.down_proj.weight"]))
 
 
-def head(x, W, c):
+def head(x, W, c, held=_same):
     """logits = rms(x, norm) W_head^T; the head is the embedding when tied.  src/mashbox/gguf/archs/dense.py:386-390,
-    tie dense.py:129."""
+    tie dense.py:129.  The logits themselves stay unrounded (this engine keeps them in float32)."""
     w = W["model.embed_tokens.weight"] if c["tie"] or "lm_head.weight" not in W else W["lm_head.weight"]
-    return rms_norm(x, W["model.norm.weight"], c["eps"]) @ w.T
+    return held(rms_norm(x, W["model.norm.weight"], c["eps"])) @ w.T
 
 
-def forward(cfg, W, tokens):
-    """Logits (T, V) float64 at every position of one whole sequence.  src/mashbox/gguf/archs/dense.py:309-392."""
+def forward(cfg, W, tokens, held=_same):
+    """Logits (T, V) float64 at every position of one whole sequence.  src/mashbox/gguf/archs/dense.py:309-392.
+    held: see block()."""
     c = sizes(cfg)
     W = {k: v.to(F64) for k, v in W.items()}
     tokens = [int(t) for t in tokens]
@@ -213,8 +230,8 @@ def forward(cfg, W, tokens):
     freqs = rope_frequencies(c["theta"], c["HD"], c["scaling"])
     x = W["model.embed_tokens.weight"][torch.tensor(tokens)]           # dense.py:328
     for l in range(c["L"]):
-        x = block(x, W, l, c, freqs, positions)
-    return head(x, W, c)
+        x = block(x, W, l, c, freqs, positions, held)
+    return head(x, W, c, held)
 
 
 def greedy(cfg, W, prompt, n):

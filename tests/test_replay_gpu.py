@@ -6,16 +6,16 @@ import pytest
 import torch
 
 from tests import helpers as H
-from tests.tolerances import assert_logits
 
 pytestmark = pytest.mark.gpu
-CASES = [(n, d) for n in ("A", "B") for d in ("float32", "bfloat16")]
+CASES = [(n, m) for n in ("A", "B") for m in H.MODES]
 
 
-def runner_for(tmp, name, dtype, max_tokens, options=None):
+def runner_for(tmp, name, mode, max_tokens, options=None):
     from mashbox_b200.engine.replay import make_runner
+    dtype, opts = H.MODES[mode]
     folder = H.make_folder(tmp, name, H.store_for(dtype))
-    return folder, make_runner(folder, dtype, max_tokens, page_size=H.TINY[name][2], options=options)
+    return folder, make_runner(folder, dtype, max_tokens, page_size=H.TINY[name][2], options=dict(opts, **(options or {})))
 
 
 def replay(runner, steps):
@@ -29,20 +29,20 @@ def replay(runner, steps):
     return out
 
 
-@pytest.mark.parametrize("name,dtype", CASES)
-def test_whole_prompts(tmp_path_factory, name, dtype):
+@pytest.mark.parametrize("name,mode", CASES)
+def test_whole_prompts(tmp_path_factory, name, mode):
     tmp = tmp_path_factory.mktemp("m")
-    folder, runner = runner_for(tmp, name, dtype, 256)
+    folder, runner = runner_for(tmp, name, mode, 256)
     for p in H.prompts_for(name, (7, 13, 70, 130)):
         got = replay(runner, [dict(entries=[dict(id="a", tokens=p, want=list(range(len(p))))], end=["a"])])[0]
-        assert_logits(got, H.plain_logits(folder, p), dtype, f"whole prompt of {len(p)}")
+        H.check(got, folder, p, mode, f"whole prompt of {len(p)}")
     runner.cache.check()
 
 
-@pytest.mark.parametrize("name,dtype", CASES)
-def test_last_32_one_by_one(tmp_path_factory, name, dtype):
+@pytest.mark.parametrize("name,mode", CASES)
+def test_last_32_one_by_one(tmp_path_factory, name, mode):
     tmp = tmp_path_factory.mktemp("m")
-    folder, runner = runner_for(tmp, name, dtype, 192)
+    folder, runner = runner_for(tmp, name, mode, 192)
     for p in H.prompts_for(name, (40, 150), seed=1):
         cut = len(p) - 32
         steps = [dict(entries=[dict(id="a", tokens=p[:cut], want=[cut - 1])], end=[])]
@@ -50,15 +50,14 @@ def test_last_32_one_by_one(tmp_path_factory, name, dtype):
                   for i in range(cut, len(p))]
         out = replay(runner, steps)
         got = np.concatenate([out[i] for i in range(len(steps))])
-        want = H.plain_logits(folder, p)[cut - 1:]
-        assert_logits(got, want, dtype, f"prompt of {len(p)}, last 32 decoded")
+        H.check(got, folder, p, mode, f"prompt of {len(p)}, last 32 decoded", slice(cut - 1, None))
     runner.cache.check()
 
 
-@pytest.mark.parametrize("name,dtype", CASES)
-def test_portions_of_changing_size(tmp_path_factory, name, dtype):
+@pytest.mark.parametrize("name,mode", CASES)
+def test_portions_of_changing_size(tmp_path_factory, name, mode):
     tmp = tmp_path_factory.mktemp("m")
-    folder, runner = runner_for(tmp, name, dtype, 192)
+    folder, runner = runner_for(tmp, name, mode, 192)
     p = H.prompts_for(name, (171,), seed=2)[0]
     sizes, at, steps = [2, 17, 3, 64, 2, 31, 16, 8, 5, 2, 21], 0, []
     for s in sizes:
@@ -70,7 +69,7 @@ def test_portions_of_changing_size(tmp_path_factory, name, dtype):
     assert at == len(p)
     out = replay(runner, steps)
     got = np.concatenate([out[i] for i in range(len(steps))])
-    assert_logits(got, H.plain_logits(folder, p), dtype, "portions")
+    H.check(got, folder, p, mode, "portions")
 
 
 def mixed_trace(prompts, rng, max_live=4):
@@ -101,16 +100,16 @@ def mixed_trace(prompts, rng, max_live=4):
     return steps, where
 
 
-@pytest.mark.parametrize("name,dtype", CASES)
-def test_mixed_batches_with_page_reuse(tmp_path_factory, name, dtype):
+@pytest.mark.parametrize("name,mode", CASES)
+def test_mixed_batches_with_page_reuse(tmp_path_factory, name, mode):
     tmp = tmp_path_factory.mktemp("m")
     lengths = (50, 33, 64, 20, 61, 47, 9, 58)
     prompts = H.prompts_for(name, lengths, seed=3)
-    folder, runner = runner_for(tmp, name, dtype, 4 * 64)         # four live requests of at most 64 tokens
+    folder, runner = runner_for(tmp, name, mode, 4 * 64)         # four live requests of at most 64 tokens
     steps, where = mixed_trace(prompts, np.random.default_rng(5))
     out = replay(runner, steps)
     for i, p in enumerate(prompts):
         got = np.concatenate([out[s][o:o + n] for s, o, n in where[i]])
-        assert_logits(got, H.plain_logits(folder, p), dtype, f"mixed, request {i}")
+        H.check(got, folder, p, mode, f"mixed, request {i}")
     runner.cache.check()
     assert all(f == runner.cache.num_pages for f in runner.cache.free_pages())
