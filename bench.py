@@ -1,0 +1,273 @@
+"""Benchmark of the engine on one B200: decode tokens per second of a Llama-3.1-8B-shaped model with random bf16
+weights at batch 8 and 8,192 tokens of context per request, with the 2,048-token prefill, the decode roofline and
+decode at batch 1 and 64 on the same JSON line.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--batch B] [--context C] [--no-points]
+    python bench.py --impl reference        # the reference arm (unavailable here: it needs JAX and a TPU)
+
+A "step" is one decode step of the whole batch.  `value` is timed on the device with CUDA events around K calls of the
+engine's step function (inputs sent from pinned host memory each step, no read-back); `e2e` is the same through the
+public entry point (Engine.admit / Engine.step: host token ids in, sampled token ids read back every step).  A decode
+step reads more than 16 GB, far over the 126 MB L2, so no flush is needed between steps.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.isfile(p):
+        try:
+            d = json.load(open(p))
+            return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+def baseline_config():
+    """Sizes of BASELINE.json's configs[2] (the Llama-3.1-8B shape), as a typed configuration."""
+    from mashbox_b200.config.llama import LlamaConfig, RopeScaling
+    return LlamaConfig(architecture="LlamaForCausalLM", num_layers=32, hidden=4096, num_heads=32, num_kv_heads=8,
+                       head_dim=128, intermediate=14336, vocab=128256, rms_eps=1e-5, rope_theta=500000.0,
+                       rope_scaling=RopeScaling("llama3", 8.0, 1.0, 4.0, 8192), tie_embeddings=False,
+                       attention_bias=False, max_position=131072)
+
+
+class Clocks:
+    """Samples nvidia-smi every 200 ms while the timed regions run."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.path = tempfile.mktemp(suffix=".csv")
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        self.proc.wait()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in open(self.path):
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        os.remove(self.path)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        busy = [x for x in sm if x > 0.5 * max(sm)] or sm
+        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(mx), "reasons": sorted(reasons)}
+
+
+def flops_prefill(c, layers, n_tokens):
+    H, KV, HD, D, F, V = c.num_heads, c.num_kv_heads, c.head_dim, c.hidden, c.intermediate, c.vocab
+    per_layer = 2 * n_tokens * (D * (H + 2 * KV) * HD + H * HD * D + 3 * D * F)
+    attn = 4 * (n_tokens * (n_tokens + 1) // 2) * HD * H
+    return layers * (per_layer + attn) + 2 * D * V
+
+
+def bytes_decode(c, layers, batch, kv_len):
+    H, KV, HD, D, F, V = c.num_heads, c.num_kv_heads, c.head_dim, c.hidden, c.intermediate, c.vocab
+    weights = layers * 2 * (D * (H + 2 * KV) * HD + H * HD * D + 3 * D * F) + 2 * D * V
+    cache = layers * batch * kv_len * 2 * KV * HD * 2
+    return weights + cache
+
+
+def run_ours(a):
+    import torch
+    from mashbox_b200 import ops
+    from mashbox_b200.config.registry import architecture
+    from mashbox_b200.engine.engine import Engine
+    from mashbox_b200.weights.random_init import RandomSource
+
+    torch.cuda.set_device(0)
+    dev = "cuda:0"
+    c = baseline_config()
+    layers = a.layers or c.num_layers
+    import dataclasses
+    cfg = dataclasses.replace(c, num_layers=layers)
+    K, W, ctx = a.steps, a.warmup, a.context
+    batches = [a.batch] + ([] if a.no_points else [b for b in (1, 64) if b != a.batch])
+    max_b = max(batches)
+    per_request = -(-(ctx + 16) // 64) * 64
+    pool_tokens = max_b * per_request + 4096
+    shapes = architecture(cfg.architecture).stored_tensors(cfg)
+    t0 = time.time()
+    eng = Engine.from_config(cfg, RandomSource(shapes, 0, torch.bfloat16, dev), dtype="bfloat16", device=dev,
+                             page_size=16, max_tokens=pool_tokens, max_requests=max_b, max_tokens_per_step=2048 + max_b,
+                             chunk=2048, max_context=per_request)
+    torch.cuda.synchronize()
+    load_s = time.time() - t0
+    gen = torch.Generator().manual_seed(1)
+    rand_ids = lambda n: torch.randint(0, cfg.vocab, (n,), generator=gen).tolist()
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    clocks = Clocks()
+    clocks.start()
+
+    # ---- prefill of 2,048 tokens: one step of one fresh request (its first token is sampled in the same step)
+    P = a.prefill_tokens
+    pre_ms = []
+    for i in range(2 + 3):
+        rows = eng.admit([dict(ids=rand_ids(P), max_new=1)])
+        torch.cuda.synchronize()
+        e0, e1 = ev(), ev()
+        e0.record()
+        eng.step()
+        e1.record()
+        torch.cuda.synchronize()
+        assert rows[0].finish == "length", rows[0].finish
+        if i >= 2:
+            pre_ms.append(e0.elapsed_time(e1))
+    pre = statistics.median(pre_ms)
+    pk = peaks()
+    prefill = {"value": P / (pre / 1e3), "tokens": P, "ms": pre,
+               "frac": flops_prefill(cfg, layers, P) / (pre / 1e3) / (pk["bf16_tflops"] * 1e12)}
+
+    # ---- decode
+    def decode(batch, with_e2e):
+        plen = ctx - 2 * (K + W) - 2
+        rows = eng.admit([dict(ids=rand_ids(plen), max_new=2 * (K + W) + 8) for _ in range(batch)])
+        while any(r.t_first is None for r in rows):
+            eng.step()
+        res = {}
+        if with_e2e:
+            for _ in range(W):
+                eng.step()
+            torch.cuda.synchronize()
+            l0 = ops.COUNTERS["launches"]
+            e0, e1 = ev(), ev()
+            e0.record()
+            t0 = time.perf_counter()
+            for _ in range(K):
+                eng.step()
+            e1.record()
+            torch.cuda.synchronize()
+            wall = time.perf_counter() - t0
+            ms = max(e0.elapsed_time(e1), wall * 1e3)
+            res["e2e"] = {"value": batch * K / (ms / 1e3), "unit": "tokens/s",
+                          "h2d_bytes_per_step": eng.runner.inputs.used * 4, "d2h_bytes_per_step": batch * 4 + 4,
+                          "ms_per_step": ms / K}
+            res["e2e_launches"] = ops.COUNTERS["launches"] - l0
+        # the step function alone: fixed next tokens, no read-back inside the timed region
+        runner = eng.runner
+        live = [r for r in rows if r.finish is None]
+        toks = rand_ids(len(live))
+        entries = lambda: [(r.rid, [t], [0]) for r, t in zip(live, toks)]
+        for _ in range(W):
+            runner.step(entries())
+        torch.cuda.synchronize()
+        l0 = ops.COUNTERS["launches"]
+        e0, e1 = ev(), ev()
+        e0.record()
+        for _ in range(K):
+            runner.step(entries())
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1)
+        runner.check()
+        kv_len = runner.cache.get(live[0].rid).length
+        res.update(value=len(live) * K / (ms / 1e3), ms_per_step=ms / K, launches=ops.COUNTERS["launches"] - l0,
+                   kv_len=kv_len, batch=len(live))
+        eng.cancel(rows)
+        return res
+
+    main = decode(a.batch, True)
+    points = {}
+    for b in batches[1:]:
+        points[f"decode_b{b}"] = decode(b, False)["value"]
+    points[f"decode_b{a.batch}"] = main["value"]
+    clk = clocks.stop()
+    nbytes = bytes_decode(cfg, layers, main["batch"], main["kv_len"])
+    achieved = nbytes / (main["ms_per_step"] / 1e3) / 1e9
+    line = {
+        "metric": "decode tokens/s, Llama-3.1-8B shape, random bf16 weights", "value": main["value"], "unit": "tokens/s",
+        "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": main["ms_per_step"], "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: seeded random weights made on the GPU, uniform random token ids",
+        "config": {"model": "llama-3.1-8b-shape", "layers": layers, "layers_of_config": c.num_layers,
+                   "hidden": cfg.hidden, "heads": cfg.num_heads, "kv_heads": cfg.num_kv_heads,
+                   "head_dim": cfg.head_dim, "intermediate": cfg.intermediate, "vocab": cfg.vocab,
+                   "global_batch": main["batch"], "seq_len": ctx, "kv_len_at_end": main["kv_len"], "page_size": 16,
+                   "prefill_tokens": P, "parallelism": "single-gpu", "l2": "inputs larger than L2 (no flush)",
+                   "cuda_graphs": bool(eng.runner.use_graphs), "peaks": pk["source"], "load_s": round(load_s, 1)},
+        "clocks": clk,
+        "e2e": {k: main["e2e"][k] for k in ("value", "unit", "h2d_bytes_per_step", "d2h_bytes_per_step")},
+        "gpu_launches": main["launches"],
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / pk["hbm_gbs"]},
+        "points": points,
+        "impl": "ours",
+    }
+    print(json.dumps(line))
+    return 0
+
+
+def run_reference(a):
+    """The reference arm: mashbox's own engine from baseline/_ref.  mashbox 0.1.15 installs there with --no-deps, but
+    its model and engine modules import JAX (not in this image, no network) and it runs on TPU chips."""
+    sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
+    try:
+        import mashbox.runtime.engine  # noqa: F401
+        import mashbox.gguf.archs.dense  # noqa: F401
+    except Exception as e:
+        print(json.dumps({"impl": "reference", "unavailable": f"mashbox's engine cannot be imported here: "
+                          f"{type(e).__name__}: {e} (it is a JAX/TPU program; JAX is not installed and there is no network)"}))
+        return 0
+    print(json.dumps({"impl": "reference", "unavailable": "mashbox imports, but its engine targets TPU chips through JAX "
+                      "and has no CUDA path for this metric"}))
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=32)
+    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (0 = all of them)")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=8192)
+    ap.add_argument("--prefill-tokens", type=int, default=2048)
+    ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
+    a = ap.parse_args()
+    if a.impl == "reference":
+        return run_reference(a)
+    if a.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
+        if int(os.environ.get("RANK", "0")) == 0:
+            print(f"bench.py: this engine runs on ONE GPU; --gpus {a.gpus} is not measured")
+        return 2
+    a.warmup = max(a.warmup, 3)
+    return run_ours(a)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -37,6 +37,16 @@ class Engine:
         model = load_model(folder, dtype=cfg.dtype, device=device, log=log)
         return cls(model, cfg, options, log)
 
+    @classmethod
+    def from_config(cls, config, source, dtype="bfloat16", device="cuda:0", options=None, log=None, **engine_options):
+        """config: an architecture's typed configuration; source: a TensorSource with its tensors (for instance
+        weights.random_init.RandomSource)."""
+        from .. import ops
+        from .loading import build_model
+        cfg = EngineConfig(dtype=dtype, device=device, **engine_options)
+        model = build_model(config.to_hf(), source, cfg.dtype, device, ops=ops, log=log)
+        return cls(model, cfg, options, log)
+
     # -------------------------------------------------------------------------------------------- low level
     def check(self, q):
         """None when request q = dict(ids, max_new, samp=None) fits, else the reason."""

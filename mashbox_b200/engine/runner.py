@@ -121,6 +121,7 @@ class ModelRunner:
         if g is not None:
             g[0].replay()
             self.stats["graph_replays"] += 1
+            kernels.COUNTERS["launches"] += g[2]
             return g[1]
         count = self.seen_signatures.get(sig, 0)
         self.seen_signatures[sig] = count + 1
@@ -128,10 +129,12 @@ class ModelRunner:
             return self.model.forward(ctx)
         torch.cuda.synchronize(self.device)
         graph = torch.cuda.CUDAGraph()
+        before = kernels.COUNTERS["launches"]
         with torch.cuda.graph(graph):
             logits = self.model.forward(ctx)
+        captured = kernels.COUNTERS["launches"] - before
         graph.replay()
-        self.graphs[sig] = (graph, logits)
+        self.graphs[sig] = (graph, logits, captured)
         self.stats["graph_captures"] += 1
         return logits
 

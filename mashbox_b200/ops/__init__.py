@@ -44,8 +44,12 @@ def _cuda(*tensors):
             raise KernelError("mashbox_b200 kernels run on CUDA tensors only; there is no CPU fallback")
 
 
+COUNTERS = {"launches": 0}      # launches of this package's own kernels (a graph replay adds what it captured)
+
+
 def _check(code, what):
     if code == 0:
+        COUNTERS["launches"] += 1
         return
     if code == -2:
         raise KernelError(f"{what}: the kernel does not take these sizes")

@@ -11,7 +11,7 @@ import zlib
 
 import torch
 
-from .safetensors_io import write_safetensors
+from .safetensors_io import TensorSource, write_safetensors
 
 
 def tensor_seed(seed, name):
@@ -32,6 +32,25 @@ def random_tensors(shapes, seed, dtype=torch.float32, device="cpu", std=0.02, no
             x = next((s for sub, s in std_by_name if sub in name), std) * x
         out[name] = x.to(dtype)
     return out
+
+
+class RandomSource(TensorSource):
+    """Seeded random tensors made when asked for, on `device` (a benchmark of a large shape makes its weights on the
+    GPU and never writes them to disk).  Values depend on the device kind: a CUDA generator and a CPU generator give
+    different numbers for one seed."""
+
+    def __init__(self, shapes, seed, dtype=torch.bfloat16, device="cpu", std=0.02, norm_std=0.01, std_by_name=()):
+        self.shapes, self.seed, self.dtype, self.device = dict(shapes), seed, dtype, device
+        self.kw = dict(std=std, norm_std=norm_std, std_by_name=std_by_name)
+
+    def names(self):
+        return list(self.shapes)
+
+    def info(self, name):
+        return self.dtype, tuple(self.shapes[name][0])
+
+    def get(self, name):
+        return random_tensors({name: self.shapes[name]}, self.seed, self.dtype, self.device, **self.kw)[name]
 
 
 def write_model_folder(folder, config, seed, dtype=torch.float32, std=0.02, norm_std=0.01, std_by_name=()):
