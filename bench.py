@@ -117,7 +117,7 @@ def run_ours(a):
     K, W, ctx = a.steps, a.warmup, a.context
     batches = [a.batch] + ([] if a.no_points else [b for b in (1, 64) if b != a.batch])
     max_b = max(batches)
-    per_request = -(-(ctx + 16) // 64) * 64
+    per_request = -(-(ctx + 1024) // 64) * 64
     pool_tokens = max_b * per_request + 4096
     shapes = architecture(cfg.architecture).stored_tensors(cfg)
     t0 = time.time()
@@ -153,8 +153,11 @@ def run_ours(a):
 
     # ---- decode
     def decode(batch, with_e2e):
-        plen = ctx - 2 * (K + W) - 2
-        rows = eng.admit([dict(ids=rand_ids(plen), max_new=2 * (K + W) + 8) for _ in range(batch)])
+        # requests finish their prompts one after the other and decode while the others still prefill: the prompt is
+        # shortened by the mean of that head start, so that the mean context in the timed steps is about `ctx`
+        chunks = -(-ctx // 2048)
+        plen = ctx - 2 * (K + W) - (batch - 1) * chunks // 2 - 2
+        rows = eng.admit([dict(ids=rand_ids(plen), max_new=2 * (K + W) + batch * chunks + 16) for _ in range(batch)])
         while any(r.t_first is None for r in rows):
             eng.step()
         res = {}
@@ -193,9 +196,9 @@ def run_ours(a):
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1)
         runner.check()
-        kv_len = runner.cache.get(live[0].rid).length
+        lens = [runner.cache.get(r.rid).length for r in live]
         res.update(value=len(live) * K / (ms / 1e3), ms_per_step=ms / K, launches=ops.COUNTERS["launches"] - l0,
-                   kv_len=kv_len, batch=len(live))
+                   kv_len=sum(lens) / len(lens) - K / 2, batch=len(live))
         eng.cancel(rows)
         return res
 
@@ -215,7 +218,8 @@ def run_ours(a):
         "config": {"model": "llama-3.1-8b-shape", "layers": layers, "layers_of_config": c.num_layers,
                    "hidden": cfg.hidden, "heads": cfg.num_heads, "kv_heads": cfg.num_kv_heads,
                    "head_dim": cfg.head_dim, "intermediate": cfg.intermediate, "vocab": cfg.vocab,
-                   "global_batch": main["batch"], "seq_len": ctx, "kv_len_at_end": main["kv_len"], "page_size": 16,
+                   "global_batch": main["batch"], "seq_len": ctx, "mean_kv_len_timed": round(main["kv_len"], 1),
+                   "page_size": 16,
                    "prefill_tokens": P, "parallelism": "single-gpu", "l2": "inputs larger than L2 (no flush)",
                    "cuda_graphs": bool(eng.runner.use_graphs), "peaks": pk["source"], "load_s": round(load_s, 1)},
         "clocks": clk,

@@ -47,7 +47,7 @@ def build_dir():
     d = os.path.join(CSRC, "_build")
     try:
         os.makedirs(d, exist_ok=True)
-        probe = os.path.join(d, f".w{os.getpid()}")
+        probe = os.path.join(d, f".w{os.getpid()}.{threading.get_ident()}")
         open(probe, "w").close()
         os.remove(probe)
         return d

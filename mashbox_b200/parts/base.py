@@ -127,10 +127,15 @@ class StepInputs:
     a 16-byte boundary.  The device buffer is the same from step to step, so a captured graph finds its inputs at the
     same addresses as long as the arrays have the same lengths (the signature)."""
 
-    def __init__(self, device, capacity=1 << 20):
+    STAGES = 4
+
+    def __init__(self, device, capacity=1 << 18):
         import torch
         self.device = device
-        self.host = torch.empty(capacity, dtype=torch.int32).pin_memory() if device is not None else None
+        self.hosts = [torch.empty(capacity, dtype=torch.int32).pin_memory() for _ in range(self.STAGES)] \
+            if device is not None else None
+        self.events = [None] * self.STAGES
+        self.turn = 0
         self.dev = torch.empty(capacity, dtype=torch.int32, device=device) if device is not None else None
         self.reset()
 
@@ -151,17 +156,29 @@ class StepInputs:
         return tuple((n, len(a)) for n, a in self.arrays.items())
 
     def upload(self):
+        """Copies the arrays to the device buffer through one of several pinned staging buffers: a staging buffer is
+        written again only after the copy that read it has run, so steps may be queued without waiting for the GPU."""
         import torch
-        if self.used > self.host.numel():
-            cap = max(self.used, 2 * self.host.numel())
-            self.host = torch.empty(cap, dtype=torch.int32).pin_memory()
+        if self.used > self.dev.numel():
+            cap = max(self.used, 2 * self.dev.numel())
+            torch.cuda.synchronize(self.device)
+            self.hosts = [torch.empty(cap, dtype=torch.int32).pin_memory() for _ in range(self.STAGES)]
+            self.events = [None] * self.STAGES
             self.dev = torch.empty(cap, dtype=torch.int32, device=self.device)
             self.generation = getattr(self, "generation", 0) + 1
-        hn = self.host.numpy()
+        slot = self.turn % self.STAGES
+        self.turn += 1
+        if self.events[slot] is not None:
+            self.events[slot].synchronize()
+        host = self.hosts[slot]
+        hn = host.numpy()
         for n, a in self.arrays.items():
             o = self.offsets[n]
             hn[o:o + len(a)] = a
-        self.dev[:self.used].copy_(self.host[:self.used], non_blocking=True)
+        self.dev[:self.used].copy_(host[:self.used], non_blocking=True)
+        ev = self.events[slot] or torch.cuda.Event()
+        ev.record()
+        self.events[slot] = ev
         self.views = {n: self.dev[o:o + len(self.arrays[n])] for n, o in self.offsets.items()}
 
     def get(self, name):
