@@ -1,0 +1,371 @@
+"""-m gpu: every kernel alone against its plain reference, at other sizes than the engine's tiny models: widths and
+vocabularies that are no power of two, head sizes in steps of 16, odd head and group counts, several page sizes.  Where
+random inputs would hide a fault the inputs are built so that it shows: one far key that takes all the weight, keys on
+both sides of a window's edge, pages in shuffled order, pool slots past a sequence's end poisoned."""
+import numpy as np
+import pytest
+import torch
+
+from tests import gpu_harness as G
+from tests.plain import llama as plain
+from tests.plain import sampling as psamp
+from tests.tolerances import KERNEL_BF16, KERNEL_F32
+
+pytestmark = pytest.mark.gpu
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def ops():
+    import mashbox_b200.ops as K
+    return K
+
+
+def close(got, want, dtype, what=""):
+    got, want = got.detach().double().cpu(), want.detach().double().cpu()
+    assert torch.isfinite(got).all(), f"{what}: non-finite values"
+    tol = (KERNEL_F32 if dtype == torch.float32 else KERNEL_BF16) * float(want.abs().max())
+    err = float((got - want).abs().max())
+    assert err <= tol, f"{what}: max error {err:.3e}, bar {tol:.3e}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embed(dtype):
+    K = ops()
+    g = torch.Generator().manual_seed(0)
+    V, D, N = 1003, 72, 37
+    table = torch.randn(V, D, generator=g).to(G.DEV, dtype)
+    tok = torch.randint(0, V, (N,), generator=g).int().to(G.DEV)
+    x = torch.empty(N, D, device=G.DEV)
+    err = K.new_error_word(G.DEV)
+    K.embed(tok, table, x, err)
+    assert torch.equal(x, table.float()[tok.long()])
+    K.check_error_word(err)
+    tok[5] = V
+    K.embed(tok, table, x, err)
+    with pytest.raises(Exception, match="token id outside"):
+        K.check_error_word(err)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("D", [200, 4096 + 8])
+def test_add_rmsnorm(dtype, D):
+    K = ops()
+    g = torch.Generator().manual_seed(1)
+    N, eps = 19, 3e-4
+    x0 = torch.randn(N, D, generator=g)
+    delta = torch.randn(N, D, generator=g).to(dtype)
+    bias, w = torch.randn(D, generator=g), 1 + 0.3 * torch.randn(D, generator=g)
+    # no delta
+    x = x0.clone().to(G.DEV)
+    out = torch.empty(N, D, device=G.DEV, dtype=dtype)
+    K.add_rmsnorm(x, None, None, w.to(G.DEV), eps, out)
+    close(out, plain.rms_norm(x0.double(), w.double(), eps), dtype, "norm")
+    assert torch.equal(x.cpu(), x0)
+    # delta + bias, in place
+    K.add_rmsnorm(x, delta.to(G.DEV), bias.to(G.DEV), w.to(G.DEV), eps, out)
+    v = x0.double() + delta.double() + bias.double()
+    close(x, v, torch.float32, "residual sum")
+    close(out, plain.rms_norm(v, w.double(), eps), dtype, "add + norm")
+    # picked rows: the stream is not written
+    x = x0.clone().to(G.DEV)
+    rows = torch.tensor([7, 0, 18, 7], dtype=torch.int32, device=G.DEV)
+    out4 = torch.empty(4, D, device=G.DEV, dtype=dtype)
+    K.add_rmsnorm(x, delta.to(G.DEV), None, w.to(G.DEV), eps, out4, rows)
+    v = (x0.double() + delta.double())[rows.long().cpu()]
+    close(out4, plain.rms_norm(v, w.double(), eps), dtype, "rows")
+    assert torch.equal(x.cpu(), x0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_swiglu(dtype):
+    K = ops()
+    g = torch.Generator().manual_seed(2)
+    N, F = 13, 333
+    gu = (2 * torch.randn(N, 2 * F, generator=g)).to(dtype)
+    out = torch.empty(N, F, device=G.DEV, dtype=dtype)
+    K.swiglu(gu.to(G.DEV), out)
+    a, b = gu[:, :F].double(), gu[:, F:].double()
+    close(out, a * torch.sigmoid(a) * b, dtype, "swiglu")
+
+
+def test_gemm_f32_is_exact_enough_and_does_not_depend_on_the_batch():
+    K = ops()
+    g = torch.Generator().manual_seed(3)
+    N, M, Kd = 70, 130, 77
+    a, w = torch.randn(N, Kd, generator=g), torch.randn(M, Kd, generator=g)
+    c = K.linear(a.to(G.DEV), w.to(G.DEV))
+    close(c, a.double() @ w.double().T, torch.float32, "gemm")
+    # the same row alone, in a batch of 3 and in the batch of 70: bit for bit the same
+    one = K.linear(a[41:42].to(G.DEV), w.to(G.DEV))
+    three = K.linear(a[40:43].to(G.DEV), w.to(G.DEV))
+    assert torch.equal(one[0], c[41]) and torch.equal(three[1], c[41])
+    # and it is float32 arithmetic, not TF32: a product that TF32 would round away
+    a2 = torch.tensor([[1.0, 2.0 ** -12]]), torch.tensor([[1.0, 1.0]])
+    assert float(K.linear(a2[0].to(G.DEV), a2[1].to(G.DEV))[0, 0]) == 1.0 + 2.0 ** -12
+
+
+def test_bf16_product_accumulates_in_float32():
+    K = ops()
+    g = torch.Generator().manual_seed(4)
+    a, w = torch.randn(5, 2048, generator=g).bfloat16(), torch.randn(300, 2048, generator=g).bfloat16()
+    c = K.linear(a.to(G.DEV), w.to(G.DEV), out_dtype=torch.float32)
+    assert c.dtype == torch.float32
+    close(c, a.double() @ w.double().T, torch.float32, "bf16 product, float32 out")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("pairing,HD,RD", [("adjacent", 48, 48), ("adjacent", 32, 16), ("halves", 64, 64), ("halves", 80, 32)])
+def test_rope_and_cache_write(dtype, pairing, HD, RD):
+    K = ops()
+    g = torch.Generator().manual_seed(5)
+    H, KV, page = 5, 1 if HD == 48 else 3, 8
+    seqs = G.PagedSequences([21, 9, 130], [21, 2, 5], H, KV, HD, page, dtype, seed=6).build()
+    N = seqs.N
+    qkv = torch.randn(N, (H + 2 * KV) * HD, generator=g).to(dtype)
+    bias = 0.5 * torch.randn((H + 2 * KV) * HD, generator=g)
+    freqs = plain.rope_frequencies(500000.0, RD, dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0,
+                                                       high_freq_factor=4.0, original_max_position_embeddings=64))
+    kpool, vpool = torch.zeros_like(seqs.kpool), torch.zeros_like(seqs.vpool)
+    dev = qkv.to(G.DEV).clone()
+    err = K.new_error_word(G.DEV)
+    K.rope_kv_write(dev, bias.to(G.DEV), seqs.positions, seqs.tok_row, seqs.table, kpool, vpool,
+                    torch.from_numpy(freqs).to(G.DEV), H, KV, HD, RD, 0 if pairing == "adjacent" else 1, page,
+                    seqs.num_pages, err)
+    K.check_error_word(err)
+    pos = seqs.positions.cpu().numpy()
+    full = qkv.double() + bias.double()
+    rope = plain.rope_adjacent if pairing == "adjacent" else plain.rope_halves
+    q = rope(full[:, :H * HD].reshape(N, H, HD), pos, freqs)
+    k = rope(full[:, H * HD:(H + KV) * HD].reshape(N, KV, HD), pos, freqs)
+    v = full[:, (H + KV) * HD:].reshape(N, KV, HD)
+    close(dev[:, :H * HD], q.reshape(N, -1), dtype, "rotated q")
+    table = seqs.table.cpu().numpy()
+    rows = seqs.tok_row.cpu().numpy()
+    got_k = torch.stack([kpool[table[r, p // page], :, p % page] for r, p in zip(rows, pos)])
+    got_v = torch.stack([vpool[table[r, p // page], :, p % page] for r, p in zip(rows, pos)])
+    close(got_k, k, dtype, "k in its pages")
+    close(got_v, v, dtype, "v in its pages")
+    # nothing else in the pools was touched
+    touched = torch.zeros(seqs.num_pages, page, dtype=torch.bool)
+    for r, p in zip(rows, pos):
+        touched[table[r, p // page], p % page] = True
+    assert float(kpool.float().abs().sum(dim=(1, 3)).cpu()[~touched].sum()) == 0.0
+    # q only (a layer that reads another layer's cache)
+    dev2 = qkv.to(G.DEV).clone()
+    K.rope_kv_write(dev2, bias.to(G.DEV), seqs.positions, seqs.tok_row, seqs.table, None, None,
+                    torch.from_numpy(freqs).to(G.DEV), H, KV, HD, RD, 0 if pairing == "adjacent" else 1, page,
+                    seqs.num_pages, err)
+    assert torch.equal(dev2[:, :H * HD], dev[:, :H * HD])
+    # a position without a page is reported, not written
+    bad = seqs.table.clone()
+    bad[seqs.rows[1]] = -1
+    K.rope_kv_write(qkv.to(G.DEV).clone(), None, seqs.positions, seqs.tok_row, bad, kpool, vpool, None, H, KV, HD, RD,
+                    0, page, seqs.num_pages, err)
+    with pytest.raises(Exception, match="block table does not hold"):
+        K.check_error_word(err)
+
+
+def dominant_key(seqs, s, key, head_group=None, gain=40.0):
+    """makes key `key` of sequence s take all the weight for that sequence's last query: q_last and k[key] are aligned
+    and long, so exp(score) dwarfs every other key"""
+    HD = seqs.HD
+    d = torch.ones(HD) / HD ** 0.5
+    seqs.q[s][-1] = gain * d
+    seqs.k[s][key] = gain * d
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("HD,H,KV,page,window", [(48, 6, 2, 8, None), (16, 3, 3, 4, 37), (64, 8, 1, 16, None),
+                                                 (256, 2, 1, 16, 100)])
+def test_attention_plain_kernel(dtype, HD, H, KV, page, window):
+    K = ops()
+    lengths, q_lens = [300, 45, 1, 77], [1, 45, 1, 13]
+    seqs = G.PagedSequences(lengths, q_lens, H, KV, HD, page, dtype, seed=7, rows=[2, 0, 5, 3])
+    dominant_key(seqs, 0, 3 if window is None else 300 - window)      # far away / the window's first key
+    seqs.round().build()
+    out = torch.empty(seqs.N, H * HD, device=G.DEV, dtype=dtype)
+    err = K.new_error_word(G.DEV)
+    scale = HD ** -0.5
+    K.attention_simple(seqs.q_dev, H * HD, out, seqs.positions, seqs.tok_row, seqs.table, seqs.kpool, seqs.vpool, H, KV,
+                       HD, page, seqs.num_pages, window, scale, err)
+    K.check_error_word(err)
+    close(out, seqs.reference(scale, window), dtype, "plain paged attention")
+    far = 3 if window is None else 300 - window
+    want = seqs.v[0][far].repeat_interleave(H // KV, 0).reshape(-1).double()
+    assert float((out[0].double().cpu() - want).abs().max()) < 0.05 * float(want.abs().max()) + 1e-3
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_plain_kernel_window_edge(dtype):
+    """the key just outside the window must not count, however large its score"""
+    K = ops()
+    H, KV, HD, page, window = 4, 2, 32, 8, 20
+    seqs = G.PagedSequences([90], [1], H, KV, HD, page, dtype, seed=8)
+    dominant_key(seqs, 0, 90 - window - 1)                            # one position too old
+    seqs.round().build()
+    out = torch.empty(1, H * HD, device=G.DEV, dtype=dtype)
+    err = K.new_error_word(G.DEV)
+    K.attention_simple(seqs.q_dev, H * HD, out, seqs.positions, seqs.tok_row, seqs.table, seqs.kpool, seqs.vpool, H, KV,
+                       HD, page, seqs.num_pages, window, HD ** -0.5, err)
+    close(out, seqs.reference(HD ** -0.5, window), dtype, "window edge")
+
+
+MMA_CASES = [  # HD, H, KV, page, window, splits
+    (128, 8, 2, 16, None, 1), (128, 8, 2, 16, None, 4), (64, 6, 2, 8, None, 3), (32, 6, 1, 8, 50, 2),
+    (16, 4, 2, 4, None, 1), (128, 32, 8, 32, 700, 8), (64, 5, 5, 16, None, 2), (128, 16, 1, 16, None, 2)]
+
+
+def run_mma(seqs, window, splits):
+    K = ops()
+    H, KV, HD, page = seqs.H, seqs.KV, seqs.HD, seqs.page
+    Gq = H // KV
+    dec, pre, part_base, part_tok = G.mma_items(seqs, Gq, splits)
+    out = torch.full((seqs.N, H * HD), float("nan"), device=G.DEV, dtype=torch.bfloat16)
+    err = K.new_error_word(G.DEV)
+    n_part = len(part_tok) // 2
+    ms = max(splits, 1)
+    part_o = torch.full((max(1, n_part) * H * ms, HD), float("nan"), device=G.DEV)
+    part_ml = torch.full((max(1, n_part) * H * ms, 2), float("nan"), device=G.DEV)
+    for items, decode in ((pre, False), (dec, True)):
+        if items:
+            K.attention_mma(seqs.q_dev, H * HD, out, seqs.kpool, seqs.vpool, G.i32(np.asarray(items).reshape(-1)),
+                            len(items), decode, seqs.q_start, seqs.q_len, seqs.pos0, G.i32(part_base), seqs.seq_row,
+                            seqs.table, part_o, part_ml, ms, H, KV, HD, page, seqs.num_pages, window, HD ** -0.5, err)
+    if n_part:
+        K.attention_merge(part_o, part_ml, G.i32(part_tok), n_part, out, H, HD, ms)
+    K.check_error_word(err)
+    return out
+
+
+@pytest.mark.parametrize("HD,H,KV,page,window,splits", MMA_CASES)
+def test_attention_tensor_core_kernel(HD, H, KV, page, window, splits):
+    """prompt portions (one starting at position 0, one in the middle of a long context), single decode tokens with
+    short and long contexts and a few tokens at once, in one launch pair; one far key that takes all the weight"""
+    lengths, q_lens = [900, 150, 1, 333, 70, 260], [1, 150, 1, 3, 33, 100]
+    seqs = G.PagedSequences(lengths, q_lens, H, KV, HD, page, torch.bfloat16, seed=9, rows=[4, 1, 0, 6, 2, 3])
+    far = 5 if window is None else 900 - window
+    dominant_key(seqs, 0, far)
+    seqs.round().build()
+    out = run_mma(seqs, window, splits)
+    close(out, seqs.reference(HD ** -0.5, window), torch.bfloat16, "tensor-core paged attention")
+    want = seqs.v[0][far].repeat_interleave(H // KV, 0).reshape(-1).double()
+    assert float((out[0].double().cpu() - want).abs().max()) < 0.05 * float(want.abs().max()) + 1e-2
+
+
+@pytest.mark.parametrize("splits", [1, 4])
+def test_attention_tensor_core_kernel_window_edge(splits):
+    H, KV, HD, page, window = 8, 2, 64, 16, 130
+    seqs = G.PagedSequences([700, 700], [1, 40], H, KV, HD, page, torch.bfloat16, seed=10)
+    dominant_key(seqs, 0, 700 - window - 1)                           # one position too old: must not count
+    dominant_key(seqs, 1, 700 - window)                               # the first key of the last query's window
+    seqs.round().build()
+    out = run_mma(seqs, window, splits)
+    close(out, seqs.reference(HD ** -0.5, window), torch.bfloat16, "window edge")
+
+
+def test_attention_kernel_refuses_head_sizes_it_does_not_take():
+    K = ops()
+    assert [K.attention_mma_supports(h) for h in (16, 32, 48, 64, 96, 128, 256)] == [True, True, False, True, False, True, False]
+    seqs = G.PagedSequences([20], [1], 2, 1, 48, 8, torch.bfloat16).round().build()
+    with pytest.raises(Exception, match="does not take these sizes"):
+        run_mma(seqs, None, 1)
+    big = G.PagedSequences([20], [1], 1, 1, 512, 8, torch.float32).build()
+    out = torch.empty(1, 512, device=G.DEV)
+    with pytest.raises(Exception, match="does not take these sizes"):
+        K.attention_simple(big.q_dev, 512, out, big.positions, big.tok_row, big.table, big.kpool, big.vpool, 1, 1, 512,
+                           8, big.num_pages, None, 1.0, K.new_error_word(G.DEV))
+
+
+# ------------------------------------------------------------------------------------------------ sampling
+def sample_rows(logits, rows, cnt=None, seen=None):
+    K = ops()
+    from mashbox_b200.sampling.sampler import ROW
+    n, V = len(rows), logits.shape[1]
+    packed = np.zeros(n, ROW)
+    for i, r in enumerate(rows):
+        packed[i] = (r.get("temperature", 0.0), r.get("top_p", 1.0), r.get("min_p", 0.0), r.get("rep", 1.0),
+                     r.get("freq", 0.0), r.get("pres", 0.0), r.get("top_k", 0), r.get("slot", -1),
+                     r.get("seed", 0) & 0xFFFFFFFF, (r.get("seed", 0) >> 32) & 0xFFFFFFFF, r.get("step", 0),
+                     r.get("row", i))
+    assert K.sample_params_size() == ROW.itemsize
+    work = torch.empty(n, V, device=G.DEV)
+    out = torch.empty(n, dtype=torch.int32, device=G.DEV)
+    K.sample(logits, work, torch.from_numpy(packed.view(np.uint8).copy()).to(G.DEV), cnt, seen, n, out)
+    return out.tolist(), work.cpu().numpy()
+
+
+def test_argmax_takes_the_lowest_index_of_the_maximum():
+    K = ops()
+    V = 128256 + 3
+    lg = torch.zeros(3, V)
+    lg[0, [70000, 9, 100000]] = 5.0
+    lg[1, V - 1] = 1.0
+    lg[2] = -torch.arange(V).float()
+    out = torch.empty(3, dtype=torch.int32, device=G.DEV)
+    K.argmax(lg.to(G.DEV), out)
+    assert out.tolist() == [9, V - 1, 0]
+    toks, _ = sample_rows(lg.to(G.DEV), [dict(), dict(), dict()])
+    assert toks == [9, V - 1, 0]
+
+
+def test_cuts_keep_exactly_the_allowed_set_ties_included():
+    g = torch.Generator().manual_seed(11)
+    V = 509
+    lg = (3 * torch.randn(6, V, generator=g)).round(decimals=1)          # rounded: many ties
+    rows = [dict(temperature=0.7, top_k=5), dict(temperature=1.3, top_p=0.8), dict(temperature=1.0, min_p=0.05),
+            dict(temperature=0.9, top_k=40, top_p=0.7, min_p=0.02), dict(temperature=2.0, top_k=1),
+            dict(temperature=1.0, top_p=1e-6)]
+    toks, work = sample_rows(lg.to(G.DEV), rows)
+    for i, r in enumerate(rows):
+        want = psamp.transform(lg[i].numpy(), r["temperature"], r.get("top_k", 0), r.get("top_p", 1.0), r.get("min_p", 0.0))
+        kept, want_kept = work[i] > -np.inf, want > -np.inf
+        assert (kept == want_kept).all(), (i, kept.sum(), want_kept.sum())
+        assert np.allclose(work[i][kept], want[kept], rtol=1e-6)
+        assert kept[toks[i]]
+    assert (work[4] > -np.inf).sum() == (lg[4] == lg[4].max()).sum()      # top_k 1 keeps the maximum and its ties
+
+
+def test_draws_equal_the_plain_generator_and_depend_on_seed_and_token_index_only():
+    g = torch.Generator().manual_seed(12)
+    V = 300
+    lg = 2 * torch.randn(1, V, generator=g)
+    rows = [dict(temperature=0.8, seed=7, step=s, row=0) for s in range(12)] + \
+           [dict(temperature=0.8, seed=(1 << 40) + 7, step=3, row=0)]
+    toks, _ = sample_rows(lg.to(G.DEV), rows)
+    want = [psamp.sample(lg[0].numpy(), temperature=0.8, seed=r["seed"], step=r["step"]) for r in rows]
+    assert toks == want
+    assert len(set(toks[:12])) > 3
+    # the same row among other rows, in another place of the batch: the same token
+    other = 2 * torch.randn(3, V, generator=g)
+    both = torch.cat([other, lg]).to(G.DEV)
+    toks2, _ = sample_rows(both, [dict(temperature=1.5, seed=1, step=0, row=0), dict(row=1),
+                                  dict(temperature=0.8, seed=7, step=5, row=3), dict(temperature=0.3, seed=9, row=2)])
+    assert toks2[2] == toks[5]
+
+
+def test_penalties_and_their_state():
+    K = ops()
+    V = 200
+    g = torch.Generator().manual_seed(13)
+    lg = 2 * torch.randn(2, V, generator=g)
+    cnt = torch.zeros(4, V, dtype=torch.int32, device=G.DEV)
+    seen = torch.zeros(4, V, dtype=torch.uint8, device=G.DEV)
+    prompt, generated = [5, 9, 5, 77], [9, 9, 120]
+    toks = torch.tensor(prompt + generated, dtype=torch.int32, device=G.DEV)
+    K.penalty_fill(cnt[2], seen[2], toks, len(prompt), len(prompt) + len(generated), V)
+    c, s = np.zeros(V, np.int32), np.zeros(V, bool)
+    c[9], c[120] = 2, 1
+    s[[5, 9, 77, 120]] = True
+    assert (cnt[2].cpu().numpy() == c).all() and (seen[2].cpu().numpy().astype(bool) == s).all()
+    lg[0, 9] = lg[0].max() + 0.5                                          # the favourite is a repeated token
+    rows = [dict(rep=1.7, freq=0.4, pres=0.3, slot=2, row=0), dict(temperature=0.9, rep=1.2, pres=1.0, slot=2, seed=3, row=1)]
+    got, work = sample_rows(lg.to(G.DEV), rows[:1], cnt, seen)
+    want = psamp.sample(lg[0].numpy(), rep=1.7, freq=0.4, pres=0.3, cnt=c, seen=s)
+    assert got == [want] and want != 9
+    assert np.allclose(work[0], psamp.penalise(lg[0].numpy(), c, s, 1.7, 0.4, 0.3), rtol=1e-6)
+    c[want] += 1
+    s[want] = True
+    assert (cnt[2].cpu().numpy() == c).all() and (seen[2].cpu().numpy().astype(bool) == s).all()   # the pick is counted
+    got, _ = sample_rows(lg.to(G.DEV), rows[1:], cnt, seen)
+    assert got == [psamp.sample(lg[1].numpy(), temperature=0.9, rep=1.2, pres=1.0, seed=3, cnt=c, seen=s)]
+    assert int(cnt[0].sum()) == 0 and int(cnt[3].sum()) == 0
