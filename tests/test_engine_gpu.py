@@ -1,0 +1,176 @@
+"""-m gpu: the engine through its Python entry point -- greedy and sampled generation against the plain implementation,
+long decoding, the first tokens of a sequence, preemption when pages run out, cancelling, the command line."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from tests import helpers as H
+from tests.plain import llama as plain
+from tests.plain import sampling as psamp
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def engine(tmp, name, mode, **kw):
+    from mashbox_b200.engine.engine import Engine
+    dtype, opts = H.MODES[mode]
+    folder = H.make_folder(tmp, name, H.store_for(dtype))
+    kw.setdefault("max_tokens", 1024)
+    kw.setdefault("max_requests", 4)
+    return folder, Engine.from_folder(folder, dtype=dtype, page_size=H.TINY[name][2], options=opts, **kw)
+
+
+def teacher_forced_ok(folder, prompt, ids, mode, samp=None):
+    """every generated token is what the plain implementation picks from the same history (or, where the plain model
+    has a near tie or bfloat16 noise reaches the gap, one of the near-best)"""
+    cfg, W = H._plain_model(folder)
+    lg = plain.forward(cfg, W, prompt + ids[:-1])[len(prompt) - 1:].numpy()
+    noise = 1e-4 if mode == "f32" else 0.03 * np.abs(lg).max()
+    for i, (t, row) in enumerate(zip(ids, lg)):
+        if samp is None:
+            assert row.max() - row[t] <= noise, (i, t, int(row.argmax()), float(row.max() - row[t]))
+        else:
+            want = psamp.sample(row.astype(np.float32), step=i, **samp)
+            if t != want:                # allowed only when the two leading noisy scores are closer than the noise
+                x = psamp.transform(row.astype(np.float32), samp["temperature"])
+                s = np.array([x[v] + psamp.gumbel(psamp.philox_word(samp["seed"], v, i)) for v in (t, want)])
+                assert abs(s[0] - s[1]) <= noise / samp["temperature"], (i, t, want, s)
+                assert mode != "f32" or abs(s[0] - s[1]) <= 1e-4
+
+
+@pytest.mark.parametrize("name,mode", [(n, m) for n in ("A", "B") for m in ("f32", "bf16")])
+def test_greedy_generation_through_the_entry_point(tmp_path_factory, name, mode):
+    folder, eng = engine(tmp_path_factory.mktemp("m"), name, mode)
+    prompts = H.prompts_for(name, (7, 13), seed=4)
+    out = eng.generate(prompts, max_new=16)
+    assert out["finish"] == ["length", "length"] and [len(x) for x in out["ids"]] == [16, 16]
+    assert out["timing"]["new_tokens"] == 32 and not out["timing"]["sampled"]
+    for p, ids in zip(prompts, out["ids"]):
+        teacher_forced_ok(folder, p, ids, mode)
+    eng.cache.check()
+    assert eng.cache.free_pages() == [eng.cache.num_pages]
+    # alone and in the batch: the same tokens
+    alone = eng.generate([prompts[1]], max_new=16)
+    if mode == "f32":
+        assert alone["ids"][0] == out["ids"][1]
+    # a stop token ends the answer and is not emitted
+    stop = out["ids"][0][5]
+    cut = eng.generate([prompts[0]], max_new=16, stop_ids=(stop,))
+    first = out["ids"][0].index(stop)
+    if mode == "f32":
+        assert cut["finish"] == ["stop"] and cut["ids"][0] == out["ids"][0][:first]
+
+
+@pytest.mark.parametrize("mode", ["f32", "bf16"])
+def test_sampled_generation_chunked_and_mixed(tmp_path_factory, mode):
+    """configuration B's workload: prompts of 5, 40 and 130 tokens, prompt portions of 32 beside decoded tokens,
+    24 tokens each at temperature 0.8 with seed 7"""
+    folder, eng = engine(tmp_path_factory.mktemp("m"), "B", mode, chunk=32, max_tokens_per_step=40)
+    prompts = H.prompts_for("B", (5, 40, 130), seed=5)
+    samp = dict(temperature=0.8, seed=7)
+    out = eng.generate(prompts, max_new=24, samp=[samp] * 3)
+    assert out["timing"]["sampled"] and [len(x) for x in out["ids"]] == [24, 24, 24]
+    for p, ids in zip(prompts, out["ids"]):
+        teacher_forced_ok(folder, p, ids, mode, samp)
+    assert len({tuple(x) for x in out["ids"]}) == 3
+    # other settings reach the kernel too: top_k 1 is greedy whatever the temperature
+    g = eng.generate(prompts[:1], max_new=8)
+    k1 = eng.generate(prompts[:1], max_new=8, samp=[dict(temperature=1.5, top_k=1, seed=3)])
+    assert g["ids"] == k1["ids"]
+    # a repetition penalty changes a greedy answer that repeats itself
+    rep = eng.generate(prompts[:1], max_new=24, samp=[dict(repetition_penalty=1.8, presence_penalty=0.5)])
+    plain_rep = eng.generate(prompts[:1], max_new=24)
+    assert len(set(rep["ids"][0])) >= len(set(plain_rep["ids"][0]))
+
+
+@pytest.mark.parametrize("mode", ["f32", "bf16"])
+def test_pages_run_out_preemption_keeps_the_answers(tmp_path_factory, mode):
+    tmp = tmp_path_factory.mktemp("m")
+    prompts = H.prompts_for("A", (20, 24, 17, 30), seed=6)
+    samp = [dict(temperature=0.7, seed=11 + i) for i in range(4)]
+    _, roomy = engine(tmp, "A", mode, max_tokens=1024)
+    want = roomy.generate(prompts, max_new=40, samp=samp)
+    assert want["preemptions"] == [0, 0, 0, 0]
+    _, tight = engine(tmp, "A", mode, max_tokens=160)                 # 4 x 70 tokens do not fit in 160
+    got = tight.generate(prompts, max_new=40, samp=samp)
+    assert sum(got["preemptions"]) > 0 and got["finish"] == ["length"] * 4
+    if mode == "f32":
+        assert got["ids"] == want["ids"]
+    else:
+        same = sum(a == b for x, y in zip(got["ids"], want["ids"]) for a, b in zip(x, y))
+        assert same >= 0.8 * 160
+    tight.cache.check()
+    assert tight.cache.free_pages() == [tight.cache.num_pages]
+    # a request that can never fit is refused alone, before anything runs
+    with pytest.raises(ValueError, match="over the context"):
+        tight.generate([list(range(100))], max_new=100)
+    rows = tight.admit([dict(ids=list(range(100)), max_new=100), dict(ids=[1, 2, 3], max_new=2)])
+    assert rows[0].finish == "error" and "over the context" in rows[0].error
+    while tight.busy():
+        tight.step()
+    assert rows[1].finish == "length" and len(rows[1].generated) == 2
+
+
+def test_cancel_through_on_step(tmp_path_factory):
+    _, eng = engine(tmp_path_factory.mktemp("m"), "A", "f32")
+    prompts = H.prompts_for("A", (9, 9), seed=7)
+    out = eng.generate(prompts, max_new=30, on_step=lambda ids, fin: [0] if len(ids[0]) >= 4 and fin[0] is None else [])
+    assert out["finish"] == ["cancel", "length"] and 4 <= len(out["ids"][0]) < 30 and len(out["ids"][1]) == 30
+    assert eng.cache.free_pages() == [eng.cache.num_pages]
+
+
+@pytest.mark.parametrize("name,mode", [("A", "f32"), ("B", "f32"), ("B", "bf16-plain"), ("A", "bf16")])
+def test_long_decoding_and_first_tokens(tmp_path_factory, name, mode):
+    """a short prompt, then 330 tokens one by one (many pages, a second request decoding beside it part of the time);
+    and sequences of one, two and three tokens"""
+    from mashbox_b200.engine.replay import make_runner, run_step
+    tmp = tmp_path_factory.mktemp("m")
+    dtype, opts = H.MODES[mode]
+    folder = H.make_folder(tmp, name, H.store_for(dtype))
+    runner = make_runner(folder, dtype, 448, page_size=H.TINY[name][2], options=opts)
+    long, side = H.prompts_for(name, (335, 90), seed=8)
+    got, got_side = [], []
+    for i in range(len(long)):
+        entries = [dict(id="long", tokens=long[:5] if i == 4 else [long[i]], want=[4] if i == 4 else [0])] if i >= 4 else []
+        if 100 <= i < 100 + len(side):
+            entries.append(dict(id="side", tokens=[side[i - 100]], want=[0]))
+        if not entries:
+            continue
+        r = run_step(runner, dict(step=i, entries=entries, end=["side"] if i == 100 + len(side) - 1 else [])).numpy()
+        got.append(r[0])
+        if len(entries) == 2:
+            got_side.append(r[1])
+    H.check(np.stack(got), folder, long, mode, "long decoding", slice(4, None))
+    H.check(np.stack(got_side), folder, side, mode, "decoding beside it")
+    run_step(runner, dict(step=0, entries=[], end=["long"]))
+    for n in (1, 2, 3):
+        p = H.prompts_for(name, (n,), seed=20 + n)[0]
+        r = run_step(runner, dict(step=0, entries=[dict(id="s", tokens=p, want=list(range(n)))], end=["s"])).numpy()
+        H.check(r, folder, p, mode, f"a sequence of {n}")
+    runner.cache.check()
+
+
+def test_command_line(tmp_path):
+    folder = H.make_folder(tmp_path, "A", "float32")
+    cmd = [sys.executable, "-m", "mashbox_b200", "run", folder, "--prompt-ids", "5,17,3,200", "--max-tokens", "6",
+           "--dtype", "float32", "--ctx", "256"]
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    r = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    ids = [int(x) for x in r.stdout.strip().split(",")]
+    cfg, W = plain.read_model(folder)
+    assert ids == plain.greedy(cfg, W, [5, 17, 3, 200], 6)
+    events = [json.loads(l) for l in r.stderr.splitlines() if l.startswith("{")]
+    assert [e["event"] for e in events if e["event"] in ("loaded", "done")] == ["loaded", "done"]
+    assert events[-1]["new_tokens"] == 6
+    s = subprocess.run(cmd[:-4] + ["--temperature", "0.8", "--seed", "7", "--top-k", "50", "--dtype", "float32", "--ctx", "256"],
+                       capture_output=True, text=True, env=env, timeout=600)
+    assert s.returncode == 0 and len(s.stdout.strip().split(",")) == 6
+    bad = subprocess.run(cmd[:5] + ["--prompt-ids", "5,999"], capture_output=True, text=True, env=env, timeout=600)
+    assert bad.returncode == 2 and "token ids must be 0..255" in bad.stderr
