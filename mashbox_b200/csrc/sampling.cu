@@ -222,6 +222,7 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) argmax_kernel(const float* __r
     if (threadIdx.x == 0) out[blockIdx.x] = best.i;
 }
 
+#ifndef MB_SAMPLING_KERNELS_ONLY
 MB_API int mb_sample(const float* logits, float* work, const void* params, int* cnt, unsigned char* seen, int n_rows,
                      int V, int* out, cudaStream_t st) {
     if (n_rows == 0) return 0;
@@ -246,3 +247,4 @@ MB_API int mb_argmax(const float* logits, int n_rows, int V, int* out, cudaStrea
 }
 
 MB_API int mb_sample_params_size() { return (int)sizeof(RowParams); }
+#endif  // MB_SAMPLING_KERNELS_ONLY

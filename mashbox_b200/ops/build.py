@@ -29,7 +29,9 @@ LIBRARIES = {            # library name -> (source file, extra link flags)
     "attention_simple": ("attention_simple.cu", []),
     "attention_mma": ("attention_mma.cu", []),
     "sampling": ("sampling.cu", []),
+    "sampling_noalloc": ("sampling_noalloc.cu", []),
 }
+EXTRA_SOURCES = {"sampling_noalloc": ["sampling.cu", "sampling_noalloc.h"]}      # files a library includes
 _loaded = {}
 _lock = threading.Lock()
 
@@ -60,7 +62,7 @@ def build_dir():
 def _digest(name):
     src, extra = LIBRARIES[name]
     h = hashlib.sha256()
-    for f in [src] + HEADERS:
+    for f in [src] + HEADERS + EXTRA_SOURCES.get(name, []):
         with open(os.path.join(CSRC, f), "rb") as fh:
             h.update(fh.read())
     h.update(" ".join(ARCH_FLAGS + FLAGS + extra).encode())
