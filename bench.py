@@ -123,7 +123,7 @@ def run_ours(a):
     t0 = time.time()
     eng = Engine.from_config(cfg, RandomSource(shapes, 0, torch.bfloat16, dev), dtype="bfloat16", device=dev,
                              page_size=16, max_tokens=pool_tokens, max_requests=max_b, max_tokens_per_step=2048 + max_b,
-                             chunk=2048, max_context=per_request)
+                             chunk=2048, max_context=per_request, cuda_graphs=not a.no_graphs)
     torch.cuda.synchronize()
     load_s = time.time() - t0
     gen = torch.Generator().manual_seed(1)
@@ -262,6 +262,7 @@ def main():
     ap.add_argument("--context", type=int, default=8192)
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
+    ap.add_argument("--no-graphs", action="store_true", help="launch every kernel directly (for profilers)")
     a = ap.parse_args()
     if a.impl == "reference":
         return run_reference(a)

@@ -24,6 +24,7 @@ struct AttnParams {
     const int* table; int max_blocks;
     float* part_o; float* part_ml; int max_splits;
     int H, KV, G, page, num_pages, window;
+    int page_shift;                         // log2(page) when the page size is a power of two, else -1
     float scale_log2;
     int* err;
 };
@@ -68,15 +69,21 @@ template <int HD, int BN>
 __device__ __forceinline__ void load_kv_tile(bf16* ks, bf16* vs, const AttnParams& P, const int* tb, int kvh, int kb,
                                              int lo, int hi, int tid) {
     constexpr int CH = HD / 8;
+    const int shift = P.page_shift, mask = P.page - 1;
+    int last_block = -1, pg = -1;
+#pragma unroll
     for (int cid = tid; cid < BN * CH; cid += 128) {
         const int row = cid / CH, c = cid % CH;
         const int kp = kb + row;
         const bf16 *ksrc = P.kpool, *vsrc = P.vpool;
         int bytes = 0;
         if (kp >= lo && kp < hi) {                       // below lo a window may have given the pages back
-            const int pg = tb[kp / P.page];
+            int block, slot;
+            if (shift >= 0) { block = kp >> shift; slot = kp & mask; }
+            else { block = kp / P.page; slot = kp - block * P.page; }
+            if (block != last_block) { pg = tb[block]; last_block = block; }
             if (pg >= 0 && pg < P.num_pages) {
-                const size_t off = (((size_t)pg * P.KV + kvh) * P.page + (kp % P.page)) * HD + c * 8;
+                const size_t off = (((size_t)pg * P.KV + kvh) * P.page + slot) * HD + c * 8;
                 ksrc += off; vsrc += off; bytes = 16;
             } else {
                 mb_set_error(P.err, pg < 0 ? MB_ERR_PAGE_MISSING : MB_ERR_PAGE_RANGE);
@@ -365,6 +372,8 @@ MB_API int mb_attn_mma_bf16(const void* q, int q_stride, void* out, const void* 
     P.table = table; P.max_blocks = max_blocks;
     P.part_o = part_o; P.part_ml = part_ml; P.max_splits = max_splits;
     P.H = H; P.KV = KV; P.G = H / KV; P.page = page; P.num_pages = num_pages; P.window = window;
+    P.page_shift = -1;
+    for (int sft = 0; sft < 31; sft++) if ((1 << sft) == page) P.page_shift = sft;
     P.scale_log2 = scale * 1.4426950408889634f;
     P.err = err;
 #define MB_ATTN_CASE(hd)                                                                   \

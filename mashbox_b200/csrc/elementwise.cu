@@ -2,6 +2,37 @@
 // T is the activation / cache storage type (float on the 32-bit path, bf16 to serve); all arithmetic is float.
 #include "common.cuh"
 
+// ------------------------------------------------------------------------------------------------ 8-wide access
+// Eight consecutive values as floats, read and written with 128-bit accesses (the address must be 16-byte aligned for
+// bf16 and 32-byte aligned rows are not needed: two float4 for float storage).
+__device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        v[2 * i] = __uint_as_float(w[i] << 16);
+        v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+__device__ __forceinline__ void store8(float* p, const float (&v)[8]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    *reinterpret_cast<float4*>(p + 4) = make_float4(v[4], v[5], v[6], v[7]);
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&v)[8]) {
+    uint4 u;
+    uint32_t* w = reinterpret_cast<uint32_t*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        w[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    *reinterpret_cast<uint4*>(p) = u;
+}
+
 // ------------------------------------------------------------------------------------------------ embedding
 // x[n, :] = table[tok[n], :] into the float residual stream.
 template <typename T>
@@ -16,6 +47,27 @@ __global__ void embed_kernel(const int* __restrict__ tok, const T* __restrict__ 
     }
     const T* row = table + (size_t)t * D;
     for (int d = threadIdx.x; d < D; d += blockDim.x) x[(size_t)n * D + d] = mb_load(row + d);
+}
+
+
+// the same with 128-bit accesses, for widths that are a multiple of 8
+template <typename T>
+__global__ void embed_vec_kernel(const int* __restrict__ tok, const T* __restrict__ table, float* __restrict__ x,
+                                 int D, int V, int* err) {
+    const int n = blockIdx.x;
+    const int t = tok[n];
+    const bool ok = t >= 0 && t < V;
+    if (!ok && threadIdx.x == 0) mb_set_error(err, MB_ERR_TOKEN_RANGE);
+    const T* row = table + (size_t)(ok ? t : 0) * D;
+    for (int c = threadIdx.x; c < D / 8; c += blockDim.x) {
+        float v[8];
+        if (ok) load8(row + c * 8, v);
+        else {
+#pragma unroll
+            for (int i = 0; i < 8; i++) v[i] = 0.0f;
+        }
+        store8(x + (size_t)n * D + c * 8, v);
+    }
 }
 
 // ------------------------------------------------------------------------------------------------ add + RMSNorm
@@ -52,6 +104,61 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
             v += a;
         }
         mb_store(o + d, v * inv * w[d]);
+    }
+}
+
+
+// The same for widths that are a multiple of 8 and at most 256 * 8 * NORM_MAX_CHUNKS: every thread keeps its values in
+// registers between the two passes and all accesses are 128 bits wide.
+#define NORM_MAX_CHUNKS 4
+template <typename T>
+__global__ void __launch_bounds__(256) add_rmsnorm_vec_kernel(float* __restrict__ x, const T* __restrict__ delta,
+                                                             const float* __restrict__ dbias,
+                                                             const int* __restrict__ rows, const float* __restrict__ w,
+                                                             float eps, T* __restrict__ out, int D) {
+    __shared__ float scratch[32];
+    const int i = blockIdx.x;
+    const size_t r = rows ? (size_t)rows[i] : (size_t)i;
+    float* xr = x + r * D;
+    const T* dr = delta ? delta + r * D : nullptr;
+    const int chunks = D / 8;
+    float v[NORM_MAX_CHUNKS][8];
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < NORM_MAX_CHUNKS; j++) {
+        const int c = threadIdx.x + j * 256;
+        if (c < chunks) {
+            load8(xr + c * 8, v[j]);
+            if (dr) {
+                float a[8];
+                load8(dr + c * 8, a);
+                if (dbias) {
+                    float b[8];
+                    load8(dbias + c * 8, b);
+#pragma unroll
+                    for (int e = 0; e < 8; e++) a[e] += b[e];
+                }
+#pragma unroll
+                for (int e = 0; e < 8; e++) v[j][e] += a[e];
+                if (!rows) store8(xr + c * 8, v[j]);
+            }
+#pragma unroll
+            for (int e = 0; e < 8; e++) ss = fmaf(v[j][e], v[j][e], ss);
+        }
+    }
+    ss = mb_block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / (float)D + eps);
+    T* o = out + (size_t)i * D;
+#pragma unroll
+    for (int j = 0; j < NORM_MAX_CHUNKS; j++) {
+        const int c = threadIdx.x + j * 256;
+        if (c < chunks) {
+            float g[8];
+            load8(w + c * 8, g);
+#pragma unroll
+            for (int e = 0; e < 8; e++) g[e] = v[j][e] * inv * g[e];
+            store8(o + c * 8, g);
+        }
     }
 }
 
@@ -132,11 +239,27 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
     mb_store(out + i, (g / (1.0f + expf(-g))) * u);
 }
 
+
+// the same, eight values per thread, for F a multiple of 8: block (x: chunks of a row), grid.y: rows
+template <typename T>
+__global__ void swiglu_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, int F) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= F / 8) return;
+    const size_t n = blockIdx.y;
+    float g[8], u[8];
+    load8(gu + n * 2 * F + c * 8, g);
+    load8(gu + n * 2 * F + F + c * 8, u);
+#pragma unroll
+    for (int e = 0; e < 8; e++) g[e] = (g[e] / (1.0f + expf(-g[e]))) * u[e];
+    store8(out + n * F + c * 8, g);
+}
+
 // ------------------------------------------------------------------------------------------------ launchers
 template <typename T>
 static int embed_launch(const int* tok, const void* table, float* x, int N, int D, int V, int* err, cudaStream_t st) {
     if (N == 0) return 0;
-    embed_kernel<T><<<N, 256, 0, st>>>(tok, (const T*)table, x, D, V, err);
+    if (D % 8 == 0) embed_vec_kernel<T><<<N, 128, 0, st>>>(tok, (const T*)table, x, D, V, err);
+    else embed_kernel<T><<<N, 256, 0, st>>>(tok, (const T*)table, x, D, V, err);
     MB_LAUNCH_CHECK();
     return 0;
 }
@@ -151,7 +274,10 @@ template <typename T>
 static int add_rmsnorm_launch(float* x, const void* delta, const float* dbias, const int* rows, const float* w,
                               float eps, void* out, int n_out, int D, cudaStream_t st) {
     if (n_out == 0) return 0;
-    add_rmsnorm_kernel<T><<<n_out, 256, 0, st>>>(x, (const T*)delta, dbias, rows, w, eps, (T*)out, D);
+    if (D % 8 == 0 && D <= 256 * 8 * NORM_MAX_CHUNKS)
+        add_rmsnorm_vec_kernel<T><<<n_out, 256, 0, st>>>(x, (const T*)delta, dbias, rows, w, eps, (T*)out, D);
+    else
+        add_rmsnorm_kernel<T><<<n_out, 256, 0, st>>>(x, (const T*)delta, dbias, rows, w, eps, (T*)out, D);
     MB_LAUNCH_CHECK();
     return 0;
 }
@@ -197,7 +323,10 @@ template <typename T>
 static int swiglu_launch(const void* gu, void* out, int N, int F, cudaStream_t st) {
     const size_t total = (size_t)N * F;
     if (total == 0) return 0;
-    swiglu_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, st>>>((const T*)gu, (T*)out, F, total);
+    if (F % 8 == 0 && N <= 65535)
+        swiglu_vec_kernel<T><<<dim3((F / 8 + 127) / 128, N), 128, 0, st>>>((const T*)gu, (T*)out, F);
+    else
+        swiglu_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, st>>>((const T*)gu, (T*)out, F, total);
     MB_LAUNCH_CHECK();
     return 0;
 }

@@ -85,22 +85,24 @@ class Attention:
         target = int(ctx.options.get("attention_target_blocks", 296))
         max_splits = int(ctx.options.get("attention_max_splits", 16))
         S = ctx.S
-        tiles = [1 if ctx.q_len[s] * G <= DECODE_ROWS else -(-ctx.q_len[s] * G // PREFILL_ROWS) for s in range(S)]
-        base = max(1, sum(tiles) * KV)
+        decode_form = [ctx.q_len[s] * G <= DECODE_ROWS for s in range(S)]
+        tiles = [1 if decode_form[s] else -(-ctx.q_len[s] * G // PREFILL_ROWS) for s in range(S)]
+        # the two forms are two launches: each is cut into splits by its own number of blocks
+        base = {f: max(1, sum(t for t, d in zip(tiles, decode_form) if d == f) * KV) for f in (True, False)}
         dec, pre, part_base, part_tok = [], [], [-1] * S, []
         for s in range(S):
             hi = ctx.pos0[s] + ctx.q_len[s]
             lo = max(0, ctx.pos0[s] - self.window + 1) if self.window else 0
             kv_tiles = -(-(hi - lo // KEY_TILE * KEY_TILE) // KEY_TILE)
             ns = 1
-            if ctx.q_len[s] <= DECODE_ROWS and base < target:
-                ns = max(1, min(max_splits, -(-target // base), kv_tiles // 2))
+            if ctx.q_len[s] <= DECODE_ROWS and base[decode_form[s]] < target:
+                ns = max(1, min(max_splits, -(-target // base[decode_form[s]]), kv_tiles // 2))
                 ns = 1 << (ns.bit_length() - 1)                    # a power of two: few distinct work-list shapes
             if ns > 1:
                 part_base[s] = len(part_tok) // 2
                 for t in range(ctx.q_len[s]):
                     part_tok += [ctx.q_start[s] + t, ns]
-            dst = dec if ctx.q_len[s] * G <= DECODE_ROWS else pre
+            dst = dec if decode_form[s] else pre
             for m in range(tiles[s]):
                 for sp in range(ns):
                     dst.append((-(ctx.pos0[s] + (m + 1) * PREFILL_ROWS // G), s, m, sp, ns))
