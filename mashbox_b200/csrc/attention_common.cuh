@@ -1,0 +1,58 @@
+// What the two tensor-core attention kernels share: the launch parameters, the PTX wrappers (cp.async, ldmatrix,
+// mma.sync m16n8k16 bf16) and the XOR swizzle of a tile whose rows hold HD bf16 values.
+#pragma once
+#include "common.cuh"
+
+typedef __nv_bfloat16 bf16;
+
+struct AttnParams {
+    const bf16* q; int q_stride;            // q[n * q_stride + h * HD + d]
+    bf16* out;                              // out[n * H * HD + h * HD + d]
+    const bf16* kpool; const bf16* vpool;   // [page][KV][slot][HD]
+    const int4* items;                      // (sequence, row tile, split, number of splits)
+    const int* q_start; const int* q_len; const int* pos0; const int* part_base;   // per sequence
+    const int* seq_row;                     // row of the block table of each sequence
+    const int* table; int max_blocks;
+    float* part_o; float* part_ml; int max_splits;
+    int H, KV, G, page, num_pages, window;
+    int page_shift;                         // log2(page) when the page size is a power of two, else -1
+    float scale_log2;
+    int* err;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, int bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(dst)), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// element offset of 16-byte chunk c of row `row` in a tile whose rows hold HD bf16 values (swizzled against bank conflicts)
+template <int HD> __device__ __forceinline__ int swz(int row, int c) {
+    constexpr int CH = HD / 8;
+    int pc;
+    if (CH >= 8) pc = c ^ (row & 7);
+    else if (CH == 4) pc = c ^ ((row >> 1) & 3);
+    else pc = c ^ ((row >> 2) & 1);
+    return (row * CH + pc) * 8;
+}
+

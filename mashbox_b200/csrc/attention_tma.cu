@@ -1,0 +1,415 @@
+// Paged flash attention with the K/V tiles brought in by the Tensor Memory Accelerator.
+//
+// Same work decomposition and arithmetic as attention_mma.cu (rows = (token, head-in-group) of one sequence and kv head;
+// PREFILL form with 64 rows per block, DECODE form with at most 16 rows and the 64 keys of a tile split over the warps;
+// splits over blocks merged by attn_merge_kernel of that file).  What changes is how keys and values reach shared
+// memory: one producer warp walks the block table and issues one cp.async.bulk.tensor.2d per (page, 128-byte half of a
+// head row) with the 128-byte swizzle, completing on an mbarrier per stage; four consumer warps wait on that barrier,
+// run ldmatrix + mma.sync on the tile and hand the stage back through a second mbarrier.  The consumer warps execute
+// no address arithmetic and no load instructions for K and V, which is what bounded the cp.async kernel (its decode
+// form spent most of its issue slots on them).  Every wait on an mbarrier is bounded: when it runs out the thread
+// records MB_ERR_WAIT_TIMEOUT in the engine's error word and returns.
+//
+// It takes head sizes 64 and 128 and page sizes 8, 16, 32 and 64 (a page's box must cover whole 8-row swizzle atoms and
+// a 64-key tile must cover whole pages); other sizes go to attention_mma.cu.  No cluster, no multicast.
+#include <cuda.h>
+#include <cstdio>
+#include <cstring>
+#include "attention_common.cuh"
+
+#define TMA_WAIT_LIMIT (1 << 20)
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+// false when the wait ran out (the error word is set)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* err) {
+    for (int it = 0; it < TMA_WAIT_LIMIT; it++) {
+        uint32_t ok;
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    mb_set_error(err, MB_ERR_WAIT_TIMEOUT);
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 128;\n" ::: "memory"); }
+
+// element offset of 16-byte chunk c of key row `row` in a K or V stage as the TMA lays it out: halves of 64 columns,
+// each 64 rows x 128 bytes, 16-byte chunks XORed with the row (the 128-byte swizzle)
+template <int HD> __device__ __forceinline__ int kv_off(int row, int c) {
+    return (c >> 3) * (64 * 64) + row * 64 + (((c & 7) ^ (row & 7)) << 3);
+}
+
+template <int HD, bool DECODE, int STAGES>
+__global__ void __launch_bounds__(160) attn_tma_kernel(const AttnParams P, const __grid_constant__ CUtensorMap kmap,
+                                                        const __grid_constant__ CUtensorMap vmap) {
+    constexpr int BM = DECODE ? 16 : 64, BN = 64, CH = HD / 8;
+    constexpr int NT = DECODE ? 2 : 8;
+    constexpr int KS = HD / 16;
+    constexpr int DT = HD / 8;
+    constexpr int HALVES = HD / 64;
+    constexpr int TILE = BN * HD;                        // elements of one K (or V) tile
+    extern __shared__ unsigned char smem_unaligned[];
+    unsigned char* smem_raw = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~static_cast<uintptr_t>(1023));
+    bf16* kvs = reinterpret_cast<bf16*>(smem_raw);                       // STAGES x (K tile, V tile), 1024-byte aligned
+    bf16* qs = kvs + (size_t)STAGES * 2 * TILE;                          // BM x HD, swizzled as in attention_mma.cu
+    uint64_t* bars = reinterpret_cast<uint64_t*>(qs + BM * HD);          // full[STAGES], empty[STAGES]
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tig = lane & 3;
+    const int4 item = P.items[blockIdx.x];
+    const int seq = item.x, m_tile = item.y, split = item.z, n_splits = item.w;
+    const int kvh = blockIdx.y;
+    const int G = P.G, R = P.q_len[seq] * G, pos0 = P.pos0[seq], tok0 = P.q_start[seq];
+    const int row0 = m_tile * BM;
+    if (row0 >= R) return;
+    const int row_last = min(R, row0 + BM) - 1;
+    const int pos_min = pos0 + row0 / G, pos_max = pos0 + row_last / G;
+    const int hi = pos_max + 1;
+    const int lo = (P.window > 0 && pos_min - P.window + 1 > 0) ? pos_min - P.window + 1 : 0;
+    const int lo_al = (lo / BN) * BN;
+    const int n_tiles = (hi - lo_al + BN - 1) / BN;
+    const int tps = (n_tiles + n_splits - 1) / n_splits;
+    const int t_begin = split * tps, t_end = min(n_tiles, t_begin + tps);
+    const int* tb = P.table + (size_t)P.seq_row[seq] * P.max_blocks;
+
+    if (tid == 0) {
+#pragma unroll
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 4);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == 4) {
+        // ---------------------------------------------------------------- producer: one lane issues every copy
+        if (lane != 0) return;
+        const int shift = P.page_shift, page = P.page;
+        const int pages_per_tile = BN >> shift;
+        for (int t = t_begin; t < t_end; t++) {
+            const int i = t - t_begin, s = i % STAGES, round = i / STAGES;
+            if (round > 0 && !mbar_wait(empty0 + 8 * s, (round - 1) & 1, P.err)) return;
+            const uint32_t fb = full0 + 8 * s;
+            mbar_expect_tx(fb, 2u * TILE * 2u);
+            const int kb = lo_al + t * BN;
+            const uint32_t kdst = smem_u32(kvs + (size_t)s * 2 * TILE), vdst = kdst + TILE * 2;
+            for (int p = 0; p < pages_per_tile; p++) {
+                const int key0 = kb + p * page, block = key0 >> shift;
+                const bool live = key0 < hi && key0 + page > lo;           // some key of the page can be read
+                int pg = (live && block < P.max_blocks) ? tb[block] : 0;
+                if (pg < 0 || pg >= P.num_pages) {
+                    if (live) mb_set_error(P.err, pg < 0 ? MB_ERR_PAGE_MISSING : MB_ERR_PAGE_RANGE);
+                    pg = 0;                                                // any page: every key of it is masked
+                }
+                const int y = (pg * P.KV + kvh) * page;
+#pragma unroll
+                for (int h = 0; h < HALVES; h++) {
+                    const uint32_t off = (uint32_t)(h * 64 * 64 + p * page * 64) * 2u;
+                    tma_load_2d(kdst + off, &kmap, h * 64, y, fb);
+                    tma_load_2d(vdst + off, &vmap, h * 64, y, fb);
+                }
+            }
+        }
+        return;
+    }
+
+    // -------------------------------------------------------------------- consumers
+    for (int cid = tid; cid < BM * CH; cid += 128) {
+        const int row = cid / CH, c = cid % CH, r = row0 + row;
+        const bf16* src = P.q;
+        int bytes = 0;
+        if (r < R) {
+            src = P.q + (size_t)(tok0 + r / G) * P.q_stride + (size_t)(kvh * G + r % G) * HD + c * 8;
+            bytes = 16;
+        }
+        cp_async16(qs + swz<HD>(row, c), src, bytes);
+    }
+    cp_async_commit();
+
+    const int m0 = DECODE ? 0 : warp * 16;
+    const int nbase = DECODE ? warp * 16 : 0;
+    int rpos[2], rlo[2];
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+        const int r = row0 + m0 + g + i * 8;
+        if (r < R) {
+            rpos[i] = pos0 + r / G;
+            rlo[i] = (P.window > 0 && rpos[i] - P.window + 1 > 0) ? rpos[i] - P.window + 1 : 0;
+        } else {
+            rpos[i] = -1; rlo[i] = 0;
+        }
+    }
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+    float o[DT][4];
+#pragma unroll
+    for (int d = 0; d < DT; d++) { o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.0f; }
+
+    cp_async_wait<0>();
+    consumer_sync();
+    uint32_t qf[KS][4];
+#pragma unroll
+    for (int ks = 0; ks < KS; ks++)
+        ldmatrix_x4(qf[ks], qs + swz<HD>(m0 + (lane & 7) + ((lane >> 3) & 1) * 8, ks * 2 + (lane >> 4)));
+
+    for (int t = t_begin; t < t_end; t++) {
+        const int i = t - t_begin, s = i % STAGES, round = i / STAGES;
+        if (!mbar_wait(full0 + 8 * s, round & 1, P.err)) return;
+        const bf16* kt = kvs + (size_t)s * 2 * TILE;
+        const bf16* vt = kt + TILE;
+        const int kb = lo_al + t * BN;
+
+        float sc[NT][4];
+#pragma unroll
+        for (int j = 0; j < NT; j++) { sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.0f; }
+#pragma unroll
+        for (int ks = 0; ks < KS; ks++) {
+#pragma unroll
+            for (int np = 0; np < NT / 2; np++) {
+                uint32_t b[4];
+                ldmatrix_x4(b, kt + kv_off<HD>(nbase + np * 16 + (lane & 7) + (lane >> 4) * 8, ks * 2 + ((lane >> 3) & 1)));
+                mma_bf16(sc[2 * np], qf[ks], b[0], b[1]);
+                mma_bf16(sc[2 * np + 1], qf[ks], b[2], b[3]);
+            }
+        }
+        // a tile whose keys every row of the block may read needs no mask (all tiles but the last and, with a window,
+        // the first ones); rows past the end of the block then get finite scores, and they are never written
+        const bool full_tile = kb + BN - 1 <= pos_min && kb >= ((P.window > 0) ? pos_max - P.window + 1 : 0);
+        float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int j = 0; j < NT; j++) {
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int ii = e >> 1;
+                float v = sc[j][e] * P.scale_log2;
+                if (!full_tile) {
+                    const int key = kb + nbase + j * 8 + 2 * tig + (e & 1);
+                    if (!(key <= rpos[ii] && key >= rlo[ii])) v = -INFINITY;
+                }
+                sc[j][e] = v;
+                tmax[ii] = fmaxf(tmax[ii], v);
+            }
+        }
+        float corr[2], muse[2];
+#pragma unroll
+        for (int ii = 0; ii < 2; ii++) {
+            tmax[ii] = fmaxf(tmax[ii], __shfl_xor_sync(0xffffffffu, tmax[ii], 1));
+            tmax[ii] = fmaxf(tmax[ii], __shfl_xor_sync(0xffffffffu, tmax[ii], 2));
+            const float m_new = fmaxf(m_run[ii], tmax[ii]);
+            muse[ii] = (m_new == -INFINITY) ? 0.0f : m_new;
+            corr[ii] = exp2f(m_run[ii] - muse[ii]);
+            m_run[ii] = m_new;
+            l_run[ii] *= corr[ii];
+        }
+#pragma unroll
+        for (int j = 0; j < NT; j++) {
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const float p = exp2f(sc[j][e] - muse[e >> 1]);
+                l_run[e >> 1] += p;
+                sc[j][e] = p;
+            }
+        }
+        // the running maximum rarely moves after the first tiles: rescale the accumulators only when it did
+        if (__any_sync(0xffffffffu, corr[0] != 1.0f || corr[1] != 1.0f)) {
+#pragma unroll
+            for (int d = 0; d < DT; d++) { o[d][0] *= corr[0]; o[d][1] *= corr[0]; o[d][2] *= corr[1]; o[d][3] *= corr[1]; }
+        }
+#pragma unroll
+        for (int kk = 0; kk < NT / 2; kk++) {
+            uint32_t a[4];
+            a[0] = pack_bf16(sc[2 * kk][0], sc[2 * kk][1]);
+            a[1] = pack_bf16(sc[2 * kk][2], sc[2 * kk][3]);
+            a[2] = pack_bf16(sc[2 * kk + 1][0], sc[2 * kk + 1][1]);
+            a[3] = pack_bf16(sc[2 * kk + 1][2], sc[2 * kk + 1][3]);
+#pragma unroll
+            for (int dp = 0; dp < HD / 16; dp++) {
+                uint32_t b[4];
+                ldmatrix_x4_trans(b, vt + kv_off<HD>(nbase + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, dp * 2 + (lane >> 4)));
+                mma_bf16(o[2 * dp], a, b[0], b[1]);
+                mma_bf16(o[2 * dp + 1], a, b[2], b[3]);
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty0 + 8 * s);           // this warp is done with the stage
+    }
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+        l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
+        l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
+    }
+    const int H = P.H;
+    if (!DECODE) {
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const int r = row0 + m0 + g + i * 8;
+            if (r >= R) continue;
+            const int tq = r / G, h = kvh * G + r % G;
+            if (n_splits == 1) {
+                const float inv = l_run[i] > 0.0f ? 1.0f / l_run[i] : 0.0f;
+                bf16* dst = P.out + ((size_t)(tok0 + tq) * H + h) * HD + 2 * tig;
+#pragma unroll
+                for (int d = 0; d < DT; d++)
+                    *reinterpret_cast<uint32_t*>(dst + d * 8) = pack_bf16(o[d][2 * i] * inv, o[d][2 * i + 1] * inv);
+            } else {
+                const size_t base = ((size_t)(P.part_base[seq] + tq) * H + h) * P.max_splits + split;
+                float* dst = P.part_o + base * HD + 2 * tig;
+#pragma unroll
+                for (int d = 0; d < DT; d++) { dst[d * 8] = o[d][2 * i]; dst[d * 8 + 1] = o[d][2 * i + 1]; }
+                if (tig == 0) { P.part_ml[base * 2] = m_run[i]; P.part_ml[base * 2 + 1] = l_run[i]; }
+            }
+        }
+    } else {
+        consumer_sync();                                    // every consumer warp is done with the K/V stages
+        float* mo = reinterpret_cast<float*>(kvs);          // [4 warps][16 rows][HD]
+        float* sm_m = mo + 4 * 16 * HD;
+        float* sm_l = sm_m + 4 * 16;
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const int row = g + i * 8;
+            float* dst = mo + ((size_t)(warp * 16 + row)) * HD + 2 * tig;
+#pragma unroll
+            for (int d = 0; d < DT; d++) { dst[d * 8] = o[d][2 * i]; dst[d * 8 + 1] = o[d][2 * i + 1]; }
+            if (tig == 0) { sm_m[warp * 16 + row] = m_run[i]; sm_l[warp * 16 + row] = l_run[i]; }
+        }
+        consumer_sync();
+        for (int idx = tid; idx < 16 * HD; idx += 128) {
+            const int row = idx / HD, d = idx % HD, r = row0 + row;
+            if (r >= R) continue;
+            float M = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < 4; w++) M = fmaxf(M, sm_m[w * 16 + row]);
+            float acc = 0.0f, L = 0.0f;
+#pragma unroll
+            for (int w = 0; w < 4; w++) {
+                const float mw = sm_m[w * 16 + row];
+                const float scl = (mw == -INFINITY) ? 0.0f : exp2f(mw - M);
+                acc += mo[((size_t)(w * 16 + row)) * HD + d] * scl;
+                L += sm_l[w * 16 + row] * scl;
+            }
+            const int tq = r / G, h = kvh * G + r % G;
+            if (n_splits == 1) {
+                P.out[((size_t)(tok0 + tq) * H + h) * HD + d] = __float2bfloat16_rn(L > 0.0f ? acc / L : 0.0f);
+            } else {
+                const size_t base = ((size_t)(P.part_base[seq] + tq) * H + h) * P.max_splits + split;
+                P.part_o[base * HD + d] = acc;
+                if (d == 0) { P.part_ml[base * 2] = M; P.part_ml[base * 2 + 1] = L; }
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiled encode_fn() {
+    static EncodeTiled fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiled>(p);
+    }
+    return fn;
+}
+
+struct MapKey { const void* ptr; long long rows; int hd, page; };
+struct MapEntry { MapKey key; CUtensorMap map; };
+#define MAP_CACHE 512
+static MapEntry map_cache[MAP_CACHE];
+static int map_count = 0;
+
+// the pool [pages][KV][page][HD] seen as a matrix of (pages * KV * page) rows of HD values; box = one page of one kv
+// head, 64 columns wide, 128-byte swizzle
+static int pool_map(const void* pool, long long rows, int HD, int page, CUtensorMap* out) {
+    for (int i = 0; i < map_count; i++) {
+        const MapKey& k = map_cache[i].key;
+        if (k.ptr == pool && k.rows == rows && k.hd == HD && k.page == page) { *out = map_cache[i].map; return 0; }
+    }
+    EncodeTiled enc = encode_fn();
+    if (!enc) return -6;
+    CUtensorMap m;
+    cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
+    cuuint32_t box[2] = {64u, (cuuint32_t)page};
+    cuuint32_t estr[2] = {1u, 1u};
+    CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return -6;
+    if (map_count < MAP_CACHE) {
+        map_cache[map_count].key = MapKey{pool, rows, HD, page};
+        map_cache[map_count].map = m;
+        map_count++;
+    }
+    *out = m;
+    return 0;
+}
+
+template <int HD, bool DECODE, int STAGES>
+static int launch_tma(const AttnParams& P, const CUtensorMap& kmap, const CUtensorMap& vmap, int n_items, cudaStream_t st) {
+    constexpr int BM = DECODE ? 16 : 64;
+    const size_t smem = 1024 + (size_t)STAGES * 2 * 64 * HD * 2 + (size_t)BM * HD * 2 + 2 * STAGES * 8;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_tma_kernel<HD, DECODE, STAGES>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    attn_tma_kernel<HD, DECODE, STAGES><<<dim3(n_items, P.KV), 160, smem, st>>>(P, kmap, vmap);
+    MB_LAUNCH_CHECK();
+    return 0;
+}
+
+MB_API int mb_attn_tma_supports(int HD, int page) {
+    return (HD == 64 || HD == 128) && (page == 8 || page == 16 || page == 32 || page == 64);
+}
+
+MB_API int mb_attn_tma_bf16(const void* q, int q_stride, void* out, const void* kpool, const void* vpool,
+                            const void* items, int n_items, int decode, const int* q_start, const int* q_len,
+                            const int* pos0, const int* part_base, const int* seq_row, const int* table, int max_blocks,
+                            float* part_o, float* part_ml, int max_splits, int H, int KV, int HD, int page, int num_pages,
+                            int window, float scale, int* err, cudaStream_t st) {
+    if (n_items == 0) return 0;
+    if (!mb_attn_tma_supports(HD, page) || KV < 1 || H % KV || KV > 65535) return -2;
+    AttnParams P;
+    P.q = (const bf16*)q; P.q_stride = q_stride; P.out = (bf16*)out;
+    P.kpool = (const bf16*)kpool; P.vpool = (const bf16*)vpool;
+    P.items = (const int4*)items;
+    P.q_start = q_start; P.q_len = q_len; P.pos0 = pos0; P.part_base = part_base; P.seq_row = seq_row;
+    P.table = table; P.max_blocks = max_blocks;
+    P.part_o = part_o; P.part_ml = part_ml; P.max_splits = max_splits;
+    P.H = H; P.KV = KV; P.G = H / KV; P.page = page; P.num_pages = num_pages; P.window = window;
+    P.page_shift = -1;
+    for (int sft = 0; sft < 31; sft++) if ((1 << sft) == page) P.page_shift = sft;
+    P.scale_log2 = scale * 1.4426950408889634f;
+    P.err = err;
+    CUtensorMap kmap, vmap;
+    const long long rows = (long long)num_pages * KV * page;
+    int rc = pool_map(kpool, rows, HD, page, &kmap);
+    if (rc) return rc;
+    rc = pool_map(vpool, rows, HD, page, &vmap);
+    if (rc) return rc;
+    if (HD == 128) return decode ? launch_tma<128, true, 3>(P, kmap, vmap, n_items, st)
+                                 : launch_tma<128, false, 2>(P, kmap, vmap, n_items, st);
+    return decode ? launch_tma<64, true, 4>(P, kmap, vmap, n_items, st)
+                  : launch_tma<64, false, 3>(P, kmap, vmap, n_items, st);
+}

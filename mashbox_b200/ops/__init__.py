@@ -177,6 +177,25 @@ def attention_mma(q, q_stride, out, kpool, vpool, items, n_items, decode, q_star
              HD, page, num_pages, window or 0, float(scale), _p(err), _stream()), "attention_mma")
 
 
+def attention_tma_supports(HD, page):
+    return HD in (64, 128) and page in (8, 16, 32, 64)
+
+
+def attention_tma(q, q_stride, out, kpool, vpool, items, n_items, decode, q_start, q_len, pos0, part_base, seq_row,
+                  table, part_o, part_ml, max_splits, H, KV, HD, page, num_pages, window, scale, err):
+    """The same contract as attention_mma, with K/V tiles loaded by TMA (head sizes 64 and 128, pages of 8 to 64)."""
+    _cuda(q, out, kpool, vpool, items, q_start, q_len, pos0, part_base, table, part_o, part_ml)
+    f = _fn("attention_tma", "mb_attn_tma_bf16",
+            [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
+             c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p] + [c_int] * 7 + [c_float, c_void_p, c_void_p])
+    code = f(_p(q), q_stride, _p(out), _p(kpool), _p(vpool), _p(items), n_items, 1 if decode else 0, _p(q_start),
+             _p(q_len), _p(pos0), _p(part_base), _p(seq_row), _p(table), table.shape[1], _p(part_o), _p(part_ml),
+             max_splits, H, KV, HD, page, num_pages, window or 0, float(scale), _p(err), _stream())
+    if code == -6:
+        raise KernelError("attention_tma: the driver refused the tensor map of the cache pool")
+    _check(code, "attention_tma")
+
+
 def attention_merge(part_o, part_ml, part_tok, n_part, out, H, HD, max_splits):
     _cuda(part_o, part_ml, part_tok, out)
     f = _fn("attention_mma", "mb_attn_merge_bf16",

@@ -22,12 +22,13 @@ from ..errors import KernelError
 CSRC = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "csrc")
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 FLAGS = ["-O3", "-lineinfo", "-std=c++17", "-shared", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
-HEADERS = ["common.cuh"]
+HEADERS = ["common.cuh", "attention_common.cuh"]
 LIBRARIES = {            # library name -> (source file, extra link flags)
     "elementwise": ("elementwise.cu", []),
     "gemm_f32": ("gemm_f32.cu", []),
     "attention_simple": ("attention_simple.cu", []),
     "attention_mma": ("attention_mma.cu", []),
+    "attention_tma": ("attention_tma.cu", []),
     "sampling": ("sampling.cu", []),
     "sampling_noalloc": ("sampling_noalloc.cu", []),
 }

@@ -148,12 +148,13 @@ class Attention:
             if n_part:
                 part_o = ctx.ws.get("attn_part_o", n_part * H * ms, (HD,), torch.float32, reserve=0)
                 part_ml = ctx.ws.get("attn_part_ml", n_part * H * ms, (2,), torch.float32, reserve=0)
+            kind = ctx.options.get("attention_kernel", "tma")
+            flash = ops.attention_tma if kind == "tma" and ops.attention_tma_supports(HD, page) else ops.attention_mma
             for form, n_items, decode in ((nm + "pre", plan["n_pre"], False), (nm + "dec", plan["n_dec"], True)):
                 if n_items:
-                    ops.attention_mma(qkv, width, out, kpool, vpool, ctx.dev(form), n_items, decode, ctx.dev("q_start"),
-                                      ctx.dev("q_len"), ctx.dev("pos0"), ctx.dev(nm + "part_base"), ctx.dev("seq_row"),
-                                      table, part_o, part_ml, ms, H, KV, HD, page, pages, self.window, self.scale,
-                                      ctx.err)
+                    flash(qkv, width, out, kpool, vpool, ctx.dev(form), n_items, decode, ctx.dev("q_start"),
+                          ctx.dev("q_len"), ctx.dev("pos0"), ctx.dev(nm + "part_base"), ctx.dev("seq_row"),
+                          table, part_o, part_ml, ms, H, KV, HD, page, pages, self.window, self.scale, ctx.err)
             if n_part:
                 ops.attention_merge(part_o, part_ml, ctx.dev(nm + "part_tok"), n_part, out, H, HD, ms)
         else:

@@ -215,8 +215,9 @@ MMA_CASES = [  # HD, H, KV, page, window, splits
     (16, 4, 2, 4, None, 1), (128, 32, 8, 32, 700, 8), (64, 5, 5, 16, None, 2), (128, 16, 1, 16, None, 2)]
 
 
-def run_mma(seqs, window, splits):
+def run_mma(seqs, window, splits, kind="mma"):
     K = ops()
+    flash = K.attention_tma if kind == "tma" else K.attention_mma
     H, KV, HD, page = seqs.H, seqs.KV, seqs.HD, seqs.page
     Gq = H // KV
     dec, pre, part_base, part_tok = G.mma_items(seqs, Gq, splits)
@@ -228,17 +229,18 @@ def run_mma(seqs, window, splits):
     part_ml = torch.full((max(1, n_part) * H * ms, 2), float("nan"), device=G.DEV)
     for items, decode in ((pre, False), (dec, True)):
         if items:
-            K.attention_mma(seqs.q_dev, H * HD, out, seqs.kpool, seqs.vpool, G.i32(np.asarray(items).reshape(-1)),
-                            len(items), decode, seqs.q_start, seqs.q_len, seqs.pos0, G.i32(part_base), seqs.seq_row,
-                            seqs.table, part_o, part_ml, ms, H, KV, HD, page, seqs.num_pages, window, HD ** -0.5, err)
+            flash(seqs.q_dev, H * HD, out, seqs.kpool, seqs.vpool, G.i32(np.asarray(items).reshape(-1)),
+                  len(items), decode, seqs.q_start, seqs.q_len, seqs.pos0, G.i32(part_base), seqs.seq_row,
+                  seqs.table, part_o, part_ml, ms, H, KV, HD, page, seqs.num_pages, window, HD ** -0.5, err)
     if n_part:
         K.attention_merge(part_o, part_ml, G.i32(part_tok), n_part, out, H, HD, ms)
     K.check_error_word(err)
     return out
 
 
+@pytest.mark.parametrize("kind", ["mma", "tma"])
 @pytest.mark.parametrize("HD,H,KV,page,window,splits", MMA_CASES)
-def test_attention_tensor_core_kernel(HD, H, KV, page, window, splits):
+def test_attention_tensor_core_kernel(HD, H, KV, page, window, splits, kind):
     """prompt portions (one starting at position 0, one in the middle of a long context), single decode tokens with
     short and long contexts and a few tokens at once, in one launch pair; one far key that takes all the weight"""
     lengths, q_lens = [900, 150, 1, 333, 70, 260], [1, 150, 1, 3, 33, 100]
@@ -246,20 +248,25 @@ def test_attention_tensor_core_kernel(HD, H, KV, page, window, splits):
     far = 5 if window is None else 900 - window
     dominant_key(seqs, 0, far)
     seqs.round().build()
-    out = run_mma(seqs, window, splits)
+    if kind == "tma" and not ops().attention_tma_supports(HD, page):
+        with pytest.raises(Exception, match="does not take these sizes"):
+            run_mma(seqs, window, splits, kind)
+        return
+    out = run_mma(seqs, window, splits, kind)
     close(out, seqs.reference(HD ** -0.5, window), torch.bfloat16, "tensor-core paged attention")
     want = seqs.v[0][far].repeat_interleave(H // KV, 0).reshape(-1).double()
     assert float((out[0].double().cpu() - want).abs().max()) < 0.05 * float(want.abs().max()) + 1e-2
 
 
+@pytest.mark.parametrize("kind", ["mma", "tma"])
 @pytest.mark.parametrize("splits", [1, 4])
-def test_attention_tensor_core_kernel_window_edge(splits):
+def test_attention_tensor_core_kernel_window_edge(splits, kind):
     H, KV, HD, page, window = 8, 2, 64, 16, 130
     seqs = G.PagedSequences([700, 700], [1, 40], H, KV, HD, page, torch.bfloat16, seed=10)
     dominant_key(seqs, 0, 700 - window - 1)                           # one position too old: must not count
     dominant_key(seqs, 1, 700 - window)                               # the first key of the last query's window
     seqs.round().build()
-    out = run_mma(seqs, window, splits)
+    out = run_mma(seqs, window, splits, kind)
     close(out, seqs.reference(HD ** -0.5, window), torch.bfloat16, "window edge")
 
 
