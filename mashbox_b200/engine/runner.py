@@ -34,7 +34,7 @@ class ModelRunner:
         self.options.setdefault("logit_rows", engine_config.max_requests)
         self.ws = Workspace(self.device, engine_config.max_tokens_per_step + engine_config.max_requests)
         self.inputs = StepInputs(self.device)
-        self.err = kernels.new_error_word(self.device)
+        self.err = kernels.error_word(self.device)
         self.graphs, self.seen_signatures = {}, {}
         self.use_graphs = bool(engine_config.cuda_graphs) and not self.options.get("no_graphs", False)
         self.stats = dict(steps=0, tokens=0, graph_replays=0, graph_captures=0)

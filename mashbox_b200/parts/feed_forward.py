@@ -22,11 +22,15 @@ class SwiGLU:
         self.wd = tensors[self.names["down"]]
 
     def forward(self, ctx, h):
+        import torch
         N = ctx.N
-        gu = ctx.ws.get("gate_up", N, (2 * self.F,), ctx.dtype)
-        ctx.ops.linear(h, self.wgu, out=gu)
         a = ctx.ws.get("ffn_act", N, (self.F,), ctx.dtype)
-        ctx.ops.swiglu(gu, a)
+        if ctx.dtype == torch.bfloat16 and ctx.ops.skinny_supports(N, self.D):
+            ctx.ops.linear_swiglu(h, self.wgu, a)           # decode batches: both products and the gate in one kernel
+        else:
+            gu = ctx.ws.get("gate_up", N, (2 * self.F,), ctx.dtype)
+            ctx.ops.linear(h, self.wgu, out=gu)
+            ctx.ops.swiglu(gu, a)
         y = ctx.ws.get("delta", N, (self.D,), ctx.dtype)
         ctx.ops.linear(a, self.wd, out=y)
         return y, None

@@ -376,3 +376,46 @@ def test_penalties_and_their_state():
     got, _ = sample_rows(lg.to(G.DEV), rows[1:], cnt, seen)
     assert got == [psamp.sample(lg[1].numpy(), temperature=0.9, rep=1.2, pres=1.0, seed=3, cnt=c, seen=s)]
     assert int(cnt[0].sum()) == 0 and int(cnt[3].sum()) == 0
+
+
+@pytest.mark.parametrize("N,M,K", [(1, 4096, 4096), (8, 6144, 4096), (3, 100, 96), (16, 509, 320), (11, 4096, 14336), (5, 17, 32), (2, 50, 72), (9, 333, 1000)])
+def test_weight_streaming_product(N, M, K):
+    K_ = ops()
+    g = torch.Generator().manual_seed(14)
+    a = torch.randn(N, K, generator=g).bfloat16()
+    w = (torch.randn(M, K, generator=g) / K ** 0.5).bfloat16()
+    K_.SKINNY["enabled"] = True
+    try:
+        _weight_streaming_checks(K_, a, w, N, M, K)
+    finally:
+        K_.SKINNY["enabled"] = False
+
+
+def _weight_streaming_checks(K_, a, w, N, M, K):
+    assert K_.skinny_supports(N, K)
+    got = K_.linear(a.to(G.DEV), w.to(G.DEV))
+    want = a.double() @ w.double().T
+    close(got, want, torch.bfloat16, "weight-streaming product")
+    assert float((got.double().cpu() - want).abs().max()) <= 2.0 ** -8 * float(want.abs().max()) + 1e-6   # one bf16 rounding
+    f32 = K_.linear(a.to(G.DEV), w.to(G.DEV), out_dtype=torch.float32)
+    close(f32, want, torch.float32, "weight-streaming product, float32 out")
+    # the same answer as the library product up to the last bf16 step, and the same row whatever the batch
+    K_.SKINNY["enabled"] = False
+    try:
+        lib = K_.linear(a.to(G.DEV), w.to(G.DEV))
+    finally:
+        K_.SKINNY["enabled"] = True
+    want = a.double() @ w.double().T
+    assert float((lib.double().cpu() - got.double().cpu()).abs().max()) <= 2.0 ** -7 * float(want.abs().max())
+    one = K_.linear(a[N - 1:].to(G.DEV).contiguous(), w.to(G.DEV))
+    assert torch.equal(one[0], got[N - 1])
+    # gate, up and their product in one kernel
+    F = M // 2
+    if F:
+        act = torch.empty(N, F, device=G.DEV, dtype=torch.bfloat16)
+        K_.linear_swiglu(a.to(G.DEV), w[:2 * F].to(G.DEV).contiguous(), act)
+        gt = (a.double() @ w[:F].double().T).float().bfloat16().double()
+        up = (a.double() @ w[F:2 * F].double().T).float().bfloat16().double()
+        close(act, gt * torch.sigmoid(gt) * up, torch.bfloat16, "fused SwiGLU product")
+    assert not K_.skinny_supports(17, 4096) and not K_.skinny_supports(4, 100)
+    K_.check_error_word(K_.error_word(G.DEV))
