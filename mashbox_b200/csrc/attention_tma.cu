@@ -52,7 +52,7 @@ template <int HD> __device__ __forceinline__ int kv_off(int row, int c) {
 }
 
 template <int HD, bool DECODE, int STAGES>
-__global__ void __launch_bounds__(160) attn_tma_kernel(const AttnParams P, const __grid_constant__ CUtensorMap kmap,
+__global__ void __launch_bounds__(160, 2) attn_tma_kernel(const AttnParams P, const __grid_constant__ CUtensorMap kmap,
                                                         const __grid_constant__ CUtensorMap vmap) {
     constexpr int BM = DECODE ? 16 : 64, BN = 64, CH = HD / 8;
     constexpr int NT = DECODE ? 2 : 8;
@@ -372,6 +372,9 @@ static int launch_tma(const AttnParams& P, const CUtensorMap& kmap, const CUtens
         cudaError_t e = cudaFuncSetAttribute(attn_tma_kernel<HD, DECODE, STAGES>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
+        // two blocks per SM need most of the SM's memory as shared memory: ask for the largest carve-out
+        cudaFuncSetAttribute(attn_tma_kernel<HD, DECODE, STAGES>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                             cudaSharedmemCarveoutMaxShared);
         configured = true;
     }
     attn_tma_kernel<HD, DECODE, STAGES><<<dim3(n_items, P.KV), 160, smem, st>>>(P, kmap, vmap);

@@ -175,7 +175,7 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float* __restric
                                      int RD, int pairing, int page, int num_pages, int* err) {
     const int n = blockIdx.x;
     const int half = HD / 2, rhalf = RD / 2;
-    const int per = blockDim.x / half;               // heads handled at once
+    const int per = blockDim.x / half;               // heads handled at once by one block; gridDim.y blocks share a token
     const int lane = threadIdx.x % half, sub = threadIdx.x / half;
     const int pos = positions[n];
     T* row = qkv + (size_t)n * (H + 2 * KV) * HD;
@@ -209,7 +209,7 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float* __restric
     } else {
         rot = false;
     }
-    for (int h = sub; h < H + 2 * KV; h += per) {
+    for (int h = sub + blockIdx.y * per; h < H + 2 * KV; h += per * gridDim.y) {
         T* p = row + (size_t)h * HD;
         float a = mb_load(p + e0), b = mb_load(p + e1);
         if (brow) { a += brow[(size_t)h * HD + e0]; b += brow[(size_t)h * HD + e1]; }
@@ -299,7 +299,11 @@ static int rope_kv_write_launch(void* qkv, const float* bias, const int* positio
     if (HD % 2 || RD % 2 || RD > HD || HD / 2 > 1024) return -2;
     int threads = 256;
     if (HD / 2 > threads) threads = ((HD / 2 + 31) / 32) * 32;
-    rope_kv_write_kernel<T><<<N, threads, 0, st>>>((T*)qkv, bias, positions, tok_seq, table, max_blocks, (T*)kpool,
+    const int per = threads / (HD / 2);
+    int split = (H + 2 * KV + per - 1) / per;       // blocks per token: enough to fill the GPU when tokens are few
+    if (split > 16) split = 16;
+    if (N >= 512) split = 1;
+    rope_kv_write_kernel<T><<<dim3(N, split), threads, 0, st>>>((T*)qkv, bias, positions, tok_seq, table, max_blocks, (T*)kpool,
                                                     (T*)vpool, freqs, H, KV, HD, RD, pairing, page, num_pages, err);
     MB_LAUNCH_CHECK();
     return 0;

@@ -212,14 +212,33 @@ __global__ void penalty_fill_kernel(int* __restrict__ cnt_row, unsigned char* __
     if (i >= n_prompt) atomicAdd(cnt_row + t, 1);
 }
 
-// first index of the maximum of each row (the greedy token without any other processing)
-__global__ void __launch_bounds__(SAMPLE_THREADS) argmax_kernel(const float* __restrict__ logits, int V, int* __restrict__ out) {
+// first index of the maximum of each row (the greedy token without any other processing), in two stages so that a few
+// rows still fill the GPU: blocks (chunk, row) reduce a chunk of the row each, then one block per row reduces the chunks
+#define ARGMAX_CHUNKS 32
+__global__ void __launch_bounds__(256) argmax_partial_kernel(const float* __restrict__ logits, int V,
+                                                              float* __restrict__ pval, int* __restrict__ pidx) {
     __shared__ ArgMax sh_a[32];
-    const float* lg = logits + (size_t)blockIdx.x * V;
+    const int row = blockIdx.y, chunk = blockIdx.x;
+    const int per = (V + ARGMAX_CHUNKS - 1) / ARGMAX_CHUNKS;
+    const int lo = chunk * per, hi = min(V, lo + per);
+    const float* lg = logits + (size_t)row * V;
     ArgMax best = {-INFINITY, 0x7FFFFFFF};
-    for (int v = threadIdx.x; v < V; v += blockDim.x) { ArgMax c = {lg[v], v}; best = better(best, c); }
+    for (int v = lo + threadIdx.x; v < hi; v += blockDim.x) { ArgMax c = {lg[v], v}; best = better(best, c); }
     best = block_argmax(best, sh_a);
-    if (threadIdx.x == 0) out[blockIdx.x] = best.i;
+    if (threadIdx.x == 0) { pval[row * ARGMAX_CHUNKS + chunk] = best.v; pidx[row * ARGMAX_CHUNKS + chunk] = best.i; }
+}
+
+__global__ void argmax_final_kernel(const float* __restrict__ pval, const int* __restrict__ pidx, int* __restrict__ out) {
+    const int row = blockIdx.x, lane = threadIdx.x;                    // 32 threads, one chunk each
+    ArgMax a = {pval[row * ARGMAX_CHUNKS + lane], pidx[row * ARGMAX_CHUNKS + lane]};
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        ArgMax b;
+        b.v = __shfl_xor_sync(0xffffffffu, a.v, o);
+        b.i = __shfl_xor_sync(0xffffffffu, a.i, o);
+        a = better(a, b);
+    }
+    if (lane == 0) out[row] = a.i;
 }
 
 #ifndef MB_SAMPLING_KERNELS_ONLY
@@ -239,9 +258,12 @@ MB_API int mb_penalty_fill(int* cnt_row, unsigned char* seen_row, const int* tok
     return 0;
 }
 
-MB_API int mb_argmax(const float* logits, int n_rows, int V, int* out, cudaStream_t st) {
+// scratch: n_rows * 32 floats and as many ints, given by the caller (pval, pidx)
+MB_API int mb_argmax(const float* logits, int n_rows, int V, float* pval, int* pidx, int* out, cudaStream_t st) {
     if (n_rows == 0) return 0;
-    argmax_kernel<<<n_rows, SAMPLE_THREADS, 0, st>>>(logits, V, out);
+    if (n_rows > 65535) return -2;
+    argmax_partial_kernel<<<dim3(ARGMAX_CHUNKS, n_rows), 256, 0, st>>>(logits, V, pval, pidx);
+    argmax_final_kernel<<<n_rows, 32, 0, st>>>(pval, pidx, out);
     MB_LAUNCH_CHECK();
     return 0;
 }

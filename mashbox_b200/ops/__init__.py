@@ -261,10 +261,21 @@ def sample(logits, work, params, cnt, seen, n_rows, out):
     _check(f(_p(logits), _p(work), _p(params), _p(cnt), _p(seen), n_rows, logits.shape[1], _p(out), _stream()), "sample")
 
 
+_argmax_scratch = {}
+
+
 def argmax(logits, out):
+    """out[r] = the lowest index of the maximum of row r"""
     _cuda(logits, out)
-    f = _fn("sampling", "mb_argmax", [c_void_p, c_int, c_int, c_void_p, c_void_p])
-    _check(f(_p(logits), logits.shape[0], logits.shape[1], _p(out), _stream()), "argmax")
+    n = logits.shape[0]
+    key = str(logits.device)
+    sc = _argmax_scratch.get(key)
+    if sc is None or sc[0].shape[0] < n * 32:
+        sc = (torch.empty(max(n, 64) * 32, dtype=torch.float32, device=logits.device),
+              torch.empty(max(n, 64) * 32, dtype=torch.int32, device=logits.device))
+        _argmax_scratch[key] = sc
+    f = _fn("sampling", "mb_argmax", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(f(_p(logits), n, logits.shape[1], _p(sc[0]), _p(sc[1]), _p(out), _stream()), "argmax")
 
 
 def penalty_fill(cnt_row, seen_row, tokens, n_prompt, n_total, V):
