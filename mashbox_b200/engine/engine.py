@@ -29,6 +29,7 @@ class Engine:
         self.sampler = Sampler(model.vocab, self.cfg.max_requests, self.runner.device)
         self.log = log
         self.counter = 0
+        self._prepared = None          # the next step, planned and laid out while the one before it ran
         self.stats = dict(steps=0, prompt_tokens=0, generated_tokens=0)
 
     @classmethod
@@ -60,6 +61,7 @@ class Engine:
         """reqs: list of dict(ids, max_new, samp=None) -> one row per request, in order.  A request that fails
         check() gets a row with finish "error" and the reason in .error, and changes nothing else."""
         from .scheduler import Request
+        self._prepared = None          # a prepared step does not know the new requests
         rows = []
         for q in reqs:
             why = self.check(q)
@@ -79,19 +81,37 @@ class Engine:
 
     def cancel(self, rows):
         for r in rows:
+            self._prepared = None
             self.scheduler.cancel(r)
 
-    def step(self):
-        """One scheduler step: plan, one batched model step, sample, bookkeeping.  -> requests that ended."""
+    PLACEHOLDER = -1        # stands for a token that is being sampled while the next step is prepared
+
+    def _prepare(self):
+        """Plans the next step and lays its arrays out on the host.  -> (plan, entries, ctx) or None"""
         plan = self.scheduler.plan()
         if not plan:
             if self.scheduler.busy():
                 raise RequestError("the scheduler has requests but nothing can run (the cache pool is too small)")
-            return []
+            return None
         entries = [(p.request.rid, p.request.tokens[p.start:p.start + p.count], [p.count - 1] if p.sample else [])
                    for p in plan]
+        return plan, entries, self.runner.prepare(entries)
+
+    def step(self):
+        """One scheduler step: one batched model step, sampling, bookkeeping.  -> requests that ended.
+
+        The host work of the NEXT step (planning, page bookkeeping, laying out its arrays) is done while the GPU runs
+        this one: the step is booked with a placeholder for every token being sampled, the next step is prepared from
+        that state, and when the sampled ids arrive they are patched into the requests and into the prepared arrays.
+        A sampled stop token is the one thing the placeholder cannot foresee: the request then ends as it should and
+        the prepared step is thrown away."""
         try:
-            logits = self.runner.step(entries)
+            prep = self._prepared if self._prepared is not None else self._prepare()
+            self._prepared = None
+            if prep is None:
+                return []
+            plan, entries, ctx = prep
+            logits = self.runner.launch(ctx, entries)
             picks = [p for p in plan if p.sample]
             rows = []
             for p in picks:
@@ -101,16 +121,42 @@ class Engine:
                     self.sampler.start_row(slot, r.prompt, r.generated)
                 r.needs_penalty_start = False
                 rows.append((r.sampling, len(r.generated), slot))
-            tokens = self.sampler.sample(logits, rows) if picks else []
-            self.runner.check()
+            pending = self.sampler.sample_async(logits, rows, self.runner.err)
+            # book the step with placeholders and prepare the next one while the GPU works
+            ended = self.scheduler.advance(plan, [self.PLACEHOLDER] * len(picks))
+            nxt = self._prepare() if self.scheduler.busy() else None
+            tokens = self.sampler.wait(pending)
         except BaseException:
+            self._prepared = None
             self._drop_live()
             raise
         now = time.perf_counter()
-        for p in picks:
-            if p.request.t_first is None:
-                p.request.t_first = now
-        ended = self.scheduler.advance(plan, tokens)
+        redo = False
+        for p, t in zip(picks, tokens):
+            r = p.request
+            if r.t_first is None:
+                r.t_first = now
+            if t in r.stop_ids:                 # the stop token is not emitted; the request ends here
+                r.generated.pop()
+                if r.finish is None:
+                    self.scheduler.finish(r, "stop")
+                    ended.append(r)
+                    redo = True                 # the prepared step still holds this request
+                else:
+                    r.finish = "stop"           # it had also reached max_new: the stop token wins, as in the reference
+                continue
+            r.generated[-1] = t
+        if nxt is not None and not redo:
+            nplan, nentries, nctx = nxt
+            at = 0
+            for p, e in zip(nplan, nentries):
+                r = p.request
+                last = len(r.prompt) + len(r.generated) - 1          # the place of the token sampled just now
+                if p.start <= last < p.start + p.count and e[1][last - p.start] == self.PLACEHOLDER:
+                    self.runner.patch_token(at + last - p.start, r.generated[-1])
+                    e[1][last - p.start] = r.generated[-1]
+                at += p.count
+            self._prepared = nxt
         for r in ended:
             r.t_end = now
         self.stats["steps"] += 1

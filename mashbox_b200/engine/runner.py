@@ -45,15 +45,29 @@ class ModelRunner:
         of the entries and of each `want`; None when nothing is wanted.  The tensor is valid until the next step."""
         if not entries:
             return None
-        ctx = self.begin(entries)
+        return self.launch(self.prepare(entries), entries)
+
+    def launch(self, ctx, entries):
+        """Sends a prepared step's arrays and the changed block-table entries to the device, runs the model (a captured
+        graph for decode-only steps) and commits the entries.  -> logits"""
+        self.inputs.upload()
+        self.cache.flush_tables()
         decode_only = self.use_graphs and ctx.N == ctx.S and ctx.n_out == ctx.S
         logits = self._run_graph(ctx) if decode_only else self.model.forward(ctx)
         self.commit(entries)
         return logits
 
     def begin(self, entries):
-        """Takes the pages the entries need, lays the step's integer arrays out, lets the mixers plan, sends the
-        arrays and the changed block-table entries to the device.  -> StepContext ready for model.forward"""
+        """prepare + upload: a StepContext ready for model.forward (tests of single parts use it)"""
+        ctx = self.prepare(entries)
+        self.inputs.upload()
+        self.cache.flush_tables()
+        return ctx
+
+    def prepare(self, entries):
+        """Takes the pages the entries need, lays the step's integer arrays out on the host and lets the mixers plan.
+        Nothing is sent to the device yet, so a step can be prepared while the step before it still runs, and token
+        ids that are not known yet can be patched in (patch_token) before launch().  -> StepContext"""
         cache = self.cache
         seen = set()
         need = [0] * len(cache.groups)
@@ -104,9 +118,11 @@ class ModelRunner:
         inp.add("seq_row", rows)
         inp.add("state_slot", ctx.state_slots)
         self.model.prepare(ctx)
-        inp.upload()
-        cache.flush_tables()
         return ctx
+
+    def patch_token(self, index, token):
+        """Sets token `index` of the prepared step (its place among the step's N tokens) before launch()."""
+        self.inputs.arrays["token_ids"][index] = token
 
     def commit(self, entries):
         """The step's tokens are in the cache: the requests grow (and windows give pages back)."""

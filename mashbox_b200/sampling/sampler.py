@@ -21,6 +21,7 @@ class Sampler:
         self.V, self.max_slots, self.device = int(vocab), int(max_slots), device
         self.cnt = self.seen = None
         self.work = None
+        self.ret = self.host = None
 
     def _penalty_state(self):
         if self.cnt is None:
@@ -36,25 +37,54 @@ class Sampler:
         toks = torch.tensor(list(prompt) + list(generated), dtype=torch.int32).to(self.device)
         kernels.penalty_fill(self.cnt[slot], self.seen[slot], toks, len(prompt), len(prompt) + len(generated), self.V)
 
-    def sample(self, logits, rows):
+    def sample(self, logits, rows, err=None):
         """logits (R, V) float32 on the device; rows: [(SamplingParams, token index, state slot or -1)], one per row of
         logits in order.  -> list of token ids (one device-to-host copy)."""
+        return self.wait(self.sample_async(logits, rows, err))
+
+    def sample_async(self, logits, rows, err=None):
+        """Launches the sampling kernels and starts the copy of the ids (and of the kernels' error word, when given)
+        to pinned host memory.  -> a handle for wait()."""
         n = len(rows)
         if n == 0:
-            return []
-        out = torch.empty(n, dtype=torch.int32, device=self.device)
+            return None
+        if self.ret is None or self.ret.shape[0] < n + 1:
+            cap = max(n, self.max_slots) + 1
+            self.ret = torch.empty(cap, dtype=torch.int32, device=self.device)
+            self.host = [torch.empty(cap, dtype=torch.int32).pin_memory() for _ in range(2)]
+            self.turn = 0
+        out = self.ret[:n]
         if all(p.plain_greedy for p, _, _ in rows):
             kernels.argmax(logits[:n], out)
-            return out.tolist()
-        packed = np.zeros(n, ROW)
-        for i, (p, step, slot) in enumerate(rows):
-            packed[i] = (p.temperature, p.top_p, p.min_p, p.repetition_penalty, p.frequency_penalty,
-                         p.presence_penalty, p.top_k, slot if p.penalised else -1, p.seed & 0xFFFFFFFF,
-                         (p.seed >> 32) & 0xFFFFFFFF, step, i)
-        if any(p.penalised for p, _, _ in rows):
-            self._penalty_state()
-        params = torch.from_numpy(packed.view(np.uint8).copy()).to(self.device)
-        if self.work is None or self.work.shape[0] < n:
-            self.work = torch.empty((max(n, self.max_slots), self.V), dtype=torch.float32, device=self.device)
-        kernels.sample(logits, self.work, params, self.cnt, self.seen, n, out)
-        return out.tolist()
+        else:
+            packed = np.zeros(n, ROW)
+            for i, (p, step, slot) in enumerate(rows):
+                packed[i] = (p.temperature, p.top_p, p.min_p, p.repetition_penalty, p.frequency_penalty,
+                             p.presence_penalty, p.top_k, slot if p.penalised else -1, p.seed & 0xFFFFFFFF,
+                             (p.seed >> 32) & 0xFFFFFFFF, step, i)
+            if any(p.penalised for p, _, _ in rows):
+                self._penalty_state()
+            params = torch.from_numpy(packed.view(np.uint8).copy()).to(self.device)
+            if self.work is None or self.work.shape[0] < n:
+                self.work = torch.empty((max(n, self.max_slots), self.V), dtype=torch.float32, device=self.device)
+            kernels.sample(logits, self.work, params, self.cnt, self.seen, n, out)
+        if err is not None:
+            self.ret[n:n + 1].copy_(err)
+        self.turn ^= 1
+        host = self.host[self.turn]
+        host[:n + 1].copy_(self.ret[:n + 1], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        return host, n, ev, err
+
+    def wait(self, pending):
+        """-> the token ids of sample_async (raises when a kernel of the step left an error code)"""
+        if pending is None:
+            return []
+        host, n, ev, err = pending
+        ev.synchronize()
+        vals = host[:n + 1].tolist()
+        if err is not None and vals[n]:
+            err.zero_()
+            raise kernels.KernelError("a kernel reported: " + kernels.DEVICE_ERRORS.get(vals[n], f"code {vals[n]}"))
+        return vals[:n]
