@@ -174,3 +174,25 @@ def test_command_line(tmp_path):
     assert s.returncode == 0 and len(s.stdout.strip().split(",")) == 6
     bad = subprocess.run(cmd[:5] + ["--prompt-ids", "5,999"], capture_output=True, text=True, env=env, timeout=600)
     assert bad.returncode == 2 and "token ids must be 0..255" in bad.stderr
+
+
+def test_command_line_with_a_tokenizer(tmp_path):
+    """--prompt TEXT: tokenizer.json of the folder turns text into ids and ids back into text"""
+    import shutil
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    folder = H.make_folder(tmp_path, "A", "float32")
+    words = {f"w{i}": i for i in range(256)}
+    tok = Tokenizer(models.WordLevel(vocab=words, unk_token="w0"))
+    tok.pre_tokenizer = pre_tokenizers.Whitespace()
+    tok.save(os.path.join(folder, "tokenizer.json"))
+    env = dict(os.environ, PYTHONPATH=ROOT)
+    cmd = [sys.executable, "-m", "mashbox_b200", "run", folder, "--prompt", "w5 w17 w3 w200", "--max-tokens", "5",
+           "--dtype", "float32"]
+    r = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    cfg, W = plain.read_model(folder)
+    want = plain.greedy(cfg, W, [5, 17, 3, 200], 5)
+    assert r.stdout.split() == [f"w{t}" for t in want]
+    os.remove(os.path.join(folder, "tokenizer.json"))
+    r = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=600)
+    assert r.returncode == 2 and "tokenizer.json" in r.stderr
