@@ -83,7 +83,7 @@ class Attention:
             return
         G, KV = self.H // self.KV, self.KV
         target = int(ctx.options.get("attention_target_blocks", 296))
-        max_splits = int(ctx.options.get("attention_max_splits", 16))
+        max_splits = int(ctx.options.get("attention_max_splits", 32))
         S = ctx.S
         decode_form = [ctx.q_len[s] * G <= DECODE_ROWS for s in range(S)]
         tiles = [1 if decode_form[s] else -(-ctx.q_len[s] * G // PREFILL_ROWS) for s in range(S)]
