@@ -25,8 +25,8 @@ class SwiGLU:
         import torch
         N = ctx.N
         a = ctx.ws.get("ffn_act", N, (self.F,), ctx.dtype)
-        if ctx.dtype == torch.bfloat16 and ctx.ops.skinny_supports(N, self.D):
-            ctx.ops.linear_swiglu(h, self.wgu, a)           # decode batches: both products and the gate in one kernel
+        if ctx.dtype == torch.bfloat16 and ctx.ops.fused_swiglu_supports(N, self.F, self.D):
+            ctx.ops.linear_swiglu(h, self.wgu, a)           # both products and the gate in one kernel
         else:
             gu = ctx.ws.get("gate_up", N, (2 * self.F,), ctx.dtype)
             ctx.ops.linear(h, self.wgu, out=gu)

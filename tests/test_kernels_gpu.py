@@ -419,3 +419,34 @@ def _weight_streaming_checks(K_, a, w, N, M, K):
         close(act, gt * torch.sigmoid(gt) * up, torch.bfloat16, "fused SwiGLU product")
     assert not K_.skinny_supports(17, 4096) and not K_.skinny_supports(4, 100)
     K_.check_error_word(K_.error_word(G.DEV))
+
+
+@pytest.mark.parametrize("N,M,K", [(128, 256, 64), (2048, 6144, 4096), (300, 1000, 200), (131, 504, 320), (513, 72, 4096)])
+def test_tcgen05_product(N, M, K):
+    """TMA + tcgen05.mma with the accumulator in tensor memory, against float64; plain, float32 out and fused SwiGLU"""
+    K_ = ops()
+    g = torch.Generator().manual_seed(15)
+    a = torch.randn(N, K, generator=g).bfloat16().to(G.DEV)
+    w = (torch.randn(M, K, generator=g) / K ** 0.5).bfloat16().to(G.DEV)
+    want = a.double() @ w.double().T
+    out = torch.full((N, M), float("nan"), device=G.DEV, dtype=torch.bfloat16)
+    K_.linear_tc5(a, w, out, "plain")
+    close(out, want, torch.bfloat16, "tcgen05 product")
+    assert float((out.double() - want).abs().max()) <= 2.0 ** -8 * float(want.abs().max()) + 1e-6       # one bf16 rounding
+    f32 = torch.full((N, M), float("nan"), device=G.DEV)
+    K_.linear_tc5(a, w, f32, "float")
+    close(f32, want, torch.float32, "tcgen05 product, float32 out")
+    F = (M // 2) // 8 * 8
+    act = torch.full((N, F), float("nan"), device=G.DEV, dtype=torch.bfloat16)
+    wgu = torch.cat([w[:F], w[M - F:]]).contiguous()
+    K_.linear_tc5(a, wgu, act, "swiglu")
+    gt = (a.double() @ wgu[:F].double().T).float().bfloat16().double()
+    up = (a.double() @ wgu[F:].double().T).float().bfloat16().double()
+    close(act, gt * torch.sigmoid(gt) * up, torch.bfloat16, "tcgen05 fused SwiGLU product")
+    # gate values far outside the exponential's range stay finite and right
+    big = torch.full((N, F), float("nan"), device=G.DEV, dtype=torch.bfloat16)
+    K_.linear_tc5(a, (wgu.float() * 80).bfloat16(), big, "swiglu")
+    assert torch.isfinite(big.float()).all()
+    K_.check_error_word(K_.error_word(G.DEV))
+    with pytest.raises(Exception, match="does not take these sizes"):
+        K_.linear_tc5(a[:, :K - 4].contiguous(), w[:, :K - 4].contiguous(), out, "plain")
