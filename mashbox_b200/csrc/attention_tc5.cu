@@ -1,0 +1,416 @@
+// Paged flash attention for prompt portions on the 5th-generation tensor cores (head size 128).
+//
+// One block works on 128 packed query rows -- (token, head-in-group) of one sequence and one kv head -- against the keys
+// up to the last row's position, 128 keys at a time:
+//   warp 0     producer: walks the block table and brings each K and V tile in with one cp.async.bulk.tensor.2d per
+//              page and 64-column half (128-byte swizzle), two stages;
+//   warp 1     one thread issues the products: S = Q K^T (tcgen05.mma, M = 128 rows, N = 128 keys, 8 k-steps over the
+//              head) into one of two score buffers in tensor memory, and O += P V (M = 128 rows, N = 128 head columns,
+//              8 k-steps over the keys; V is the MN-major operand, read as the TMA laid it out).  The score product of
+//              the next tile is issued before the softmax of the current one is done.
+//   warps 2-5  softmax: thread = row.  tcgen05.ld brings the row's 128 scores; maximum and sum need no shuffle; the
+//              probabilities are written as bf16 into shared memory in the swizzled K-major layout the next product
+//              reads.  The output accumulator stays in tensor memory over all tiles; a row rescales its own lane of
+//              it (tcgen05.ld / tcgen05.st) only when its running maximum moved.  At the end the row is normalised
+//              and written.
+// Softmax, scale and running sums are float32.  Waits on mbarriers are bounded; every role reaches the common exit,
+// where the tensor memory is given back.  Page sizes 8..128 (powers of two); other sizes go to the mma.sync kernels.
+#include <cuda.h>
+#include "attention_common.cuh"
+
+#define T5_WAIT_LIMIT (1 << 22)
+#define T5_BM 128
+#define T5_BN 128
+#define T5_HD 128
+#define T5_TILE (T5_BN * T5_HD * 2)            // bytes of one K or V tile (two 64-column halves of 16 KB)
+#define T5_HALF (128 * 128)                    // bytes of one half: 128 rows x 128 bytes
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* err) {
+    for (int it = 0; it < T5_WAIT_LIMIT; it++) {
+        uint32_t ok;
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    mb_set_error(err, MB_ERR_WAIT_TIMEOUT);
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
+                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+                 ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31};\n"
+        ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+          "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
+          "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
+          "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]), "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+
+// shared-memory matrix descriptor, 128-byte swizzle, version 1: start address, leading and stride byte offsets
+__device__ __forceinline__ uint64_t umma_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)((lbo >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+__global__ void __launch_bounds__(192, 1) attn_tc5_kernel(const AttnParams P, const __grid_constant__ CUtensorMap kmap,
+                                                           const __grid_constant__ CUtensorMap vmap) {
+    extern __shared__ unsigned char smem_unaligned[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~static_cast<uintptr_t>(1023));
+    // Q (32 KB) | P (32 KB) | 2 stages x (K tile 32 KB, V tile 32 KB) | barriers
+    const uint32_t q_s = smem_u32(smem), p_s = q_s + 2 * T5_HALF, kv_s = p_s + 2 * T5_HALF;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 4 * T5_HALF + 2 * 2 * T5_TILE);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+    const uint32_t kv_full0 = smem_u32(bars), kv_empty0 = kv_full0 + 16, s_full0 = kv_full0 + 32, p_full = kv_full0 + 48,
+                   pv_done = kv_full0 + 56, q_ready = kv_full0 + 64;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int4 item = P.items[blockIdx.x];
+    const int seq = item.x, m_tile = item.y;
+    const int kvh = blockIdx.y;
+    const int G = P.G, R = P.q_len[seq] * G, pos0 = P.pos0[seq], tok0 = P.q_start[seq];
+    const int row0 = m_tile * T5_BM;
+    if (row0 >= R) return;
+    const int row_last = min(R, row0 + T5_BM) - 1;
+    const int pos_min = pos0 + row0 / G, pos_max = pos0 + row_last / G;
+    const int hi = pos_max + 1;
+    const int lo = (P.window > 0 && pos_min - P.window + 1 > 0) ? pos_min - P.window + 1 : 0;
+    const int lo_al = (lo / T5_BN) * T5_BN;
+    const int T = (hi - lo_al + T5_BN - 1) / T5_BN;                 // key tiles of this block (at least one)
+    const int* tb = P.table + (size_t)P.seq_row[seq] * P.max_blocks;
+
+    if (tid == 0) {
+        for (int s = 0; s < 2; s++) { mbar_init(kv_full0 + 8 * s, 1); mbar_init(kv_empty0 + 8 * s, 1); mbar_init(s_full0 + 8 * s, 1); }
+        mbar_init(p_full, 128);
+        mbar_init(pv_done, 1);
+        mbar_init(q_ready, 128);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tm_s0 = tmem_base, tm_o = tmem_base + 256;       // scores: columns 0..127 and 128..255; output: 256..383
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- producer
+        if (lane == 0) {
+            const int shift = P.page_shift, page = P.page;
+            const int pages_per_tile = T5_BN >> shift;
+            for (int t = 0; t < T; t++) {
+                const int s = t & 1, round = t >> 1;
+                if (round > 0 && !mbar_wait(kv_empty0 + 8 * s, (round - 1) & 1, P.err)) break;
+                const uint32_t fb = kv_full0 + 8 * s;
+                mbar_expect_tx(fb, 2u * T5_TILE);
+                const int kb = lo_al + t * T5_BN;
+                const uint32_t kdst = kv_s + s * 2 * T5_TILE, vdst = kdst + T5_TILE;
+                for (int p = 0; p < pages_per_tile; p++) {
+                    const int key0 = kb + p * page, block = key0 >> shift;
+                    const bool live = key0 < hi && key0 + page > lo;
+                    int pg = (live && block < P.max_blocks) ? tb[block] : 0;
+                    if (pg < 0 || pg >= P.num_pages) {
+                        if (live) mb_set_error(P.err, pg < 0 ? MB_ERR_PAGE_MISSING : MB_ERR_PAGE_RANGE);
+                        pg = 0;                                      // any page: every key of it is masked
+                    }
+                    const int y = (pg * P.KV + kvh) * page;
+#pragma unroll
+                    for (int h = 0; h < 2; h++) {
+                        const uint32_t off = (uint32_t)(h * T5_HALF + p * page * 128);
+                        tma_load_2d(kdst + off, &kmap, h * 64, y, fb);
+                        tma_load_2d(vdst + off, &vmap, h * 64, y, fb);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- products
+        if (lane == 0) {
+            // D float, A and B bf16, M = 128, N = 128; the second descriptor has B MN-major (bit 16) for P V
+            constexpr uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+            constexpr uint32_t idesc_pv = idesc_qk | (1u << 16);
+            bool ok = mbar_wait(q_ready, 0, P.err);
+            auto scores = [&](int t) -> bool {                      // S[t % 2] = Q K_t^T
+                const int s = t & 1;
+                if (!mbar_wait(kv_full0 + 8 * s, (t >> 1) & 1, P.err)) return false;
+                tc_fence_after();
+                const uint32_t k_s = kv_s + s * 2 * T5_TILE;
+#pragma unroll
+                for (int ks = 0; ks < 8; ks++) {
+                    const uint32_t off = (ks >> 2) * T5_HALF + (ks & 3) * 32;
+                    umma_f16(tm_s0 + s * 128, umma_desc(q_s + off, 0, 1024), umma_desc(k_s + off, 0, 1024), idesc_qk, ks > 0);
+                }
+                umma_commit(s_full0 + 8 * s);
+                return true;
+            };
+            if (ok) ok = scores(0);
+            for (int t = 0; t < T && ok; t++) {
+                if (t + 1 < T) ok = scores(t + 1);
+                if (!ok || !mbar_wait(p_full, t & 1, P.err)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t v_s = kv_s + (t & 1) * 2 * T5_TILE + T5_TILE;
+#pragma unroll
+                for (int kk = 0; kk < 8; kk++) {                    // 16 keys per step
+                    const uint64_t pd = umma_desc(p_s + (kk >> 2) * T5_HALF + (kk & 3) * 32, 0, 1024);
+                    const uint64_t vd = umma_desc(v_s + kk * 2048, T5_HALF, 1024);
+                    umma_f16(tm_o, pd, vd, idesc_pv, (t > 0 || kk > 0) ? 1u : 0u);
+                }
+                umma_commit(kv_empty0 + 8 * (t & 1));
+                umma_commit(pv_done);
+            }
+        }
+    } else {
+        // ---------------------------------------------------------------- softmax: thread = row
+        const int q = warp & 3, r_loc = q * 32 + lane, r = row0 + r_loc;
+        const int st = tid - 64;                                    // 0..127 among the softmax threads
+        for (int cid = st; cid < T5_BM * 16; cid += 128) {
+            const int row = cid >> 4, c = cid & 15, rr = row0 + row;
+            const bf16* src = P.q;
+            int bytes = 0;
+            if (rr < R) {
+                src = P.q + (size_t)(tok0 + rr / G) * P.q_stride + (size_t)(kvh * G + rr % G) * T5_HD + c * 8;
+                bytes = 16;
+            }
+            const uint32_t dst = q_s + (c >> 3) * T5_HALF + (row >> 3) * 1024 + (row & 7) * 128 + (((c & 7) ^ (row & 7)) << 4);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes));
+        }
+        cp_async_commit();
+        cp_async_wait<0>();
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        mbar_arrive(q_ready);
+
+        int rpos = -1, rlo = 0;
+        if (r < R) {
+            rpos = pos0 + r / G;
+            rlo = (P.window > 0 && rpos - P.window + 1 > 0) ? rpos - P.window + 1 : 0;
+        }
+        const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+        const uint32_t prow = p_s + (r_loc >> 3) * 1024 + (r_loc & 7) * 128;
+        float m_run = -INFINITY, l_run = 0.0f;
+        bool ok = true;
+        for (int t = 0; t < T && ok; t++) {
+            if (!mbar_wait(s_full0 + 8 * (t & 1), (t >> 1) & 1, P.err)) { ok = false; break; }
+            tc_fence_after();
+            const int kb = lo_al + t * T5_BN;
+            const bool full_tile = kb + T5_BN - 1 <= pos_min && kb >= ((P.window > 0) ? pos_max - P.window + 1 : 0);
+            uint32_t sv[4][32];
+#pragma unroll
+            for (int c = 0; c < 4; c++) tmem_ld32(tm_s0 + (t & 1) * 128 + lane_addr + c * 32, sv[c]);
+            tmem_ld_wait();
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 4; c++)
+#pragma unroll
+                for (int i = 0; i < 32; i++) {
+                    float v = __uint_as_float(sv[c][i]) * P.scale_log2;
+                    if (!full_tile) {
+                        const int key = kb + c * 32 + i;
+                        if (!(key <= rpos && key >= rlo)) v = -INFINITY;
+                    }
+                    sv[c][i] = __float_as_uint(v);
+                    mx = fmaxf(mx, v);
+                }
+            const float m_new = fmaxf(m_run, mx);
+            const float muse = (m_new == -INFINITY) ? 0.0f : m_new;
+            const float corr = exp2f(m_run - muse);
+            // the product before this one must be done before P is written again or the output is touched
+            if (t > 0 && !mbar_wait(pv_done, (t - 1) & 1, P.err)) { ok = false; break; }
+            // a row whose running maximum moved rescales its lane of the output; the loads and stores are warp-wide
+            // instructions, so the whole warp goes when any of its rows has to (the others multiply by one)
+            if (t > 0 && __any_sync(0xffffffffu, m_new > m_run)) {
+                tc_fence_after();
+#pragma unroll 1
+                for (int c = 0; c < 4; c++) {
+                    uint32_t ov[32];
+                    tmem_ld32(tm_o + lane_addr + c * 32, ov);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; i++) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * corr);
+                    tmem_st32(tm_o + lane_addr + c * 32, ov);
+                }
+                tmem_st_wait();
+            }
+            m_run = m_new;
+            float sum = 0.0f;
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
+#pragma unroll
+                for (int j = 0; j < 4; j++) {                       // 8 keys = one 16-byte chunk
+                    float pr[8];
+#pragma unroll
+                    for (int e = 0; e < 8; e++) { pr[e] = exp2f(__uint_as_float(sv[c][j * 8 + e]) - muse); sum += pr[e]; }
+                    const int chunk = c * 4 + j;                    // 0..15 over the 128 keys
+                    const uint32_t dst = prow + (chunk >> 3) * T5_HALF + (((chunk & 7) ^ (r_loc & 7)) << 4);
+                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(dst), "r"(pack_bf16(pr[0], pr[1])),
+                                 "r"(pack_bf16(pr[2], pr[3])), "r"(pack_bf16(pr[4], pr[5])), "r"(pack_bf16(pr[6], pr[7])) : "memory");
+                }
+            }
+            l_run = l_run * corr + sum;
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            tc_fence_before();
+            mbar_arrive(p_full);
+        }
+        if (ok && mbar_wait(pv_done, (T - 1) & 1, P.err)) {
+            tc_fence_after();
+            const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
+            const bool live = r < R;                                // rows past the end take part in the loads only
+            bf16* dst = P.out + (live ? ((size_t)(tok0 + r / G) * P.H + (kvh * G + r % G)) * T5_HD : 0);
+#pragma unroll 1
+            for (int c = 0; c < 4; c++) {
+                uint32_t ov[32];
+                tmem_ld32(tm_o + lane_addr + c * 32, ov);
+                tmem_ld_wait();
+                if (live) {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 v;
+                        v.x = pack_bf16(__uint_as_float(ov[i]) * inv, __uint_as_float(ov[i + 1]) * inv);
+                        v.y = pack_bf16(__uint_as_float(ov[i + 2]) * inv, __uint_as_float(ov[i + 3]) * inv);
+                        v.z = pack_bf16(__uint_as_float(ov[i + 4]) * inv, __uint_as_float(ov[i + 5]) * inv);
+                        v.w = pack_bf16(__uint_as_float(ov[i + 6]) * inv, __uint_as_float(ov[i + 7]) * inv);
+                        *reinterpret_cast<uint4*>(dst + c * 32 + i) = v;
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiled encode_fn() {
+    static EncodeTiled fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiled>(p);
+    }
+    return fn;
+}
+
+struct MapKey { const void* ptr; long long rows; int hd, page; };
+struct MapEntry { MapKey key; CUtensorMap map; };
+#define MAP_CACHE 512
+static MapEntry map_cache[MAP_CACHE];
+static int map_count = 0;
+
+static int pool_map(const void* pool, long long rows, int HD, int page, CUtensorMap* out) {
+    for (int i = 0; i < map_count; i++) {
+        const MapKey& k = map_cache[i].key;
+        if (k.ptr == pool && k.rows == rows && k.hd == HD && k.page == page) { *out = map_cache[i].map; return 0; }
+    }
+    EncodeTiled enc = encode_fn();
+    if (!enc) return -6;
+    CUtensorMap m;
+    cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
+    cuuint32_t box[2] = {64u, (cuuint32_t)page};
+    cuuint32_t estr[2] = {1u, 1u};
+    CUresult r = enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(pool), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return -6;
+    if (map_count < MAP_CACHE) {
+        map_cache[map_count].key = MapKey{pool, rows, HD, page};
+        map_cache[map_count].map = m;
+        map_count++;
+    }
+    *out = m;
+    return 0;
+}
+
+MB_API int mb_attn_tc5_supports(int HD, int page) {
+    return HD == 128 && (page == 8 || page == 16 || page == 32 || page == 64 || page == 128);
+}
+
+// items: (sequence, tile of 128 packed rows, 0, 1) -- this kernel does not split the keys over blocks
+MB_API int mb_attn_tc5_bf16(const void* q, int q_stride, void* out, const void* kpool, const void* vpool,
+                            const void* items, int n_items, const int* q_start, const int* q_len, const int* pos0,
+                            const int* seq_row, const int* table, int max_blocks, int H, int KV, int HD, int page,
+                            int num_pages, int window, float scale, int* err, cudaStream_t st) {
+    if (n_items == 0) return 0;
+    if (!mb_attn_tc5_supports(HD, page) || KV < 1 || H % KV || KV > 65535) return -2;
+    AttnParams P;
+    P.q = (const bf16*)q; P.q_stride = q_stride; P.out = (bf16*)out;
+    P.kpool = (const bf16*)kpool; P.vpool = (const bf16*)vpool;
+    P.items = (const int4*)items;
+    P.q_start = q_start; P.q_len = q_len; P.pos0 = pos0; P.part_base = nullptr; P.seq_row = seq_row;
+    P.table = table; P.max_blocks = max_blocks;
+    P.part_o = nullptr; P.part_ml = nullptr; P.max_splits = 1;
+    P.H = H; P.KV = KV; P.G = H / KV; P.page = page; P.num_pages = num_pages; P.window = window;
+    P.page_shift = -1;
+    for (int sft = 0; sft < 31; sft++) if ((1 << sft) == page) P.page_shift = sft;
+    P.scale_log2 = scale * 1.4426950408889634f;
+    P.err = err;
+    CUtensorMap kmap, vmap;
+    const long long rows = (long long)num_pages * KV * page;
+    int rc = pool_map(kpool, rows, HD, page, &kmap);
+    if (rc) return rc;
+    rc = pool_map(vpool, rows, HD, page, &vmap);
+    if (rc) return rc;
+    const size_t smem = 1024 + 4 * T5_HALF + 2 * 2 * T5_TILE + 10 * 8 + 16;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    attn_tc5_kernel<<<dim3(n_items, KV), 192, smem, st>>>(P, kmap, vmap);
+    MB_LAUNCH_CHECK();
+    return 0;
+}

@@ -31,6 +31,7 @@ LIBRARIES = {            # library name -> (source file, extra link flags)
     "attention_simple": ("attention_simple.cu", []),
     "attention_mma": ("attention_mma.cu", []),
     "attention_tma": ("attention_tma.cu", []),
+    "attention_tc5": ("attention_tc5.cu", []),
     "sampling": ("sampling.cu", []),
     "sampling_noalloc": ("sampling_noalloc.cu", []),
 }

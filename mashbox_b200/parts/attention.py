@@ -69,6 +69,11 @@ class Attention:
         return ctx.dtype == torch.bfloat16 and ctx.ops.attention_mma_supports(self.HD) and not ctx.options.get(
             "plain_attention", False)
 
+    def uses_tc5(self, ctx):
+        """prompt-form tiles go to the tcgen05 kernel (128 packed rows per block, no splits) when it takes the sizes"""
+        return (ctx.options.get("attention_prefill_kernel", "tc5") == "tc5"
+                and ctx.ops.attention_tc5_supports(self.HD, ctx.cache.page_size))
+
     def plan_key(self):
         return ("attention", self.H // self.KV, self.KV, self.window)
 
@@ -85,8 +90,10 @@ class Attention:
         target = int(ctx.options.get("attention_target_blocks", 296))
         max_splits = int(ctx.options.get("attention_max_splits", 32))
         S = ctx.S
+        tc5 = self.uses_tc5(ctx)
+        pre_rows = 128 if tc5 else PREFILL_ROWS
         decode_form = [ctx.q_len[s] * G <= DECODE_ROWS for s in range(S)]
-        tiles = [1 if decode_form[s] else -(-ctx.q_len[s] * G // PREFILL_ROWS) for s in range(S)]
+        tiles = [1 if decode_form[s] else -(-ctx.q_len[s] * G // pre_rows) for s in range(S)]
         # the two forms are two launches: each is cut into splits by its own number of blocks
         base = {f: max(1, sum(t for t, d in zip(tiles, decode_form) if d == f) * KV) for f in (True, False)}
         dec, pre, part_base, part_tok = [], [], [-1] * S, []
@@ -95,7 +102,7 @@ class Attention:
             lo = max(0, ctx.pos0[s] - self.window + 1) if self.window else 0
             kv_tiles = -(-(hi - lo // KEY_TILE * KEY_TILE) // KEY_TILE)
             ns = 1
-            if ctx.q_len[s] <= DECODE_ROWS and base[decode_form[s]] < target:
+            if ctx.q_len[s] <= DECODE_ROWS and base[decode_form[s]] < target and (decode_form[s] or not tc5):
                 ns = max(1, min(max_splits, -(-target // base[decode_form[s]]), kv_tiles // 2))
                 ns = 1 << (ns.bit_length() - 1)                    # a power of two: few distinct work-list shapes
             if ns > 1:
@@ -105,7 +112,7 @@ class Attention:
             dst = dec if decode_form[s] else pre
             for m in range(tiles[s]):
                 for sp in range(ns):
-                    dst.append((-(ctx.pos0[s] + (m + 1) * PREFILL_ROWS // G), s, m, sp, ns))
+                    dst.append((-(ctx.pos0[s] + (m + 1) * pre_rows // G), s, m, sp, ns))
         pre.sort()                                                  # the tiles with the most keys first
         name = "attn%d_" % len([k for k in ctx.memo if k[0] == "attention"])
         flat = lambda items: np.asarray([i[1:] for i in items], np.int32).reshape(-1)
@@ -114,7 +121,7 @@ class Attention:
         ctx.inputs.add(name + "part_base", np.asarray(part_base, np.int32))
         ctx.inputs.add(name + "part_tok", np.asarray(part_tok, np.int32))
         ctx.memo[key] = dict(name=name, n_dec=len(dec), n_pre=len(pre), n_part=len(part_tok) // 2,
-                             max_splits=max_splits)
+                             max_splits=max_splits, tc5=tc5)
 
     # ------------------------------------------------------------------------------------------ forward
     def forward(self, ctx, h, run):
@@ -150,7 +157,12 @@ class Attention:
                 part_ml = ctx.ws.get("attn_part_ml", n_part * H * ms, (2,), torch.float32, reserve=0)
             kind = ctx.options.get("attention_kernel", "tma")
             flash = ops.attention_tma if kind == "tma" and ops.attention_tma_supports(HD, page) else ops.attention_mma
-            for form, n_items, decode in ((nm + "pre", plan["n_pre"], False), (nm + "dec", plan["n_dec"], True)):
+            if plan["tc5"] and plan["n_pre"]:
+                ops.attention_tc5(qkv, width, out, kpool, vpool, ctx.dev(nm + "pre"), plan["n_pre"], ctx.dev("q_start"),
+                                  ctx.dev("q_len"), ctx.dev("pos0"), ctx.dev("seq_row"), table, H, KV, HD, page, pages,
+                                  self.window, self.scale, ctx.err)
+            for form, n_items, decode in ((nm + "pre", 0 if plan["tc5"] else plan["n_pre"], False),
+                                          (nm + "dec", plan["n_dec"], True)):
                 if n_items:
                     flash(qkv, width, out, kpool, vpool, ctx.dev(form), n_items, decode, ctx.dev("q_start"),
                           ctx.dev("q_len"), ctx.dev("pos0"), ctx.dev(nm + "part_base"), ctx.dev("seq_row"),

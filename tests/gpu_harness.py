@@ -79,7 +79,7 @@ class PagedSequences:
         return torch.cat(out)
 
 
-def mma_items(seqs, G, target_splits=1, decode_rows=16, prefill_rows=64):
+def mma_items(seqs, G, target_splits=1, decode_rows=16, prefill_rows=64, split_prefill=True):
     """work lists of the tensor-core kernel: every sequence with at most decode_rows packed rows goes to the decode
     form, the others to the prompt form; sequences of at most 16 tokens are cut into target_splits splits"""
     dec, pre, part_base, part_tok = [], [], [], []
@@ -88,7 +88,7 @@ def mma_items(seqs, G, target_splits=1, decode_rows=16, prefill_rows=64):
         rows = ql * G
         decode = rows <= decode_rows
         tiles = 1 if decode else -(-rows // prefill_rows)
-        ns = target_splits if ql <= 16 else 1
+        ns = target_splits if ql <= 16 and (decode or split_prefill) else 1
         if ns > 1:
             part_base.append(len(part_tok) // 2)
             for t in range(ql):

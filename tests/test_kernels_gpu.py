@@ -217,16 +217,22 @@ MMA_CASES = [  # HD, H, KV, page, window, splits
 
 def run_mma(seqs, window, splits, kind="mma"):
     K = ops()
-    flash = K.attention_tma if kind == "tma" else K.attention_mma
+    flash = K.attention_mma if kind == "mma" else K.attention_tma
     H, KV, HD, page = seqs.H, seqs.KV, seqs.HD, seqs.page
     Gq = H // KV
-    dec, pre, part_base, part_tok = G.mma_items(seqs, Gq, splits)
+    dec, pre, part_base, part_tok = G.mma_items(seqs, Gq, splits, prefill_rows=128 if kind == "tc5" else 64,
+                                                split_prefill=kind != "tc5")
     out = torch.full((seqs.N, H * HD), float("nan"), device=G.DEV, dtype=torch.bfloat16)
     err = K.new_error_word(G.DEV)
     n_part = len(part_tok) // 2
     ms = max(splits, 1)
     part_o = torch.full((max(1, n_part) * H * ms, HD), float("nan"), device=G.DEV)
     part_ml = torch.full((max(1, n_part) * H * ms, 2), float("nan"), device=G.DEV)
+    if kind == "tc5" and pre:        # prompt-form tiles of 128 rows on tcgen05; decode-form items stay on the TMA kernel
+        K.attention_tc5(seqs.q_dev, H * HD, out, seqs.kpool, seqs.vpool, G.i32(np.asarray(pre).reshape(-1)), len(pre),
+                        seqs.q_start, seqs.q_len, seqs.pos0, seqs.seq_row, seqs.table, H, KV, HD, page, seqs.num_pages,
+                        window, HD ** -0.5, err)
+        pre = []
     for items, decode in ((pre, False), (dec, True)):
         if items:
             flash(seqs.q_dev, H * HD, out, seqs.kpool, seqs.vpool, G.i32(np.asarray(items).reshape(-1)),
@@ -238,7 +244,7 @@ def run_mma(seqs, window, splits, kind="mma"):
     return out
 
 
-@pytest.mark.parametrize("kind", ["mma", "tma"])
+@pytest.mark.parametrize("kind", ["mma", "tma", "tc5"])
 @pytest.mark.parametrize("HD,H,KV,page,window,splits", MMA_CASES)
 def test_attention_tensor_core_kernel(HD, H, KV, page, window, splits, kind):
     """prompt portions (one starting at position 0, one in the middle of a long context), single decode tokens with
@@ -248,6 +254,8 @@ def test_attention_tensor_core_kernel(HD, H, KV, page, window, splits, kind):
     far = 5 if window is None else 900 - window
     dominant_key(seqs, 0, far)
     seqs.round().build()
+    if kind == "tc5" and not ops().attention_tc5_supports(HD, page):
+        pytest.skip("the tcgen05 kernel takes head size 128 only")
     if kind == "tma" and not ops().attention_tma_supports(HD, page):
         with pytest.raises(Exception, match="does not take these sizes"):
             run_mma(seqs, window, splits, kind)
@@ -258,10 +266,10 @@ def test_attention_tensor_core_kernel(HD, H, KV, page, window, splits, kind):
     assert float((out[0].double().cpu() - want).abs().max()) < 0.05 * float(want.abs().max()) + 1e-2
 
 
-@pytest.mark.parametrize("kind", ["mma", "tma"])
+@pytest.mark.parametrize("kind,HD", [("mma", 64), ("tma", 64), ("tma", 128), ("tc5", 128)])
 @pytest.mark.parametrize("splits", [1, 4])
-def test_attention_tensor_core_kernel_window_edge(splits, kind):
-    H, KV, HD, page, window = 8, 2, 64, 16, 130
+def test_attention_tensor_core_kernel_window_edge(splits, kind, HD):
+    H, KV, page, window = 8, 2, 16, 130
     seqs = G.PagedSequences([700, 700], [1, 40], H, KV, HD, page, torch.bfloat16, seed=10)
     dominant_key(seqs, 0, 700 - window - 1)                           # one position too old: must not count
     dominant_key(seqs, 1, 700 - window)                               # the first key of the last query's window
