@@ -81,6 +81,24 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 
+// Build with -DT5_TRACE to record, for the first unit of block 0, the SM clock at the hand-over points of the three roles
+// (a debugging aid: the array is read back with mb_attn_tc5_trace).
+#ifdef T5_TRACE
+__device__ long long t5_trace[3 * 4096];
+__device__ int t5_trace_n;
+#define T5_MARK(ev, t) do { if (blockIdx.x == 0 && first_unit && (threadIdx.x & 31) == 0) { int i__ = atomicAdd(&t5_trace_n, 1); if (i__ < 4096) { \
+    t5_trace[3 * i__] = (ev); t5_trace[3 * i__ + 1] = (t); t5_trace[3 * i__ + 2] = clock64(); } } } while (0)
+#else
+#define T5_MARK(ev, t) do { } while (0)
+#endif
+
+// 2^x with the special-function unit (ex2.approx.ftz: 2 ulp; -inf gives 0)
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // shared-memory matrix descriptor, 128-byte swizzle, version 1: start address, leading and stride byte offsets
 __device__ __forceinline__ uint64_t umma_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
     uint64_t d = 0;
@@ -93,24 +111,40 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t addr, uint32_t lbo, uint3
 }
 
 __global__ void __launch_bounds__(192, 1) attn_tc5_kernel(const AttnParams P, const __grid_constant__ CUtensorMap kmap,
-                                                           const __grid_constant__ CUtensorMap vmap) {
+                                                           const __grid_constant__ CUtensorMap vmap, int n_units,
+                                                           int* __restrict__ counter) {
     extern __shared__ unsigned char smem_unaligned[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(
         (reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~static_cast<uintptr_t>(1023));
-    // Q (32 KB) | P (32 KB) | 2 stages x (K tile 32 KB, V tile 32 KB) | barriers
-    const uint32_t q_s = smem_u32(smem), p_s = q_s + 2 * T5_HALF, kv_s = p_s + 2 * T5_HALF;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 4 * T5_HALF + 2 * 2 * T5_TILE);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
-    const uint32_t kv_full0 = smem_u32(bars), kv_empty0 = kv_full0 + 16, s_full0 = kv_full0 + 32, p_full = kv_full0 + 48,
-                   pv_done = kv_full0 + 56, q_ready = kv_full0 + 64;
+    // Q (32 KB) | 2 x P (32 KB) | 2 stages x (K tile 32 KB, V tile 32 KB) | barriers
+    const uint32_t q_s = smem_u32(smem), p_s0 = q_s + 2 * T5_HALF, kv_s = p_s0 + 4 * T5_HALF;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * T5_HALF + 2 * 2 * T5_TILE);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+    int* unit_slot = reinterpret_cast<int*>(tmem_slot + 1);
+    const uint32_t k_full0 = smem_u32(bars), k_empty0 = k_full0 + 16, v_full0 = k_full0 + 32, v_empty0 = k_full0 + 48,
+                   s_full0 = k_full0 + 64, p_full0 = k_full0 + 80, pv_done0 = k_full0 + 96, q_ready = k_full0 + 112;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int4 item = P.items[blockIdx.x];
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    // Work units (item, kv head) are handed out by a counter in global memory, heaviest first, so blocks stay busy until
+    // the list is empty whatever the mix of short and long rows.
+    bool first_unit = true;
+    for (;; first_unit = false) {
+    tc_fence_before();
+    __syncthreads();                                                  // the unit before is finished by every role
+    if (tid == 0) *unit_slot = atomicAdd(counter, 1);
+    __syncthreads();
+    const int unit = *unit_slot;
+    if (unit >= n_units) break;
+    const int4 item = P.items[unit / P.KV];
     const int seq = item.x, m_tile = item.y;
-    const int kvh = blockIdx.y;
+    const int kvh = unit % P.KV;
     const int G = P.G, R = P.q_len[seq] * G, pos0 = P.pos0[seq], tok0 = P.q_start[seq];
     const int row0 = m_tile * T5_BM;
-    if (row0 >= R) return;
+    if (row0 >= R) continue;
     const int row_last = min(R, row0 + T5_BM) - 1;
     const int pos_min = pos0 + row0 / G, pos_max = pos0 + row_last / G;
     const int hi = pos_max + 1;
@@ -120,16 +154,16 @@ __global__ void __launch_bounds__(192, 1) attn_tc5_kernel(const AttnParams P, co
     const int* tb = P.table + (size_t)P.seq_row[seq] * P.max_blocks;
 
     if (tid == 0) {
-        for (int s = 0; s < 2; s++) { mbar_init(kv_full0 + 8 * s, 1); mbar_init(kv_empty0 + 8 * s, 1); mbar_init(s_full0 + 8 * s, 1); }
-        mbar_init(p_full, 128);
-        mbar_init(pv_done, 1);
+        if (!first_unit)                                             // the barriers of the unit before are retired first
+            for (int b = 0; b < 15; b++) asm volatile("mbarrier.inval.shared::cta.b64 [%0];\n" ::"r"(k_full0 + 8 * b) : "memory");
+        for (int s = 0; s < 2; s++) {
+            mbar_init(k_full0 + 8 * s, 1); mbar_init(k_empty0 + 8 * s, 1); mbar_init(v_full0 + 8 * s, 1);
+            mbar_init(v_empty0 + 8 * s, 1); mbar_init(s_full0 + 8 * s, 1);
+            mbar_init(p_full0 + 8 * s, 128); mbar_init(pv_done0 + 8 * s, 1);
+        }
         mbar_init(q_ready, 128);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-    }
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
     tc_fence_before();
     __syncthreads();
@@ -139,32 +173,47 @@ __global__ void __launch_bounds__(192, 1) attn_tc5_kernel(const AttnParams P, co
 
     if (warp == 0) {
         // ---------------------------------------------------------------- producer
-        if (lane == 0) {
+        // Every copy of a tile is issued by a lane of its own: lane = (page of the tile, 64-column half).  One thread
+        // issuing them one after the other took 3,000 to 4,000 cycles per 32 KB tile and was what the whole block
+        // waited for.  The lane's page id is read from the block table one tile ahead.
+        {
             const int shift = P.page_shift, page = P.page;
-            const int pages_per_tile = T5_BN >> shift;
-            for (int t = 0; t < T; t++) {
+            const int boxes = (T5_BN >> shift) * 2;                  // 2 .. 32
+            const int p = lane >> 1, h = lane & 1;
+            auto page_of = [&](int t) -> int {
+                const int key0 = lo_al + t * T5_BN + p * page, block = key0 >> shift;
+                const bool live = lane < boxes && key0 < hi && key0 + page > lo && block < P.max_blocks;
+                return live ? __ldg(tb + block) : 0;
+            };
+            // K of tile t+1 goes out before V of tile t: the key stage is free as soon as the score product that read it
+            // is done, the value stage only after the output product, one tile later
+            auto load = [&](int t, bool keys, int pg) -> bool {
                 const int s = t & 1, round = t >> 1;
-                if (round > 0 && !mbar_wait(kv_empty0 + 8 * s, (round - 1) & 1, P.err)) break;
-                const uint32_t fb = kv_full0 + 8 * s;
-                mbar_expect_tx(fb, 2u * T5_TILE);
-                const int kb = lo_al + t * T5_BN;
-                const uint32_t kdst = kv_s + s * 2 * T5_TILE, vdst = kdst + T5_TILE;
-                for (int p = 0; p < pages_per_tile; p++) {
-                    const int key0 = kb + p * page, block = key0 >> shift;
-                    const bool live = key0 < hi && key0 + page > lo;
-                    int pg = (live && block < P.max_blocks) ? tb[block] : 0;
+                const uint32_t empty = (keys ? k_empty0 : v_empty0) + 8 * s, fb = (keys ? k_full0 : v_full0) + 8 * s;
+                bool ok = round == 0 || mbar_wait(empty, (round - 1) & 1, P.err);
+                if (!__all_sync(0xffffffffu, ok)) return false;
+                T5_MARK(keys ? 10 : 12, t);
+                if (lane == 0) mbar_expect_tx(fb, T5_TILE);
+                __syncwarp();
+                if (lane < boxes) {
+                    const int key0 = lo_al + t * T5_BN + p * page;
                     if (pg < 0 || pg >= P.num_pages) {
-                        if (live) mb_set_error(P.err, pg < 0 ? MB_ERR_PAGE_MISSING : MB_ERR_PAGE_RANGE);
+                        if (key0 < hi && key0 + page > lo) mb_set_error(P.err, pg < 0 ? MB_ERR_PAGE_MISSING : MB_ERR_PAGE_RANGE);
                         pg = 0;                                      // any page: every key of it is masked
                     }
-                    const int y = (pg * P.KV + kvh) * page;
-#pragma unroll
-                    for (int h = 0; h < 2; h++) {
-                        const uint32_t off = (uint32_t)(h * T5_HALF + p * page * 128);
-                        tma_load_2d(kdst + off, &kmap, h * 64, y, fb);
-                        tma_load_2d(vdst + off, &vmap, h * 64, y, fb);
-                    }
+                    const uint32_t dst = kv_s + s * 2 * T5_TILE + (keys ? 0 : T5_TILE) + h * T5_HALF + p * page * 128;
+                    tma_load_2d(dst, keys ? &kmap : &vmap, h * 64, (pg * P.KV + kvh) * page, fb);
                 }
+                T5_MARK(keys ? 11 : 13, t);
+                return true;
+            };
+            int pg_cur = page_of(0);
+            bool ok = load(0, true, pg_cur);
+            for (int t = 0; t < T && ok; t++) {
+                int pg_next = 0;
+                if (t + 1 < T) { pg_next = page_of(t + 1); ok = load(t + 1, true, pg_next); }
+                if (ok) ok = load(t, false, pg_cur);
+                pg_cur = pg_next;
             }
         }
     } else if (warp == 1) {
@@ -176,7 +225,9 @@ __global__ void __launch_bounds__(192, 1) attn_tc5_kernel(const AttnParams P, co
             bool ok = mbar_wait(q_ready, 0, P.err);
             auto scores = [&](int t) -> bool {                      // S[t % 2] = Q K_t^T
                 const int s = t & 1;
-                if (!mbar_wait(kv_full0 + 8 * s, (t >> 1) & 1, P.err)) return false;
+                T5_MARK(20, t);
+                if (!mbar_wait(k_full0 + 8 * s, (t >> 1) & 1, P.err)) return false;
+                T5_MARK(21, t);
                 tc_fence_after();
                 const uint32_t k_s = kv_s + s * 2 * T5_TILE;
 #pragma unroll
@@ -184,23 +235,30 @@ __global__ void __launch_bounds__(192, 1) attn_tc5_kernel(const AttnParams P, co
                     const uint32_t off = (ks >> 2) * T5_HALF + (ks & 3) * 32;
                     umma_f16(tm_s0 + s * 128, umma_desc(q_s + off, 0, 1024), umma_desc(k_s + off, 0, 1024), idesc_qk, ks > 0);
                 }
+                umma_commit(k_empty0 + 8 * s);                      // the key stage is free once these products are done
                 umma_commit(s_full0 + 8 * s);
+                T5_MARK(22, t);
                 return true;
             };
             if (ok) ok = scores(0);
             for (int t = 0; t < T && ok; t++) {
                 if (t + 1 < T) ok = scores(t + 1);
-                if (!ok || !mbar_wait(p_full, t & 1, P.err)) { ok = false; break; }
+                T5_MARK(23, t);
+                if (!ok || !mbar_wait(p_full0 + 8 * (t & 1), (t >> 1) & 1, P.err)) { ok = false; break; }
+                T5_MARK(24, t);
+                if (!mbar_wait(v_full0 + 8 * (t & 1), (t >> 1) & 1, P.err)) { ok = false; break; }
+                T5_MARK(25, t);
                 tc_fence_after();
-                const uint32_t v_s = kv_s + (t & 1) * 2 * T5_TILE + T5_TILE;
+                const uint32_t v_s = kv_s + (t & 1) * 2 * T5_TILE + T5_TILE, p_s = p_s0 + (t & 1) * 2 * T5_HALF;
 #pragma unroll
                 for (int kk = 0; kk < 8; kk++) {                    // 16 keys per step
                     const uint64_t pd = umma_desc(p_s + (kk >> 2) * T5_HALF + (kk & 3) * 32, 0, 1024);
                     const uint64_t vd = umma_desc(v_s + kk * 2048, T5_HALF, 1024);
                     umma_f16(tm_o, pd, vd, idesc_pv, (t > 0 || kk > 0) ? 1u : 0u);
                 }
-                umma_commit(kv_empty0 + 8 * (t & 1));
-                umma_commit(pv_done);
+                umma_commit(v_empty0 + 8 * (t & 1));
+                umma_commit(pv_done0 + 8 * (t & 1));
+                T5_MARK(26, t);
             }
         }
     } else {
@@ -229,39 +287,62 @@ __global__ void __launch_bounds__(192, 1) attn_tc5_kernel(const AttnParams P, co
             rlo = (P.window > 0 && rpos - P.window + 1 > 0) ? rpos - P.window + 1 : 0;
         }
         const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
-        const uint32_t prow = p_s + (r_loc >> 3) * 1024 + (r_loc & 7) * 128;
+        const uint32_t prow0 = p_s0 + (r_loc >> 3) * 1024 + (r_loc & 7) * 128;
         float m_run = -INFINITY, l_run = 0.0f;
         bool ok = true;
         for (int t = 0; t < T && ok; t++) {
+            if (st == 0) T5_MARK(30, t);
             if (!mbar_wait(s_full0 + 8 * (t & 1), (t >> 1) & 1, P.err)) { ok = false; break; }
+            if (st == 0) T5_MARK(31, t);
             tc_fence_after();
             const int kb = lo_al + t * T5_BN;
             const bool full_tile = kb + T5_BN - 1 <= pos_min && kb >= ((P.window > 0) ? pos_max - P.window + 1 : 0);
+            // the row's 128 scores come from tensor memory with four loads and ONE wait (a load and its wait are a round
+            // trip of several hundred cycles) and stay in registers for both passes
+            const uint32_t s_addr = tm_s0 + (t & 1) * 128 + lane_addr;
             uint32_t sv[4][32];
 #pragma unroll
-            for (int c = 0; c < 4; c++) tmem_ld32(tm_s0 + (t & 1) * 128 + lane_addr + c * 32, sv[c]);
+            for (int c = 0; c < 4; c++) tmem_ld32(s_addr + c * 32, sv[c]);
             tmem_ld_wait();
-            float mx = -INFINITY;
+            if (st == 0) T5_MARK(32, t);
+            // eight running maxima (and eight partial sums below): one chain of 128 dependent operations would cost
+            // its latency 128 times over
+            float mxs[8];
 #pragma unroll
-            for (int c = 0; c < 4; c++)
+            for (int k = 0; k < 8; k++) mxs[k] = -INFINITY;
+            if (full_tile) {
 #pragma unroll
-                for (int i = 0; i < 32; i++) {
-                    float v = __uint_as_float(sv[c][i]) * P.scale_log2;
-                    if (!full_tile) {
+                for (int c = 0; c < 4; c++)
+#pragma unroll
+                    for (int i = 0; i < 32; i++) mxs[i & 7] = fmaxf(mxs[i & 7], __uint_as_float(sv[c][i]));
+            } else {
+                // masked keys become -inf once, here; 2^(-inf) = 0 does the rest
+#pragma unroll
+                for (int c = 0; c < 4; c++)
+#pragma unroll
+                    for (int i = 0; i < 32; i++) {
                         const int key = kb + c * 32 + i;
-                        if (!(key <= rpos && key >= rlo)) v = -INFINITY;
+                        if (!(key <= rpos && key >= rlo)) sv[c][i] = 0xff800000u;
+                        mxs[i & 7] = fmaxf(mxs[i & 7], __uint_as_float(sv[c][i]));
                     }
-                    sv[c][i] = __float_as_uint(v);
-                    mx = fmaxf(mx, v);
-                }
-            const float m_new = fmaxf(m_run, mx);
+            }
+            float mx = fmaxf(fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3])), fmaxf(fmaxf(mxs[4], mxs[5]), fmaxf(mxs[6], mxs[7])));
+            mx *= P.scale_log2;                                       // the scale is positive: max(scale * s) = scale * max(s)
+            // The reference point of the exponentials follows the running maximum lazily: it moves only when the maximum
+            // has grown by more than 8 (a factor of 256), so probabilities stay below 256 and the output accumulator
+            // is rescaled a few times per row instead of at almost every tile.  The result is the same: the sums and
+            // the output use one reference point at any time and the final division cancels it.
+            const float m_new = (m_run == -INFINITY || mx > m_run + 8.0f) ? fmaxf(m_run, mx) : m_run;
             const float muse = (m_new == -INFINITY) ? 0.0f : m_new;
-            const float corr = exp2f(m_run - muse);
-            // the product before this one must be done before P is written again or the output is touched
-            if (t > 0 && !mbar_wait(pv_done, (t - 1) & 1, P.err)) { ok = false; break; }
+            const float corr = fast_exp2(m_run - muse);
+            // this tile's P buffer was read by the output product two tiles ago
+            if (t > 1 && !mbar_wait(pv_done0 + 8 * (t & 1), ((t - 2) >> 1) & 1, P.err)) { ok = false; break; }
+            // the output may be touched only when the product before this one is done
+            const bool rescale = t > 0 && __any_sync(0xffffffffu, m_new != m_run);
+            if (rescale && !mbar_wait(pv_done0 + 8 * ((t - 1) & 1), ((t - 1) >> 1) & 1, P.err)) { ok = false; break; }
             // a row whose running maximum moved rescales its lane of the output; the loads and stores are warp-wide
             // instructions, so the whole warp goes when any of its rows has to (the others multiply by one)
-            if (t > 0 && __any_sync(0xffffffffu, m_new > m_run)) {
+            if (rescale) {
                 tc_fence_after();
 #pragma unroll 1
                 for (int c = 0; c < 4; c++) {
@@ -274,27 +355,37 @@ __global__ void __launch_bounds__(192, 1) attn_tc5_kernel(const AttnParams P, co
                 }
                 tmem_st_wait();
             }
+            if (st == 0) T5_MARK(33 + (rescale ? 100 : 0), t);
             m_run = m_new;
-            float sum = 0.0f;
+            // probabilities = 2^(scale * s - reference), one fused multiply-add and one ex2 each, into the P buffer
+            float sums[8];
+#pragma unroll
+            for (int k = 0; k < 8; k++) sums[k] = 0.0f;
+            const uint32_t prow = prow0 + (t & 1) * 2 * T5_HALF;
 #pragma unroll
             for (int c = 0; c < 4; c++) {
 #pragma unroll
                 for (int j = 0; j < 4; j++) {                       // 8 keys = one 16-byte chunk
                     float pr[8];
 #pragma unroll
-                    for (int e = 0; e < 8; e++) { pr[e] = exp2f(__uint_as_float(sv[c][j * 8 + e]) - muse); sum += pr[e]; }
+                    for (int e = 0; e < 8; e++) {
+                        pr[e] = fast_exp2(fmaf(__uint_as_float(sv[c][j * 8 + e]), P.scale_log2, -muse));
+                        sums[e] += pr[e];
+                    }
                     const int chunk = c * 4 + j;                    // 0..15 over the 128 keys
                     const uint32_t dst = prow + (chunk >> 3) * T5_HALF + (((chunk & 7) ^ (r_loc & 7)) << 4);
                     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(dst), "r"(pack_bf16(pr[0], pr[1])),
                                  "r"(pack_bf16(pr[2], pr[3])), "r"(pack_bf16(pr[4], pr[5])), "r"(pack_bf16(pr[6], pr[7])) : "memory");
                 }
             }
+            const float sum = ((sums[0] + sums[1]) + (sums[2] + sums[3])) + ((sums[4] + sums[5]) + (sums[6] + sums[7]));
             l_run = l_run * corr + sum;
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
             tc_fence_before();
-            mbar_arrive(p_full);
+            mbar_arrive(p_full0 + 8 * (t & 1));
+            if (st == 0) T5_MARK(34, t);
         }
-        if (ok && mbar_wait(pv_done, (T - 1) & 1, P.err)) {
+        if (ok && mbar_wait(pv_done0 + 8 * ((T - 1) & 1), ((T - 1) >> 1) & 1, P.err)) {
             tc_fence_after();
             const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
             const bool live = r < R;                                // rows past the end take part in the loads only
@@ -318,11 +409,10 @@ __global__ void __launch_bounds__(192, 1) attn_tc5_kernel(const AttnParams P, co
             }
         }
     }
-    tc_fence_before();
-    __syncthreads();
+    }   // units
     if (warp == 1) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(512u) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(*tmem_slot), "r"(512u) : "memory");
     }
 }
 
@@ -378,13 +468,14 @@ MB_API int mb_attn_tc5_supports(int HD, int page) {
     return HD == 128 && (page == 8 || page == 16 || page == 32 || page == 64 || page == 128);
 }
 
-// items: (sequence, tile of 128 packed rows, 0, 1) -- this kernel does not split the keys over blocks
+// items: (sequence, tile of 128 packed rows, 0, 1), heaviest first -- this kernel does not split the keys over blocks.
+// counter: one int of scratch in device memory (the work counter the blocks draw from)
 MB_API int mb_attn_tc5_bf16(const void* q, int q_stride, void* out, const void* kpool, const void* vpool,
                             const void* items, int n_items, const int* q_start, const int* q_len, const int* pos0,
                             const int* seq_row, const int* table, int max_blocks, int H, int KV, int HD, int page,
-                            int num_pages, int window, float scale, int* err, cudaStream_t st) {
+                            int num_pages, int window, float scale, int* counter, int* err, cudaStream_t st) {
     if (n_items == 0) return 0;
-    if (!mb_attn_tc5_supports(HD, page) || KV < 1 || H % KV || KV > 65535) return -2;
+    if (!mb_attn_tc5_supports(HD, page) || KV < 1 || H % KV || KV > 65535 || !counter) return -2;
     AttnParams P;
     P.q = (const bf16*)q; P.q_stride = q_stride; P.out = (bf16*)out;
     P.kpool = (const bf16*)kpool; P.vpool = (const bf16*)vpool;
@@ -403,14 +494,35 @@ MB_API int mb_attn_tc5_bf16(const void* q, int q_stride, void* out, const void* 
     if (rc) return rc;
     rc = pool_map(vpool, rows, HD, page, &vmap);
     if (rc) return rc;
-    const size_t smem = 1024 + 4 * T5_HALF + 2 * 2 * T5_TILE + 10 * 8 + 16;
+    const size_t smem = 1024 + 6 * T5_HALF + 2 * 2 * T5_TILE + 16 * 8 + 16;
     static bool configured = false;
+    static int sms = 0;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (sms <= 0) sms = 148;
         configured = true;
     }
-    attn_tc5_kernel<<<dim3(n_items, KV), 192, smem, st>>>(P, kmap, vmap);
+    const int n_units = n_items * KV;
+    cudaError_t e = cudaMemsetAsync(counter, 0, sizeof(int), st);       // the work counter starts at zero for every launch
+    if (e != cudaSuccess) return (int)e;
+    attn_tc5_kernel<<<n_units < sms ? n_units : sms, 192, smem, st>>>(P, kmap, vmap, n_units, counter);
     MB_LAUNCH_CHECK();
     return 0;
 }
+
+#ifdef T5_TRACE
+MB_API int mb_attn_tc5_trace(long long* host, int max_events) {
+    int n = 0;
+    cudaMemcpyFromSymbol(&n, t5_trace_n, sizeof(int));
+    if (n > max_events) n = max_events;
+    if (n > 4096) n = 4096;
+    cudaMemcpyFromSymbol(host, t5_trace, (size_t)n * 3 * sizeof(long long));
+    int zero = 0;
+    cudaMemcpyToSymbol(t5_trace_n, &zero, sizeof(int));
+    return n;
+}
+#endif

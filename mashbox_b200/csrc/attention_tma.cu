@@ -97,33 +97,40 @@ __global__ void __launch_bounds__(160, 2) attn_tma_kernel(const AttnParams P, co
     __syncthreads();
 
     if (warp == 4) {
-        // ---------------------------------------------------------------- producer: one lane issues every copy
-        if (lane != 0) return;
+        // ---------------------------------------------------------------- producer
+        // Every copy of a tile is issued by a lane of its own: lane = (K or V, page of the tile, 64-column half).  One
+        // thread issuing them one after the other took thousands of cycles per tile and bounded the whole block.  The
+        // lane's page id is read from the block table one tile ahead.
         const int shift = P.page_shift, page = P.page;
-        const int pages_per_tile = BN >> shift;
+        const int boxes = (BN >> shift) * HALVES;                   // per operand: 1 .. 16
+        const int which = lane / boxes, b = lane % boxes;           // which: 0 = K, 1 = V (lanes past 2 * boxes idle)
+        const int p = b / HALVES, h = b % HALVES;
+        const bool active = lane < 2 * boxes;
+        auto page_of = [&](int t) -> int {
+            const int key0 = lo_al + t * BN + p * page, block = key0 >> shift;
+            const bool live = active && key0 < hi && key0 + page > lo && block < P.max_blocks;
+            return live ? __ldg(tb + block) : 0;
+        };
+        int pg = (t_begin < t_end) ? page_of(t_begin) : 0;
         for (int t = t_begin; t < t_end; t++) {
             const int i = t - t_begin, s = i % STAGES, round = i / STAGES;
-            if (round > 0 && !mbar_wait(empty0 + 8 * s, (round - 1) & 1, P.err)) return;
+            const int pg_next = (t + 1 < t_end) ? page_of(t + 1) : 0;
+            const bool ok = round == 0 || mbar_wait(empty0 + 8 * s, (round - 1) & 1, P.err);
+            if (!__all_sync(0xffffffffu, ok)) return;
             const uint32_t fb = full0 + 8 * s;
-            mbar_expect_tx(fb, 2u * TILE * 2u);
-            const int kb = lo_al + t * BN;
-            const uint32_t kdst = smem_u32(kvs + (size_t)s * 2 * TILE), vdst = kdst + TILE * 2;
-            for (int p = 0; p < pages_per_tile; p++) {
-                const int key0 = kb + p * page, block = key0 >> shift;
-                const bool live = key0 < hi && key0 + page > lo;           // some key of the page can be read
-                int pg = (live && block < P.max_blocks) ? tb[block] : 0;
+            if (lane == 0) mbar_expect_tx(fb, 2u * TILE * 2u);
+            __syncwarp();
+            if (active) {
+                const int key0 = lo_al + t * BN + p * page;
                 if (pg < 0 || pg >= P.num_pages) {
-                    if (live) mb_set_error(P.err, pg < 0 ? MB_ERR_PAGE_MISSING : MB_ERR_PAGE_RANGE);
-                    pg = 0;                                                // any page: every key of it is masked
+                    if (key0 < hi && key0 + page > lo) mb_set_error(P.err, pg < 0 ? MB_ERR_PAGE_MISSING : MB_ERR_PAGE_RANGE);
+                    pg = 0;                                            // any page: every key of it is masked
                 }
-                const int y = (pg * P.KV + kvh) * page;
-#pragma unroll
-                for (int h = 0; h < HALVES; h++) {
-                    const uint32_t off = (uint32_t)(h * 64 * 64 + p * page * 64) * 2u;
-                    tma_load_2d(kdst + off, &kmap, h * 64, y, fb);
-                    tma_load_2d(vdst + off, &vmap, h * 64, y, fb);
-                }
+                const uint32_t dst = smem_u32(kvs + (size_t)s * 2 * TILE) + which * TILE * 2 +
+                                     (uint32_t)(h * 64 * 64 + p * page * 64) * 2u;
+                tma_load_2d(dst, which ? &vmap : &kmap, h * 64, (pg * P.KV + kvh) * page, fb);
             }
+            pg = pg_next;
         }
         return;
     }
