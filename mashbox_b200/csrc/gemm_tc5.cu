@@ -251,6 +251,185 @@ __global__ void __launch_bounds__(192, 1) gemm_tc5_kernel(const __grid_constant_
     }
 }
 
+// ------------------------------------------------------------------------------------------------ decode batches
+// The same machinery turned around for at most 16 tokens ("swap AB"): the 128 rows of a tile of W are the M side of the
+// product, the tokens (padded to 16 by the TMA's zero fill) the N side, and the accumulator is 16 float columns.  The
+// product is bound by reading W once, so the kernel is a deep stream: stages of one 128-row x 64-k box of W (16 KB, one
+// TMA copy) plus the 2 KB of activations that go with it, ten stages in flight per SM.  Matrices with few row tiles are
+// also cut along K so that every SM has work; the split that finishes last for a row tile adds the partial sums in a
+// fixed order and writes the result (a counter per row tile in global memory tells which one is last; it resets itself).
+#define S_STAGE_K 64
+#define S_W_BYTES (128 * 64 * 2)
+#define S_X_BYTES (16 * 64 * 2)
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+}
+
+// MODE 0: bf16 out (N, M); 1: SwiGLU, W has 2 * M rows, bf16 out (N, M); 2: float out (N, M).  N <= 16.
+template <int MODE>
+__global__ void __launch_bounds__(192, 1) gemm_tc5_stream_kernel(const __grid_constant__ CUtensorMap wmap,
+                                                                  const __grid_constant__ CUtensorMap xmap,
+                                                                  void* __restrict__ out, int N, int M, int K, int splits,
+                                                                  int kb_per, float* __restrict__ partial,
+                                                                  int* __restrict__ tile_done, int* err) {
+    constexpr int SETS = MODE == 1 ? 2 : 1;
+    constexpr int STAGE = SETS * S_W_BYTES + S_X_BYTES;
+    constexpr int STAGES = MODE == 1 ? 5 : 10;
+    extern __shared__ unsigned char smem_unaligned[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)STAGES * STAGE);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    int* last_flag = reinterpret_cast<int*>(tmem_slot + 1);
+    const uint32_t stage0 = smem_u32(smem);
+    const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES;
+    const uint32_t tfull0 = empty0 + 8 * STAGES, tempty0 = tfull0 + 16;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int row_tiles = (M + 127) / 128, units = row_tiles * splits, kblocks = (K + S_STAGE_K - 1) / S_STAGE_K;
+
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        for (int a = 0; a < 2; a++) { mbar_init(tfull0 + 8 * a, 1); mbar_init(tempty0 + 8 * a, 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), 64);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int it = 0;
+            for (int u = blockIdx.x; u < units; u += gridDim.x) {
+                const int m0 = (u / splits) * 128, k_lo = (u % splits) * kb_per, k_hi = min(kblocks, k_lo + kb_per);
+                bool ok = true;
+                for (int kb = k_lo; kb < k_hi; kb++, it++) {
+                    const int s = it % STAGES, round = it / STAGES;
+                    if (round > 0 && !mbar_wait(empty0 + 8 * s, (round - 1) & 1, err)) { ok = false; break; }
+                    const uint32_t fb = full0 + 8 * s, dst = stage0 + s * STAGE;
+                    mbar_expect_tx(fb, STAGE);
+                    tma_load_2d(dst, &wmap, kb * S_STAGE_K, m0, fb);
+                    if (MODE == 1) tma_load_2d(dst + S_W_BYTES, &wmap, kb * S_STAGE_K, M + m0, fb);
+                    tma_load_2d(dst + SETS * S_W_BYTES, &xmap, kb * S_STAGE_K, 0, fb);
+                }
+                if (!ok) break;
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc(128, 16);
+            int it = 0, j = 0;
+            for (int u = blockIdx.x; u < units; u += gridDim.x, j++) {
+                const int acc = j & 1, use = j >> 1;
+                const int k_lo = (u % splits) * kb_per, k_hi = min(kblocks, k_lo + kb_per);
+                if (use > 0 && !mbar_wait(tempty0 + 8 * acc, (use - 1) & 1, err)) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * 32;
+                bool ok = true;
+                for (int kb = k_lo; kb < k_hi; kb++, it++) {
+                    const int s = it % STAGES, round = it / STAGES;
+                    if (!mbar_wait(full0 + 8 * s, round & 1, err)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t w_addr = stage0 + s * STAGE, x_addr = w_addr + SETS * S_W_BYTES;
+                    const uint64_t xdesc = umma_desc(x_addr);
+#pragma unroll
+                    for (int set = 0; set < SETS; set++) {
+                        const uint64_t wdesc = umma_desc(w_addr + set * S_W_BYTES);
+#pragma unroll
+                        for (int k = 0; k < S_STAGE_K / 16; k++)
+                            umma_f16(d_tmem + set * 16, wdesc + 2 * k, xdesc + 2 * k, idesc, (kb > k_lo || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(empty0 + 8 * s);
+                }
+                if (!ok) break;
+                umma_commit(tfull0 + 8 * acc);
+            }
+        }
+    } else {
+        const int q = warp & 3, et = q * 32 + lane;                   // et: this thread's row of the tile (TMEM lane)
+        int j = 0;
+        for (int u = blockIdx.x; u < units; u += gridDim.x, j++) {
+            const int acc = j & 1, use = j >> 1;
+            const int row_tile = u / splits, split = u % splits, m = row_tile * 128 + et;
+            if (!mbar_wait(tfull0 + 8 * acc, use & 1, err)) break;
+            tc_fence_after();
+            uint32_t v[SETS][16];
+#pragma unroll
+            for (int set = 0; set < SETS; set++) tmem_ld16(tmem_base + acc * 32 + set * 16 + ((uint32_t)(q * 32) << 16), v[set]);
+            tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty0 + 8 * acc);            // the accumulator may be written again
+            bool finish = true;
+            if (splits > 1) {
+                // partial[split][set][n][m]; the last split to arrive for this row tile adds them up
+                if (m < M) {
+#pragma unroll
+                    for (int set = 0; set < SETS; set++)
+#pragma unroll
+                        for (int n = 0; n < 16; n++)
+                            if (n < N) partial[(((size_t)split * SETS + set) * 16 + n) * M + m] = __uint_as_float(v[set][n]);
+                }
+                __threadfence();
+                asm volatile("bar.sync 1, 128;\n" ::: "memory");
+                if (et == 0) *last_flag = (atomicAdd(tile_done + row_tile, 1) == splits - 1);
+                asm volatile("bar.sync 1, 128;\n" ::: "memory");
+                finish = *last_flag != 0;
+                if (finish) {
+                    __threadfence();
+                    if (m < M) {
+#pragma unroll
+                        for (int set = 0; set < SETS; set++)
+#pragma unroll
+                            for (int n = 0; n < 16; n++) {
+                                float t = 0.0f;
+                                if (n < N)
+                                    for (int sp = 0; sp < splits; sp++)
+                                        t += __ldcg(partial + (((size_t)sp * SETS + set) * 16 + n) * M + m);
+                                v[set][n] = __float_as_uint(t);
+                            }
+                    }
+                    if (et == 0) tile_done[row_tile] = 0;             // ready for the next launch
+                }
+                asm volatile("bar.sync 1, 128;\n" ::: "memory");      // last_flag may be written again
+            }
+            if (finish && m < M) {
+#pragma unroll
+                for (int n = 0; n < 16; n++) {
+                    if (n >= N) continue;
+                    const float a = __uint_as_float(v[0][n]);
+                    if (MODE == 2) {
+                        reinterpret_cast<float*>(out)[(size_t)n * M + m] = a;
+                    } else if (MODE == 1) {
+                        const float g = __bfloat162float(__float2bfloat16_rn(a));
+                        const float up = __bfloat162float(__float2bfloat16_rn(__uint_as_float(v[SETS - 1][n])));
+                        reinterpret_cast<bf16*>(out)[(size_t)n * M + m] = __float2bfloat16_rn(__fdividef(g, 1.0f + __expf(-g)) * up);
+                    } else {
+                        reinterpret_cast<bf16*>(out)[(size_t)n * M + m] = __float2bfloat16_rn(a);
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 64);
+    }
+}
+
 // ------------------------------------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -340,4 +519,76 @@ MB_API int mb_gemm_tc5_swiglu_bf16(const void* act, const void* W, void* out, in
 }
 MB_API int mb_gemm_tc5_f32out(const void* act, const void* W, void* out, int N, int M, int K, int* err, cudaStream_t st) {
     return tc5_launch<2>(act, W, out, N, M, K, err, st);
+}
+
+// k splits of the stream kernels for a (M, K) matrix: about two units per SM, at least four k blocks per split
+static int stream_splits(int M, int K, int sms) {
+    const int row_tiles = (M + 127) / 128, kblocks = (K + S_STAGE_K - 1) / S_STAGE_K;
+    int splits = (2 * sms + row_tiles - 1) / row_tiles;
+    if (splits > 16) splits = 16;
+    if (splits > kblocks / 4) splits = kblocks / 4;
+    if (splits < 1) splits = 1;
+    const int kb_per = (kblocks + splits - 1) / splits;
+    return (kblocks + kb_per - 1) / kb_per;
+}
+
+// ---- decode batches (at most 16 tokens): workspace = float scratch for the partial sums of the k splits
+// (mb_gemm_tc5_stream_workspace says how many floats), counters = one int per 128 rows of W, zero
+// before the first call (the kernel leaves them zero)
+template <int MODE>
+static int stream_launch(const void* act, const void* W, void* out, int N, int M, int K, float* workspace, int* counters,
+                         int* err, cudaStream_t st) {
+    if (N == 0 || M == 0) return 0;
+    if (N > 16 || K % 8 || K < 8 || (reinterpret_cast<uintptr_t>(W) & 15) || (reinterpret_cast<uintptr_t>(act) & 15)) return -2;
+    constexpr int SETS = MODE == 1 ? 2 : 1;
+    constexpr int STAGES = MODE == 1 ? 5 : 10;
+    CUtensorMap wmap, xmap;
+    int rc = matrix_map(W, (long long)SETS * M, K, 128, &wmap);
+    if (rc) return rc;
+    rc = matrix_map(act, N, K, 16, &xmap);
+    if (rc) return rc;
+    const size_t smem = 1024 + (size_t)STAGES * (SETS * S_W_BYTES + S_X_BYTES) + (2 * STAGES + 4) * 8 + 16;
+    static bool configured = false;
+    static int sms = 0;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc5_stream_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (sms <= 0) sms = 148;
+        configured = true;
+    }
+    const int row_tiles = (M + 127) / 128, kblocks = (K + S_STAGE_K - 1) / S_STAGE_K;
+    int splits = stream_splits(M, K, sms);
+    if (!workspace || !counters) splits = 1;
+    const int kb_per = (kblocks + splits - 1) / splits;
+    splits = (kblocks + kb_per - 1) / kb_per;
+    const int units = row_tiles * splits;
+    gemm_tc5_stream_kernel<MODE><<<units < sms ? units : sms, 192, smem, st>>>(wmap, xmap, out, N, M, K, splits, kb_per,
+                                                                               workspace, counters, err);
+    MB_LAUNCH_CHECK();
+    return 0;
+}
+
+// floats of workspace the stream kernels may use for an output of M features (SwiGLU: M = the gate's width)
+MB_API long long mb_gemm_tc5_stream_workspace(int M, int K, int sets) {
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const int splits = stream_splits(M, K, sms > 0 ? sms : 148);
+    return splits > 1 ? (long long)splits * sets * 16 * M : 0;
+}
+
+MB_API int mb_gemm_tc5_stream_bf16(const void* act, const void* W, void* out, int N, int M, int K, float* workspace,
+                                   int* counters, int* err, cudaStream_t st) {
+    return stream_launch<0>(act, W, out, N, M, K, workspace, counters, err, st);
+}
+MB_API int mb_gemm_tc5_stream_swiglu_bf16(const void* act, const void* W, void* out, int N, int M, int K, float* workspace,
+                                          int* counters, int* err, cudaStream_t st) {
+    return stream_launch<1>(act, W, out, N, M, K, workspace, counters, err, st);
+}
+MB_API int mb_gemm_tc5_stream_f32out(const void* act, const void* W, void* out, int N, int M, int K, float* workspace,
+                                     int* counters, int* err, cudaStream_t st) {
+    return stream_launch<2>(act, W, out, N, M, K, workspace, counters, err, st);
 }

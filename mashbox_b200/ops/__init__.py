@@ -158,15 +158,12 @@ def linear(a, w, out=None, out_dtype=None):
             out = torch.empty((N, M), dtype=want, device=a.device)
         if out.is_contiguous() and out.dtype == want and want in (torch.bfloat16, torch.float32):
             return linear_tc5(a, w, out, "plain" if want == torch.bfloat16 else "float")
-    if skinny_supports(N, K) and a.is_contiguous() and w.is_contiguous():
+    if stream_supports(N, K) and a.is_contiguous() and w.is_contiguous() and a.dtype == torch.bfloat16 and M % 8 == 0:
         want = a.dtype if out_dtype is None else out_dtype
         if out is None:
             out = torch.empty((N, M), dtype=want, device=a.device)
         if out.is_contiguous() and out.dtype == want and want in (torch.bfloat16, torch.float32):
-            name = "mb_gemm_skinny_bf16" if want == torch.bfloat16 else "mb_gemm_skinny_f32out"
-            f = _fn("gemm_skinny", name, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p])
-            _check(f(_p(a), _p(w), _p(out), N, M, K, _p(error_word(a.device)), _stream()), "gemm_skinny")
-            return out
+            return linear_stream(a, w, out, "plain" if want == torch.bfloat16 else "float")
     if out_dtype is not None and out_dtype != a.dtype:
         r = torch.mm(a, w.t(), out_dtype=out_dtype)
         if out is not None:
@@ -176,15 +173,6 @@ def linear(a, w, out=None, out_dtype=None):
     if out is not None:
         return torch.mm(a, w.t(), out=out)
     return torch.mm(a, w.t())
-
-
-# The package's own weight-streaming product for decode batches (at most 16 tokens).  Off by default: measured on a B200
-# it reads W at 2.5 to 4.8 TB/s where the library's kernels reach 2.9 to 6.7 TB/s on the same shapes.
-SKINNY = {"enabled": False}
-
-
-def skinny_supports(N, K):
-    return SKINNY["enabled"] and 1 <= N <= 16 and K >= 8 and K % 8 == 0
 
 
 # The package's own tcgen05 product for prompt portions (128 tokens or more).  "swiglu": the fused gate/up product
@@ -208,22 +196,55 @@ def linear_tc5(a, w, out, mode="plain"):
     return out
 
 
+# The tcgen05 weight-streaming product for decode batches (at most 16 tokens): W is the M side of the product.  Off by
+# default: measured on a B200 it matches the library on the output head (6.3 against 6.7 TB/s) and loses on the layer's
+# own matrices, which have too few row tiles and must be cut along K (1.6 to 3 against 2.9 to 5.8 TB/s).
+STREAM = {"enabled": False}
+_stream_scratch = {}
+
+
+def stream_supports(N, K):
+    return STREAM["enabled"] and 1 <= N <= 16 and K >= 8 and K % 8 == 0
+
+
+def linear_stream(a, w, out, mode="plain"):
+    """a (N <= 16, K) bf16, w (M, K) bf16 ("swiglu": (2M, K)) -> out (N, M), as linear_tc5, for decode batches."""
+    _cuda(a, w, out)
+    N, K = a.shape
+    M = out.shape[1]
+    lib = load_library("gemm_tc5")
+    lib.mb_gemm_tc5_stream_workspace.restype = ctypes.c_longlong
+    lib.mb_gemm_tc5_stream_workspace.argtypes = [c_int, c_int, c_int]
+    need = lib.mb_gemm_tc5_stream_workspace(M, K, 2 if mode == "swiglu" else 1)
+    key = str(a.device)
+    sc = _stream_scratch.get(key)
+    tiles = (M + 127) // 128
+    if sc is None or sc[0].numel() < need or sc[1].numel() < tiles:
+        sc = (torch.empty(max(need, 1 << 20), dtype=torch.float32, device=a.device),
+              torch.zeros(max(tiles, 4096), dtype=torch.int32, device=a.device))
+        _stream_scratch[key] = sc
+    name = {"plain": "mb_gemm_tc5_stream_bf16", "swiglu": "mb_gemm_tc5_stream_swiglu_bf16",
+            "float": "mb_gemm_tc5_stream_f32out"}[mode]
+    f = _fn("gemm_tc5", name, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(f(_p(a), _p(w), _p(out), N, M, K, _p(sc[0]), _p(sc[1]), _p(error_word(a.device)), _stream()), "gemm_tc5_stream")
+    return out
+
+
 def fused_swiglu_supports(N, F, K):
-    return skinny_supports(N, K) or tc5_supports(N, F, K, "swiglu")
+    return stream_supports(N, K) or tc5_supports(N, F, K, "swiglu")
 
 
 def linear_swiglu(a, wgu, out):
     """a (N, K) bf16, wgu (2F, K) = [gate rows | up rows] -> out (N, F) = silu(a Wg^T) * (a Wu^T), one kernel: the
-    tcgen05 product for prompt portions, the weight-streaming product for decode batches (when enabled).
+    tcgen05 product for prompt portions, its weight-streaming form for decode batches (when enabled).
     Only for shapes fused_swiglu_supports() takes."""
     _cuda(a, wgu, out)
     N, K = a.shape
     if tc5_supports(N, out.shape[1], K, "swiglu"):
         return linear_tc5(a, wgu, out, "swiglu")
-    f = _fn("gemm_skinny", "mb_gemm_skinny_swiglu_bf16",
-            [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p])
-    _check(f(_p(a), _p(wgu), _p(out), N, out.shape[1], K, _p(error_word(a.device)), _stream()), "gemm_skinny_swiglu")
-    return out
+    if stream_supports(N, K):
+        return linear_stream(a, wgu, out, "swiglu")
+    raise KernelError("linear_swiglu: no fused kernel takes these sizes")
 
 
 # ------------------------------------------------------------------------------------------------ attention

@@ -26,7 +26,6 @@ HEADERS = ["common.cuh", "attention_common.cuh"]
 LIBRARIES = {            # library name -> (source file, extra link flags)
     "elementwise": ("elementwise.cu", []),
     "gemm_f32": ("gemm_f32.cu", []),
-    "gemm_skinny": ("gemm_skinny.cu", []),
     "gemm_tc5": ("gemm_tc5.cu", []),
     "attention_simple": ("attention_simple.cu", []),
     "attention_mma": ("attention_mma.cu", []),

@@ -386,46 +386,32 @@ def test_penalties_and_their_state():
     assert int(cnt[0].sum()) == 0 and int(cnt[3].sum()) == 0
 
 
-@pytest.mark.parametrize("N,M,K", [(1, 4096, 4096), (8, 6144, 4096), (3, 100, 96), (16, 509, 320), (11, 4096, 14336), (5, 17, 32), (2, 50, 72), (9, 333, 1000)])
-def test_weight_streaming_product(N, M, K):
+@pytest.mark.parametrize("N,M,K", [(1, 4096, 4096), (8, 6144, 4096), (3, 1000, 200), (16, 4096, 14336), (5, 504, 320), (2, 56, 72)])
+def test_tcgen05_weight_streaming_product(N, M, K):
+    """the swap-AB form for decode batches: W is the M side, the tokens the N side, matrices with few row tiles are cut
+    along K and the last split adds the partial sums; called twice so that the self-resetting counters are exercised"""
     K_ = ops()
     g = torch.Generator().manual_seed(14)
-    a = torch.randn(N, K, generator=g).bfloat16()
-    w = (torch.randn(M, K, generator=g) / K ** 0.5).bfloat16()
-    K_.SKINNY["enabled"] = True
-    try:
-        _weight_streaming_checks(K_, a, w, N, M, K)
-    finally:
-        K_.SKINNY["enabled"] = False
-
-
-def _weight_streaming_checks(K_, a, w, N, M, K):
-    assert K_.skinny_supports(N, K)
-    got = K_.linear(a.to(G.DEV), w.to(G.DEV))
+    a = torch.randn(N, K, generator=g).bfloat16().to(G.DEV)
+    w = (torch.randn(M, K, generator=g) / K ** 0.5).bfloat16().to(G.DEV)
     want = a.double() @ w.double().T
-    close(got, want, torch.bfloat16, "weight-streaming product")
-    assert float((got.double().cpu() - want).abs().max()) <= 2.0 ** -8 * float(want.abs().max()) + 1e-6   # one bf16 rounding
-    f32 = K_.linear(a.to(G.DEV), w.to(G.DEV), out_dtype=torch.float32)
-    close(f32, want, torch.float32, "weight-streaming product, float32 out")
-    # the same answer as the library product up to the last bf16 step, and the same row whatever the batch
-    K_.SKINNY["enabled"] = False
-    try:
-        lib = K_.linear(a.to(G.DEV), w.to(G.DEV))
-    finally:
-        K_.SKINNY["enabled"] = True
-    want = a.double() @ w.double().T
-    assert float((lib.double().cpu() - got.double().cpu()).abs().max()) <= 2.0 ** -7 * float(want.abs().max())
-    one = K_.linear(a[N - 1:].to(G.DEV).contiguous(), w.to(G.DEV))
-    assert torch.equal(one[0], got[N - 1])
-    # gate, up and their product in one kernel
-    F = M // 2
-    if F:
-        act = torch.empty(N, F, device=G.DEV, dtype=torch.bfloat16)
-        K_.linear_swiglu(a.to(G.DEV), w[:2 * F].to(G.DEV).contiguous(), act)
-        gt = (a.double() @ w[:F].double().T).float().bfloat16().double()
-        up = (a.double() @ w[F:2 * F].double().T).float().bfloat16().double()
-        close(act, gt * torch.sigmoid(gt) * up, torch.bfloat16, "fused SwiGLU product")
-    assert not K_.skinny_supports(17, 4096) and not K_.skinny_supports(4, 100)
+    for _ in range(2):
+        out = torch.full((N, M), float("nan"), device=G.DEV, dtype=torch.bfloat16)
+        K_.linear_stream(a, w, out, "plain")
+        close(out, want, torch.bfloat16, "tcgen05 weight-streaming product")
+    f32 = torch.full((N, M), float("nan"), device=G.DEV)
+    K_.linear_stream(a, w, f32, "float")
+    close(f32, want, torch.float32, "tcgen05 weight-streaming product, float32 out")
+    one = torch.empty(1, M, device=G.DEV, dtype=torch.bfloat16)
+    K_.linear_stream(a[N - 1:].contiguous(), w, one, "plain")
+    assert torch.equal(one[0], out[N - 1])                 # a row does not depend on the batch it is in
+    F = (M // 2) // 8 * 8
+    act = torch.full((N, F), float("nan"), device=G.DEV, dtype=torch.bfloat16)
+    wgu = torch.cat([w[:F], w[M - F:]]).contiguous()
+    K_.linear_stream(a, wgu, act, "swiglu")
+    gt = (a.double() @ wgu[:F].double().T).float().bfloat16().double()
+    up = (a.double() @ wgu[F:].double().T).float().bfloat16().double()
+    close(act, gt * torch.sigmoid(gt) * up, torch.bfloat16, "tcgen05 weight-streaming fused SwiGLU")
     K_.check_error_word(K_.error_word(G.DEV))
 
 
