@@ -1,0 +1,128 @@
+// Matrix-vector products for decode steps with at most 4 tokens: out[n, m] = sum_k act[n, k] * W[m, k].
+//
+// With one to four tokens the product is a pure stream of W and needs no tensor core: a warp owns two rows of W from
+// end to end, each lane reads 16 bytes of both rows at a time (four chunks ahead), multiplies them with the matching
+// 16 bytes of every token's activations (read through L1) in float32, and one shuffle tree per (row, token) finishes
+// the sums.  No shared memory, no partial sums across blocks: 2,048 independent warps for a 4,096-row matrix, so every
+// SM has loads in flight all the time.  A token's result does not depend on how many tokens share the call.
+//
+// Modes: plain (bf16 out), float32 out (the output head), SwiGLU (W = [gate rows | up rows]: a warp takes a gate row and
+// the up row of the same feature and writes silu(gate) * up).  K must be a multiple of 8.
+#include "common.cuh"
+
+typedef __nv_bfloat16 bf16;
+
+#define GV_WARPS 8
+#define GV_ROWS 2
+#define GV_MAX_TOKENS 4
+
+__device__ __forceinline__ uint4 ld_stream16(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ float dot8(const uint4& w, const uint4& x, float acc) {
+    const uint32_t wv[4] = {w.x, w.y, w.z, w.w}, xv[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        acc = fmaf(__uint_as_float(wv[i] << 16), __uint_as_float(xv[i] << 16), acc);
+        acc = fmaf(__uint_as_float(wv[i] & 0xffff0000u), __uint_as_float(xv[i] & 0xffff0000u), acc);
+    }
+    return acc;
+}
+
+// NT tokens (1..4).  MODE 0: bf16 out (N, M); 1: SwiGLU, W has 2 * M rows, bf16 out (N, M); 2: float out.
+template <int NT, int MODE>
+__global__ void __launch_bounds__(GV_WARPS * 32) gemv_kernel(const bf16* __restrict__ act, const bf16* __restrict__ W,
+                                                             void* __restrict__ out, int M, int K) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int unit = blockIdx.x * GV_WARPS + warp;                   // MODE 1: one feature (two rows); else two rows
+    const int m0 = MODE == 1 ? unit : unit * GV_ROWS;
+    if (m0 >= M) return;
+    const bf16* rows[GV_ROWS];
+    rows[0] = W + (size_t)m0 * K;
+    rows[1] = MODE == 1 ? W + (size_t)(M + m0) * K : W + (size_t)min(m0 + 1, M - 1) * K;
+    float acc[GV_ROWS][NT];
+#pragma unroll
+    for (int r = 0; r < GV_ROWS; r++)
+#pragma unroll
+        for (int n = 0; n < NT; n++) acc[r][n] = 0.0f;
+    const int chunks = K / 8;
+    int c = lane;
+    for (; c + 96 < chunks; c += 128) {
+        uint4 w[4][GV_ROWS];
+#pragma unroll
+        for (int u = 0; u < 4; u++)
+#pragma unroll
+            for (int r = 0; r < GV_ROWS; r++) w[u][r] = ld_stream16(rows[r] + (size_t)(c + 32 * u) * 8);
+#pragma unroll
+        for (int u = 0; u < 4; u++)
+#pragma unroll
+            for (int n = 0; n < NT; n++) {
+                const uint4 x = __ldg(reinterpret_cast<const uint4*>(act + (size_t)n * K + (size_t)(c + 32 * u) * 8));
+#pragma unroll
+                for (int r = 0; r < GV_ROWS; r++) acc[r][n] = dot8(w[u][r], x, acc[r][n]);
+            }
+    }
+    for (; c < chunks; c += 32) {
+        uint4 w[GV_ROWS];
+#pragma unroll
+        for (int r = 0; r < GV_ROWS; r++) w[r] = ld_stream16(rows[r] + (size_t)c * 8);
+#pragma unroll
+        for (int n = 0; n < NT; n++) {
+            const uint4 x = __ldg(reinterpret_cast<const uint4*>(act + (size_t)n * K + (size_t)c * 8));
+#pragma unroll
+            for (int r = 0; r < GV_ROWS; r++) acc[r][n] = dot8(w[r], x, acc[r][n]);
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < GV_ROWS; r++)
+#pragma unroll
+        for (int n = 0; n < NT; n++) acc[r][n] = mb_warp_sum(acc[r][n]);
+    if (lane != 0) return;
+#pragma unroll
+    for (int n = 0; n < NT; n++) {
+        if (MODE == 1) {
+            // gate and up pass through bf16 as they do when the products are separate kernels
+            const float g = __bfloat162float(__float2bfloat16_rn(acc[0][n])), up = __bfloat162float(__float2bfloat16_rn(acc[1][n]));
+            reinterpret_cast<bf16*>(out)[(size_t)n * M + m0] = __float2bfloat16_rn((g / (1.0f + expf(-g))) * up);
+        } else {
+#pragma unroll
+            for (int r = 0; r < GV_ROWS; r++) {
+                if (m0 + r >= M) continue;
+                if (MODE == 2) reinterpret_cast<float*>(out)[(size_t)n * M + m0 + r] = acc[r][n];
+                else reinterpret_cast<bf16*>(out)[(size_t)n * M + m0 + r] = __float2bfloat16_rn(acc[r][n]);
+            }
+        }
+    }
+}
+
+template <int MODE>
+static int gemv_launch(const void* act, const void* W, void* out, int N, int M, int K, cudaStream_t st) {
+    if (N == 0 || M == 0) return 0;
+    if (N > GV_MAX_TOKENS || K % 8 || K < 8 || (reinterpret_cast<uintptr_t>(W) & 15) || (reinterpret_cast<uintptr_t>(act) & 15))
+        return -2;
+    const int units = MODE == 1 ? M : (M + GV_ROWS - 1) / GV_ROWS;
+    const unsigned grid = (unsigned)((units + GV_WARPS - 1) / GV_WARPS);
+    const bf16* a = (const bf16*)act;
+    const bf16* w = (const bf16*)W;
+    switch (N) {
+        case 1: gemv_kernel<1, MODE><<<grid, GV_WARPS * 32, 0, st>>>(a, w, out, M, K); break;
+        case 2: gemv_kernel<2, MODE><<<grid, GV_WARPS * 32, 0, st>>>(a, w, out, M, K); break;
+        case 3: gemv_kernel<3, MODE><<<grid, GV_WARPS * 32, 0, st>>>(a, w, out, M, K); break;
+        default: gemv_kernel<4, MODE><<<grid, GV_WARPS * 32, 0, st>>>(a, w, out, M, K); break;
+    }
+    MB_LAUNCH_CHECK();
+    return 0;
+}
+
+MB_API int mb_gemv_bf16(const void* act, const void* W, void* out, int N, int M, int K, cudaStream_t st) {
+    return gemv_launch<0>(act, W, out, N, M, K, st);
+}
+MB_API int mb_gemv_swiglu_bf16(const void* act, const void* W, void* out, int N, int M, int K, cudaStream_t st) {
+    return gemv_launch<1>(act, W, out, N, M, K, st);
+}
+MB_API int mb_gemv_f32out(const void* act, const void* W, void* out, int N, int M, int K, cudaStream_t st) {
+    return gemv_launch<2>(act, W, out, N, M, K, st);
+}

@@ -27,6 +27,7 @@ LIBRARIES = {            # library name -> (source file, extra link flags)
     "elementwise": ("elementwise.cu", []),
     "gemm_f32": ("gemm_f32.cu", []),
     "gemm_tc5": ("gemm_tc5.cu", []),
+    "gemv": ("gemv.cu", []),
     "attention_simple": ("attention_simple.cu", []),
     "attention_mma": ("attention_mma.cu", []),
     "attention_tma": ("attention_tma.cu", []),

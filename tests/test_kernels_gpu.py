@@ -444,3 +444,32 @@ def test_tcgen05_product(N, M, K):
     K_.check_error_word(K_.error_word(G.DEV))
     with pytest.raises(Exception, match="does not take these sizes"):
         K_.linear_tc5(a[:, :K - 4].contiguous(), w[:, :K - 4].contiguous(), out, "plain")
+
+
+@pytest.mark.parametrize("N,M,K", [(1, 4096, 4096), (4, 6144, 4096), (2, 509, 320), (3, 4096, 14336), (1, 57, 72)])
+def test_matrix_vector_product(N, M, K):
+    """at most 4 tokens: one warp per two rows of W, float32 sums; plain, float32 out and fused SwiGLU"""
+    K_ = ops()
+    g = torch.Generator().manual_seed(16)
+    a = torch.randn(N, K, generator=g).bfloat16().to(G.DEV)
+    w = (torch.randn(M, K, generator=g) / K ** 0.5).bfloat16().to(G.DEV)
+    want = a.double() @ w.double().T
+    out = torch.full((N, M), float("nan"), device=G.DEV, dtype=torch.bfloat16)
+    K_.linear_gemv(a, w, out, "plain")
+    close(out, want, torch.bfloat16, "matrix-vector product")
+    assert float((out.double() - want).abs().max()) <= 2.0 ** -8 * float(want.abs().max()) + 1e-6
+    f32 = torch.full((N, M), float("nan"), device=G.DEV)
+    K_.linear_gemv(a, w, f32, "float")
+    close(f32, want, torch.float32, "matrix-vector product, float32 out")
+    one = torch.empty(1, M, device=G.DEV, dtype=torch.bfloat16)
+    K_.linear_gemv(a[N - 1:].contiguous(), w, one, "plain")
+    assert torch.equal(one[0], out[N - 1])                          # a token's result does not depend on the batch
+    F = M // 2
+    act = torch.full((N, F), float("nan"), device=G.DEV, dtype=torch.bfloat16)
+    wgu = torch.cat([w[:F], w[M - F:]]).contiguous()
+    K_.linear_gemv(a, wgu, act, "swiglu")
+    gt = (a.double() @ wgu[:F].double().T).float().bfloat16().double()
+    up = (a.double() @ wgu[F:].double().T).float().bfloat16().double()
+    close(act, gt * torch.sigmoid(gt) * up, torch.bfloat16, "matrix-vector fused SwiGLU")
+    with pytest.raises(Exception, match="does not take these sizes"):
+        K_.linear_gemv(torch.zeros(5, K, device=G.DEV, dtype=torch.bfloat16), w, torch.empty(5, M, device=G.DEV, dtype=torch.bfloat16))
