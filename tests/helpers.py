@@ -18,14 +18,26 @@ TINY_B = LlamaConfig(architecture="LlamaForCausalLM", num_layers=3, hidden=96, n
                      intermediate=320, vocab=509, rms_eps=1e-6, rope_theta=500000.0,
                      rope_scaling=RopeScaling("llama3", 8.0, 1.0, 4.0, 64), tie_embeddings=False, attention_bias=True,
                      max_position=512)
-TINY = {"A": (TINY_A, 0, 16), "B": (TINY_B, 1, 8)}          # config, seed, page size
+# a third one with the head size of the large models, so that the engine-level tests reach the kernels that take only
+# head size 128 (the tcgen05 attention kernel) and 64/128 (the TMA-fed one): linear rope scaling, 2 query heads per kv head
+TINY_C = LlamaConfig(architecture="LlamaForCausalLM", num_layers=2, hidden=256, num_heads=4, num_kv_heads=2, head_dim=128,
+                     intermediate=384, vocab=311, rms_eps=1e-5, rope_theta=1000000.0,
+                     rope_scaling=RopeScaling("linear", 2.0), tie_embeddings=False, attention_bias=False,
+                     max_position=1024)
+TINY = {"A": (TINY_A, 0, 16), "B": (TINY_B, 1, 8), "C": (TINY_C, 2, 16)}          # config, seed, page size
 # Random weights shaped like a trained model's rather than like an initialisation: an embedding of order one, readers
 # (q, k, v, gate, up, head) near 1/sqrt(fan in) so that attention is not uniform, and writers into the residual stream
 # (o_proj, down_proj) small, so that a layer changes the stream a little instead of replacing it.  With every matrix
 # at one width the stream is whatever the last layer wrote and the model amplifies any perturbation about seven-fold
 # per layer (measured: one-step bf16 differences in 1e-4 of the first product's outputs reached most values two layers
 # later), which buries every comparison in bfloat16 under noise.
-STD = 0.1
+# Readers are N(0, STD(hidden)) with STD about 1/sqrt(fan in), so that q, k and the scores are of order one at every width
+# (at 0.1 the 256-wide model C has scores of standard deviation 2.6 and a softmax sharp enough to turn one-step bf16
+# differences of the first product into 1.4e-5 of the logits).
+def STD(hidden):
+    return min(0.1, hidden ** -0.5)
+
+
 STD_BY_NAME = (("embed_tokens", 1.0), ("o_proj", 0.02), ("down_proj", 0.02))
 
 
@@ -33,7 +45,8 @@ def make_folder(tmp, name, store="float32"):
     cfg, seed, _ = TINY[name]
     d = os.path.join(str(tmp), f"tiny_{name}_{store}")
     if not os.path.isdir(d):
-        write_model_folder(d, cfg, seed, dtype=getattr(torch, store), std=STD, norm_std=0.1, std_by_name=STD_BY_NAME)
+        write_model_folder(d, cfg, seed, dtype=getattr(torch, store), std=STD(cfg.hidden), norm_std=0.1,
+                           std_by_name=STD_BY_NAME)
     return d
 
 

@@ -8,7 +8,7 @@ import torch
 from tests import helpers as H
 
 pytestmark = pytest.mark.gpu
-CASES = [(n, m) for n in ("A", "B") for m in H.MODES]
+CASES = [(n, m) for n in ("A", "B", "C") for m in H.MODES]
 
 
 def runner_for(tmp, name, mode, max_tokens, options=None):
