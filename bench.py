@@ -235,6 +235,57 @@ def run_ours(a):
     return 0
 
 
+def run_kernels(a):
+    """Times this repo's matrix-product and attention kernels next to the library's on the layer shapes of the
+    configuration (2,048 tokens and a decode batch), one JSON line; also the workload of the ncu captures of single
+    kernels (few launches, under 2 GB on the device)."""
+    import torch
+    from mashbox_b200 import ops
+    dev = "cuda:0"
+    c = baseline_config()
+    D, F, QKV, V = c.hidden, c.intermediate, (c.num_heads + 2 * c.num_kv_heads) * c.head_dim, c.vocab
+    gen = torch.Generator(device=dev).manual_seed(0)
+    rnd = lambda *s: (torch.randn(*s, generator=gen, device=dev) * 0.02).to(torch.bfloat16)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def timed(f, n=a.steps):
+        for _ in range(max(3, a.warmup)):
+            f()
+        ts = []
+        for _ in range(n):
+            flush.zero_()                                   # L2 is flushed between timed launches
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            f()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) * 1e3)
+        return statistics.median(ts)
+
+    out = {}
+    T = a.prefill_tokens
+    for name, M, K in (("qkv", QKV, D), ("o", D, D), ("gate_up", 2 * F, D), ("down", D, F)):
+        x, w = rnd(T, K), rnd(M, K)
+        y = torch.empty(T, M, device=dev, dtype=torch.bfloat16)
+        own = timed(lambda: ops.linear_tc5(x, w, y, "plain"))
+        lib = timed(lambda: torch.mm(x, w.t(), out=y))
+        fl = 2 * T * M * K
+        out[f"prefill_{name}"] = {"own_us": own, "library_us": lib, "own_tflops": fl / own / 1e6, "library_tflops": fl / lib / 1e6}
+    x, w = rnd(T, D), rnd(2 * F, D)
+    y = torch.empty(T, F, device=dev, dtype=torch.bfloat16)
+    out["prefill_gate_up_swiglu_fused"] = {"own_us": timed(lambda: ops.linear_tc5(x, w, y, "swiglu"))}
+    for name, M, K in (("o", D, D), ("gate_up", 2 * F, D), ("head", V, D)):
+        x, w = rnd(a.batch, K), rnd(M, K)
+        y = torch.empty(a.batch, M, device=dev, dtype=torch.bfloat16)
+        own = timed(lambda: ops.linear_stream(x, w, y, "plain"))
+        lib = timed(lambda: torch.mm(x, w.t(), out=y))
+        out[f"decode_{name}"] = {"own_us": own, "library_us": lib, "own_gbs": M * K * 2 / own / 1e3, "library_gbs": M * K * 2 / lib / 1e3}
+    ops.check_error_word(ops.error_word(dev))
+    print(json.dumps({"impl": "ours", "kernels": out, "note": "CUDA-event time of single launches after an L2 flush; "
+                      "launch gaps of the Python caller are inside these figures"}))
+    return 0
+
+
 def run_reference(a):
     """The reference arm: mashbox's own engine from baseline/_ref.  mashbox 0.1.15 installs there with --no-deps, but
     its model and engine modules import JAX (not in this image, no network) and it runs on TPU chips."""
@@ -263,6 +314,7 @@ def main():
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-graphs", action="store_true", help="launch every kernel directly (for profilers)")
+    ap.add_argument("--kernels", action="store_true", help="time single kernels against the library instead of the model")
     a = ap.parse_args()
     if a.impl == "reference":
         return run_reference(a)
@@ -271,7 +323,7 @@ def main():
             print(f"bench.py: this engine runs on ONE GPU; --gpus {a.gpus} is not measured")
         return 2
     a.warmup = max(a.warmup, 3)
-    return run_ours(a)
+    return run_kernels(a) if a.kernels else run_ours(a)
 
 
 if __name__ == "__main__":
