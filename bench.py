@@ -123,7 +123,8 @@ def run_ours(a):
     t0 = time.time()
     eng = Engine.from_config(cfg, RandomSource(shapes, 0, torch.bfloat16, dev), dtype="bfloat16", device=dev,
                              page_size=16, max_tokens=pool_tokens, max_requests=max_b, max_tokens_per_step=2048 + max_b,
-                             chunk=2048, max_context=per_request, cuda_graphs=not a.no_graphs)
+                             chunk=2048, max_context=per_request, cuda_graphs=not a.no_graphs,
+                             options=json.loads(a.options) if a.options else None)
     torch.cuda.synchronize()
     load_s = time.time() - t0
     gen = torch.Generator().manual_seed(1)
@@ -314,6 +315,7 @@ def main():
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-graphs", action="store_true", help="launch every kernel directly (for profilers)")
+    ap.add_argument("--options", default="", help="JSON of engine options (kernel choices), for experiments")
     ap.add_argument("--kernels", action="store_true", help="time single kernels against the library instead of the model")
     a = ap.parse_args()
     if a.impl == "reference":
