@@ -19,7 +19,10 @@
 #include "attention_common.cuh"
 
 #define T5_WAIT_LIMIT (1 << 22)
-#define T5_BM 128
+#define T5_BM 128                              // rows of one query tile: one softmax warpgroup, thread = row
+#define T5_QT 2                                // query tiles of a block, sharing the K and V tiles
+#define T5_ROWS (T5_BM * T5_QT)
+#define T5_THREADS (T5_QT * T5_BM + 64)        // softmax warpgroups, producer warp, product warp
 #define T5_BN 128
 #define T5_HD 128
 #define T5_TILE (T5_BN * T5_HD * 2)            // bytes of one K or V tile (two 64-column halves of 16 KB)
@@ -54,6 +57,11 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64
     asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
                  ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// the same product with the A operand in tensor memory (row = lane, two bf16 per 32-bit column, k ascending)
+__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+                 ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
 }
@@ -86,7 +94,10 @@ __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.
 #ifdef T5_TRACE
 __device__ long long t5_trace[3 * 4096];
 __device__ int t5_trace_n;
-#define T5_MARK(ev, t) do { if (blockIdx.x == 0 && first_unit && (threadIdx.x & 31) == 0) { int i__ = atomicAdd(&t5_trace_n, 1); if (i__ < 4096) { \
+// each role writes into a quarter of its own (no atomics: a mark costs a few stores); the role is taken from the event
+#define T5_MARK(ev, t) do { if (blockIdx.x == 0 && first_unit && (threadIdx.x & 31) == 0) { \
+    const int role__ = (ev) < 20 ? 0 : ((ev) % 100) < 30 ? 1 : 2 + ((ev) & 1); \
+    if (trace_i < 1024) { const int i__ = role__ * 1024 + trace_i++; \
     t5_trace[3 * i__] = (ev); t5_trace[3 * i__ + 1] = (t); t5_trace[3 * i__ + 2] = clock64(); } } } while (0)
 #else
 #define T5_MARK(ev, t) do { } while (0)
@@ -110,28 +121,44 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t addr, uint32_t lbo, uint3
     return d;
 }
 
-__global__ void __launch_bounds__(192, 1) attn_tc5_kernel(const AttnParams P, const __grid_constant__ CUtensorMap kmap,
-                                                           const __grid_constant__ CUtensorMap vmap, int n_units,
-                                                           int* __restrict__ counter) {
+// The same descriptor in two halves.  Only the low word changes from product to product (start address in bits 0-13,
+// leading byte offset in bits 16-29), so the issuing thread keeps one low word per operand and adds a constant: built
+// whole for every product, the descriptors cost that one thread more time than the products take to run.
+constexpr uint32_t T5_DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);       // stride byte offset 1024, version 1, 128-byte swizzle
+__device__ __forceinline__ uint32_t umma_desc_lo(uint32_t addr, uint32_t lbo) {
+    return ((addr & 0x3FFFFu) >> 4) | (((lbo >> 4) & 0x3FFFu) << 16);
+}
+__device__ __forceinline__ uint64_t umma_desc_join(uint32_t lo) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};\n" : "=l"(d) : "r"(lo), "r"(T5_DESC_HI));
+    return d;
+}
+
+__global__ void __launch_bounds__(T5_THREADS, 1) attn_tc5_kernel(const AttnParams P, const __grid_constant__ CUtensorMap kmap,
+                                                                  const __grid_constant__ CUtensorMap vmap, int n_units,
+                                                                  int* __restrict__ counter) {
     extern __shared__ unsigned char smem_unaligned[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(
         (reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~static_cast<uintptr_t>(1023));
-    // Q (32 KB) | 2 x P (32 KB) | 2 stages x (K tile 32 KB, V tile 32 KB) | barriers
-    const uint32_t q_s = smem_u32(smem), p_s0 = q_s + 2 * T5_HALF, kv_s = p_s0 + 4 * T5_HALF;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * T5_HALF + 2 * 2 * T5_TILE);
+    // 2 x Q tile (32 KB each) | 2 stages x K tile (32 KB) | 2 stages x V tile (32 KB) | barriers
+    const uint32_t q_s0 = smem_u32(smem), k_s0 = q_s0 + T5_QT * 2 * T5_HALF, v_s0 = k_s0 + 2 * T5_TILE;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + T5_QT * 2 * T5_HALF + 4 * T5_TILE);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
     int* unit_slot = reinterpret_cast<int*>(tmem_slot + 1);
     const uint32_t k_full0 = smem_u32(bars), k_empty0 = k_full0 + 16, v_full0 = k_full0 + 32, v_empty0 = k_full0 + 48,
-                   s_full0 = k_full0 + 64, p_full0 = k_full0 + 80, pv_done0 = k_full0 + 96, q_ready = k_full0 + 112;
+                   s_full0 = k_full0 + 64, p_full0 = k_full0 + 80, o_done0 = k_full0 + 96, q_ready0 = k_full0 + 112;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    if (warp == 1) {
+    if (warp == 9) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
     // Work units (item, kv head) are handed out by a counter in global memory, heaviest first, so blocks stay busy until
     // the list is empty whatever the mix of short and long rows.
     bool first_unit = true;
+#ifdef T5_TRACE
+    int trace_i = 0;
+#endif
     for (;; first_unit = false) {
     tc_fence_before();
     __syncthreads();                                                  // the unit before is finished by every role
@@ -143,25 +170,37 @@ __global__ void __launch_bounds__(192, 1) attn_tc5_kernel(const AttnParams P, co
     const int seq = item.x, m_tile = item.y;
     const int kvh = unit % P.KV;
     const int G = P.G, R = P.q_len[seq] * G, pos0 = P.pos0[seq], tok0 = P.q_start[seq];
-    const int row0 = m_tile * T5_BM;
+    const int row0 = m_tile * T5_ROWS;
     if (row0 >= R) continue;
-    const int row_last = min(R, row0 + T5_BM) - 1;
-    const int pos_min = pos0 + row0 / G, pos_max = pos0 + row_last / G;
-    const int hi = pos_max + 1;
+    // the unit's two query tiles: rows, positions and key tiles of each (the second may be empty)
+    const int pos_min = pos0 + row0 / G;
     const int lo = (P.window > 0 && pos_min - P.window + 1 > 0) ? pos_min - P.window + 1 : 0;
     const int lo_al = (lo / T5_BN) * T5_BN;
-    const int T = (hi - lo_al + T5_BN - 1) / T5_BN;                 // key tiles of this block (at least one)
+    int Tg[T5_QT], pmin[T5_QT], pmax[T5_QT];
+#pragma unroll
+    for (int g = 0; g < T5_QT; g++) {
+        const int r0 = row0 + g * T5_BM;
+        if (r0 < R) {
+            pmin[g] = pos0 + r0 / G;
+            pmax[g] = pos0 + (min(R, r0 + T5_BM) - 1) / G;
+            Tg[g] = (pmax[g] + 1 - lo_al + T5_BN - 1) / T5_BN;      // at least one
+        } else {
+            pmin[g] = pmax[g] = 0;
+            Tg[g] = 0;
+        }
+    }
+    const int T = max(Tg[0], Tg[1]);
+    const int hi = max(pmax[0], pmax[1]) + 1;
     const int* tb = P.table + (size_t)P.seq_row[seq] * P.max_blocks;
 
     if (tid == 0) {
         if (!first_unit)                                             // the barriers of the unit before are retired first
-            for (int b = 0; b < 15; b++) asm volatile("mbarrier.inval.shared::cta.b64 [%0];\n" ::"r"(k_full0 + 8 * b) : "memory");
+            for (int b = 0; b < 16; b++) asm volatile("mbarrier.inval.shared::cta.b64 [%0];\n" ::"r"(k_full0 + 8 * b) : "memory");
         for (int s = 0; s < 2; s++) {
             mbar_init(k_full0 + 8 * s, 1); mbar_init(k_empty0 + 8 * s, 1); mbar_init(v_full0 + 8 * s, 1);
-            mbar_init(v_empty0 + 8 * s, 1); mbar_init(s_full0 + 8 * s, 1);
-            mbar_init(p_full0 + 8 * s, 128); mbar_init(pv_done0 + 8 * s, 1);
+            mbar_init(v_empty0 + 8 * s, 1); mbar_init(s_full0 + 8 * s, 1); mbar_init(p_full0 + 8 * s, T5_BM);
+            mbar_init(o_done0 + 8 * s, 1); mbar_init(q_ready0 + 8 * s, T5_BM);
         }
-        mbar_init(q_ready, 128);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     }
@@ -169,104 +208,122 @@ __global__ void __launch_bounds__(192, 1) attn_tc5_kernel(const AttnParams P, co
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tm_s0 = tmem_base, tm_o = tmem_base + 256;       // scores: columns 0..127 and 128..255; output: 256..383
+    // tensor memory: scores of tile g in columns g*128 .. +127 (its probabilities go back into the first 64 of them as
+    // bf16 pairs), output accumulator of tile g in columns 256 + g*128 .. +127
+    const uint32_t tm_s0 = tmem_base, tm_o0 = tmem_base + 256;
 
-    if (warp == 0) {
+    if (warp == 8) {
         // ---------------------------------------------------------------- producer
         // Every copy of a tile is issued by a lane of its own: lane = (page of the tile, 64-column half).  One thread
         // issuing them one after the other took 3,000 to 4,000 cycles per 32 KB tile and was what the whole block
         // waited for.  The lane's page id is read from the block table one tile ahead.
-        {
-            const int shift = P.page_shift, page = P.page;
-            const int boxes = (T5_BN >> shift) * 2;                  // 2 .. 32
-            const int p = lane >> 1, h = lane & 1;
-            auto page_of = [&](int t) -> int {
-                const int key0 = lo_al + t * T5_BN + p * page, block = key0 >> shift;
-                const bool live = lane < boxes && key0 < hi && key0 + page > lo && block < P.max_blocks;
-                return live ? __ldg(tb + block) : 0;
-            };
-            // K of tile t+1 goes out before V of tile t: the key stage is free as soon as the score product that read it
-            // is done, the value stage only after the output product, one tile later
-            auto load = [&](int t, bool keys, int pg) -> bool {
-                const int s = t & 1, round = t >> 1;
-                const uint32_t empty = (keys ? k_empty0 : v_empty0) + 8 * s, fb = (keys ? k_full0 : v_full0) + 8 * s;
-                bool ok = round == 0 || mbar_wait(empty, (round - 1) & 1, P.err);
-                if (!__all_sync(0xffffffffu, ok)) return false;
-                T5_MARK(keys ? 10 : 12, t);
-                if (lane == 0) mbar_expect_tx(fb, T5_TILE);
-                __syncwarp();
-                if (lane < boxes) {
-                    const int key0 = lo_al + t * T5_BN + p * page;
-                    if (pg < 0 || pg >= P.num_pages) {
-                        if (key0 < hi && key0 + page > lo) mb_set_error(P.err, pg < 0 ? MB_ERR_PAGE_MISSING : MB_ERR_PAGE_RANGE);
-                        pg = 0;                                      // any page: every key of it is masked
-                    }
-                    const uint32_t dst = kv_s + s * 2 * T5_TILE + (keys ? 0 : T5_TILE) + h * T5_HALF + p * page * 128;
-                    tma_load_2d(dst, keys ? &kmap : &vmap, h * 64, (pg * P.KV + kvh) * page, fb);
+        const int shift = P.page_shift, page = P.page;
+        const int boxes = (T5_BN >> shift) * 2;                      // 2 .. 32
+        const int p = lane >> 1, h = lane & 1;
+        auto page_of = [&](int t) -> int {
+            const int key0 = lo_al + t * T5_BN + p * page, block = key0 >> shift;
+            const bool live = lane < boxes && key0 < hi && key0 + page > lo && block < P.max_blocks;
+            return live ? __ldg(tb + block) : 0;
+        };
+        // K of tile t+1 goes out before V of tile t: the key stage is free as soon as the score products that read it
+        // are done, the value stage only after the output products, one tile later
+        auto load = [&](int t, bool keys, int pg) -> bool {
+            const int s = t & 1, round = t >> 1;
+            const uint32_t empty = (keys ? k_empty0 : v_empty0) + 8 * s, fb = (keys ? k_full0 : v_full0) + 8 * s;
+            bool ok = round == 0 || mbar_wait(empty, (round - 1) & 1, P.err);
+            if (!__all_sync(0xffffffffu, ok)) return false;
+            T5_MARK(keys ? 10 : 12, t);
+            if (lane == 0) mbar_expect_tx(fb, T5_TILE);
+            __syncwarp();
+            if (lane < boxes) {
+                const int key0 = lo_al + t * T5_BN + p * page;
+                if (pg < 0 || pg >= P.num_pages) {
+                    if (key0 < hi && key0 + page > lo) mb_set_error(P.err, pg < 0 ? MB_ERR_PAGE_MISSING : MB_ERR_PAGE_RANGE);
+                    pg = 0;                                          // any page: every key of it is masked
                 }
-                T5_MARK(keys ? 11 : 13, t);
-                return true;
-            };
-            int pg_cur = page_of(0);
-            bool ok = load(0, true, pg_cur);
-            for (int t = 0; t < T && ok; t++) {
-                int pg_next = 0;
-                if (t + 1 < T) { pg_next = page_of(t + 1); ok = load(t + 1, true, pg_next); }
-                if (ok) ok = load(t, false, pg_cur);
-                pg_cur = pg_next;
+                const uint32_t dst = (keys ? k_s0 : v_s0) + s * T5_TILE + h * T5_HALF + p * page * 128;
+                tma_load_2d(dst, keys ? &kmap : &vmap, h * 64, (pg * P.KV + kvh) * page, fb);
             }
+            T5_MARK(keys ? 11 : 13, t);
+            return true;
+        };
+        int pg_cur = page_of(0);
+        bool ok = load(0, true, pg_cur);
+        for (int t = 0; t < T && ok; t++) {
+            int pg_next = 0;
+            if (t + 1 < T) { pg_next = page_of(t + 1); ok = load(t + 1, true, pg_next); }
+            if (ok) ok = load(t, false, pg_cur);
+            pg_cur = pg_next;
         }
-    } else if (warp == 1) {
+    } else if (warp == 9) {
         // ---------------------------------------------------------------- products
+        // One thread issues, for the two query tiles in turn: O_g += P_g(t) V(t), then S_g = Q_g K(t+1)^T.  While the
+        // softmax warps of one tile work, the tensor cores run the products of the other.  The score product of a tile
+        // overwrites the buffer its probabilities lay in; it is issued after the output product that read them, and the
+        // products run in the order they were issued.
         if (lane == 0) {
             // D float, A and B bf16, M = 128, N = 128; the second descriptor has B MN-major (bit 16) for P V
             constexpr uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
             constexpr uint32_t idesc_pv = idesc_qk | (1u << 16);
-            bool ok = mbar_wait(q_ready, 0, P.err);
-            auto scores = [&](int t) -> bool {                      // S[t % 2] = Q K_t^T
+            bool ok = true;
+#pragma unroll
+            for (int g = 0; g < T5_QT; g++)
+                if (ok && Tg[g] > 0) ok = mbar_wait(q_ready0 + 8 * g, 0, P.err);
+            auto scores = [&](int g, int t) -> bool {               // S_g = Q_g K_t^T
                 const int s = t & 1;
-                T5_MARK(20, t);
+                T5_MARK(20 + g, t);
                 if (!mbar_wait(k_full0 + 8 * s, (t >> 1) & 1, P.err)) return false;
-                T5_MARK(21, t);
                 tc_fence_after();
-                const uint32_t k_s = kv_s + s * 2 * T5_TILE;
+                const uint32_t k_lo = umma_desc_lo(k_s0 + s * T5_TILE, 0), q_lo = umma_desc_lo(q_s0 + g * 2 * T5_HALF, 0);
 #pragma unroll
                 for (int ks = 0; ks < 8; ks++) {
-                    const uint32_t off = (ks >> 2) * T5_HALF + (ks & 3) * 32;
-                    umma_f16(tm_s0 + s * 128, umma_desc(q_s + off, 0, 1024), umma_desc(k_s + off, 0, 1024), idesc_qk, ks > 0);
+                    constexpr uint32_t half = T5_HALF >> 4;
+                    const uint32_t off = (ks >> 2) * half + (ks & 3) * 2;                 // in 16-byte units
+                    umma_f16(tm_s0 + g * 128, umma_desc_join(q_lo + off), umma_desc_join(k_lo + off), idesc_qk, ks > 0);
                 }
-                umma_commit(k_empty0 + 8 * s);                      // the key stage is free once these products are done
-                umma_commit(s_full0 + 8 * s);
-                T5_MARK(22, t);
+                if (g == T5_QT - 1 || t >= Tg[g + 1 < T5_QT ? g + 1 : g])    // the last tile that reads this key stage
+                    umma_commit(k_empty0 + 8 * s);
+                umma_commit(s_full0 + 8 * g);
+                T5_MARK(22 + g, t);
                 return true;
             };
-            if (ok) ok = scores(0);
-            for (int t = 0; t < T && ok; t++) {
-                if (t + 1 < T) ok = scores(t + 1);
-                T5_MARK(23, t);
-                if (!ok || !mbar_wait(p_full0 + 8 * (t & 1), (t >> 1) & 1, P.err)) { ok = false; break; }
-                T5_MARK(24, t);
-                if (!mbar_wait(v_full0 + 8 * (t & 1), (t >> 1) & 1, P.err)) { ok = false; break; }
-                T5_MARK(25, t);
+            auto outputs = [&](int g, int t) -> bool {              // O_g += P_g V_t
+                const int s = t & 1;
+                T5_MARK(24 + g, t);
+                if (!mbar_wait(p_full0 + 8 * g, t & 1, P.err)) return false;
+                if (!mbar_wait(v_full0 + 8 * s, (t >> 1) & 1, P.err)) return false;
+                T5_MARK(26 + g, t);
                 tc_fence_after();
-                const uint32_t v_s = kv_s + (t & 1) * 2 * T5_TILE + T5_TILE, p_s = p_s0 + (t & 1) * 2 * T5_HALF;
+                const uint32_t v_lo = umma_desc_lo(v_s0 + s * T5_TILE, T5_HALF);
 #pragma unroll
-                for (int kk = 0; kk < 8; kk++) {                    // 16 keys per step
-                    const uint64_t pd = umma_desc(p_s + (kk >> 2) * T5_HALF + (kk & 3) * 32, 0, 1024);
-                    const uint64_t vd = umma_desc(v_s + kk * 2048, T5_HALF, 1024);
-                    umma_f16(tm_o, pd, vd, idesc_pv, (t > 0 || kk > 0) ? 1u : 0u);
+                for (int kk = 0; kk < 8; kk++)                      // 16 keys per step: 2,048 bytes further in the tile
+                    umma_f16_ts(tm_o0 + g * 128, tm_s0 + g * 128 + kk * 8, umma_desc_join(v_lo + kk * 128), idesc_pv,
+                                (t > 0 || kk > 0) ? 1u : 0u);
+                if (g == T5_QT - 1 || t >= Tg[g + 1 < T5_QT ? g + 1 : g]) umma_commit(v_empty0 + 8 * s);
+                if (t == Tg[g] - 1) umma_commit(o_done0 + 8 * g);
+                T5_MARK(28 + g, t);
+                return true;
+            };
+#pragma unroll
+            for (int g = 0; g < T5_QT; g++)
+                if (ok && Tg[g] > 0) ok = scores(g, 0);
+            for (int t = 0; t < T && ok; t++) {
+#pragma unroll
+                for (int g = 0; g < T5_QT; g++) {
+                    if (ok && t < Tg[g]) ok = outputs(g, t);
+                    if (ok && t + 1 < Tg[g]) ok = scores(g, t + 1);
                 }
-                umma_commit(v_empty0 + 8 * (t & 1));
-                umma_commit(pv_done0 + 8 * (t & 1));
-                T5_MARK(26, t);
             }
         }
-    } else {
-        // ---------------------------------------------------------------- softmax: thread = row
-        const int q = warp & 3, r_loc = q * 32 + lane, r = row0 + r_loc;
-        const int st = tid - 64;                                    // 0..127 among the softmax threads
-        for (int cid = st; cid < T5_BM * 16; cid += 128) {
-            const int row = cid >> 4, c = cid & 15, rr = row0 + row;
+    } else if (warp < 8) {
+        // ---------------------------------------------------------------- softmax: warpgroup = query tile, thread = row
+        const int g = warp >> 2, q = warp & 3, r_loc = q * 32 + lane, r = row0 + g * T5_BM + r_loc;
+        const int st = tid - g * T5_BM;                             // 0..127 within the warpgroup
+        const int Tq = g == 0 ? Tg[0] : Tg[1], pos_min_g = g == 0 ? pmin[0] : pmin[1], pos_max_g = g == 0 ? pmax[0] : pmax[1];
+        if (Tq > 0) {
+        const uint32_t q_s = q_s0 + g * 2 * T5_HALF;
+        for (int cid = st; cid < T5_BM * 16; cid += T5_BM) {
+            const int row = cid >> 4, c = cid & 15, rr = row0 + g * T5_BM + row;
             const bf16* src = P.q;
             int bytes = 0;
             if (rr < R) {
@@ -279,7 +336,7 @@ __global__ void __launch_bounds__(192, 1) attn_tc5_kernel(const AttnParams P, co
         cp_async_commit();
         cp_async_wait<0>();
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-        mbar_arrive(q_ready);
+        mbar_arrive(q_ready0 + 8 * g);
 
         int rpos = -1, rlo = 0;
         if (r < R) {
@@ -287,24 +344,24 @@ __global__ void __launch_bounds__(192, 1) attn_tc5_kernel(const AttnParams P, co
             rlo = (P.window > 0 && rpos - P.window + 1 > 0) ? rpos - P.window + 1 : 0;
         }
         const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
-        const uint32_t prow0 = p_s0 + (r_loc >> 3) * 1024 + (r_loc & 7) * 128;
+        const uint32_t s_addr = tm_s0 + g * 128 + lane_addr, o_addr = tm_o0 + g * 128 + lane_addr;
         float m_run = -INFINITY, l_run = 0.0f;
         bool ok = true;
-        for (int t = 0; t < T && ok; t++) {
-            if (st == 0) T5_MARK(30, t);
-            if (!mbar_wait(s_full0 + 8 * (t & 1), (t >> 1) & 1, P.err)) { ok = false; break; }
-            if (st == 0) T5_MARK(31, t);
+        for (int t = 0; t < Tq && ok; t++) {
+            if (st == 0) T5_MARK(30 + g, t);
+            // the scores of this tile are complete -- and so is every product issued before them: the output product
+            // of the tile before, which read the probabilities in this buffer and wrote the accumulator
+            if (!mbar_wait(s_full0 + 8 * g, t & 1, P.err)) { ok = false; break; }
+            if (st == 0) T5_MARK(32 + g, t);
             tc_fence_after();
             const int kb = lo_al + t * T5_BN;
-            const bool full_tile = kb + T5_BN - 1 <= pos_min && kb >= ((P.window > 0) ? pos_max - P.window + 1 : 0);
+            const bool full_tile = kb + T5_BN - 1 <= pos_min_g && kb >= ((P.window > 0) ? pos_max_g - P.window + 1 : 0);
             // the row's 128 scores come from tensor memory with four loads and ONE wait (a load and its wait are a round
             // trip of several hundred cycles) and stay in registers for both passes
-            const uint32_t s_addr = tm_s0 + (t & 1) * 128 + lane_addr;
             uint32_t sv[4][32];
 #pragma unroll
             for (int c = 0; c < 4; c++) tmem_ld32(s_addr + c * 32, sv[c]);
             tmem_ld_wait();
-            if (st == 0) T5_MARK(32, t);
             // eight running maxima (and eight partial sums below): one chain of 128 dependent operations would cost
             // its latency 128 times over
             float mxs[8];
@@ -335,57 +392,52 @@ __global__ void __launch_bounds__(192, 1) attn_tc5_kernel(const AttnParams P, co
             const float m_new = (m_run == -INFINITY || mx > m_run + 8.0f) ? fmaxf(m_run, mx) : m_run;
             const float muse = (m_new == -INFINITY) ? 0.0f : m_new;
             const float corr = fast_exp2(m_run - muse);
-            // this tile's P buffer was read by the output product two tiles ago
-            if (t > 1 && !mbar_wait(pv_done0 + 8 * (t & 1), ((t - 2) >> 1) & 1, P.err)) { ok = false; break; }
-            // the output may be touched only when the product before this one is done
-            const bool rescale = t > 0 && __any_sync(0xffffffffu, m_new != m_run);
-            if (rescale && !mbar_wait(pv_done0 + 8 * ((t - 1) & 1), ((t - 1) >> 1) & 1, P.err)) { ok = false; break; }
             // a row whose running maximum moved rescales its lane of the output; the loads and stores are warp-wide
             // instructions, so the whole warp goes when any of its rows has to (the others multiply by one)
+            const bool rescale = t > 0 && __any_sync(0xffffffffu, m_new != m_run);
             if (rescale) {
-                tc_fence_after();
 #pragma unroll 1
                 for (int c = 0; c < 4; c++) {
                     uint32_t ov[32];
-                    tmem_ld32(tm_o + lane_addr + c * 32, ov);
+                    tmem_ld32(o_addr + c * 32, ov);
                     tmem_ld_wait();
 #pragma unroll
                     for (int i = 0; i < 32; i++) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * corr);
-                    tmem_st32(tm_o + lane_addr + c * 32, ov);
+                    tmem_st32(o_addr + c * 32, ov);
                 }
-                tmem_st_wait();
             }
-            if (st == 0) T5_MARK(33 + (rescale ? 100 : 0), t);
+            if (st == 0) T5_MARK(34 + g + (rescale ? 100 : 0), t);
             m_run = m_new;
-            // probabilities = 2^(scale * s - reference), one fused multiply-add and one ex2 each, into the P buffer
+            // probabilities = 2^(scale * s - reference), one fused multiply-add and one ex2 each; as bf16 pairs they go
+            // back into the first 64 columns of the score buffer, where the output product reads them as its A operand
             float sums[8];
 #pragma unroll
             for (int k = 0; k < 8; k++) sums[k] = 0.0f;
-            const uint32_t prow = prow0 + (t & 1) * 2 * T5_HALF;
+            uint32_t pk[2][32];
 #pragma unroll
             for (int c = 0; c < 4; c++) {
 #pragma unroll
-                for (int j = 0; j < 4; j++) {                       // 8 keys = one 16-byte chunk
+                for (int j = 0; j < 4; j++) {                       // 8 keys = four packed columns
                     float pr[8];
 #pragma unroll
                     for (int e = 0; e < 8; e++) {
                         pr[e] = fast_exp2(fmaf(__uint_as_float(sv[c][j * 8 + e]), P.scale_log2, -muse));
                         sums[e] += pr[e];
                     }
-                    const int chunk = c * 4 + j;                    // 0..15 over the 128 keys
-                    const uint32_t dst = prow + (chunk >> 3) * T5_HALF + (((chunk & 7) ^ (r_loc & 7)) << 4);
-                    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(dst), "r"(pack_bf16(pr[0], pr[1])),
-                                 "r"(pack_bf16(pr[2], pr[3])), "r"(pack_bf16(pr[4], pr[5])), "r"(pack_bf16(pr[6], pr[7])) : "memory");
+#pragma unroll
+                    for (int e = 0; e < 4; e++) pk[c >> 1][(c & 1) * 16 + j * 4 + e] = pack_bf16(pr[2 * e], pr[2 * e + 1]);
                 }
+                if (c == 1) tmem_st32(s_addr, pk[0]);
             }
+            tmem_st32(s_addr + 32, pk[1]);
+            tmem_st_wait();
             const float sum = ((sums[0] + sums[1]) + (sums[2] + sums[3])) + ((sums[4] + sums[5]) + (sums[6] + sums[7]));
             l_run = l_run * corr + sum;
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
             tc_fence_before();
-            mbar_arrive(p_full0 + 8 * (t & 1));
-            if (st == 0) T5_MARK(34, t);
+            mbar_arrive(p_full0 + 8 * g);
+            if (st == 0) T5_MARK(36 + g, t);
         }
-        if (ok && mbar_wait(pv_done0 + 8 * ((T - 1) & 1), ((T - 1) >> 1) & 1, P.err)) {
+        if (ok && mbar_wait(o_done0 + 8 * g, 0, P.err)) {
             tc_fence_after();
             const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
             const bool live = r < R;                                // rows past the end take part in the loads only
@@ -393,7 +445,7 @@ __global__ void __launch_bounds__(192, 1) attn_tc5_kernel(const AttnParams P, co
 #pragma unroll 1
             for (int c = 0; c < 4; c++) {
                 uint32_t ov[32];
-                tmem_ld32(tm_o + lane_addr + c * 32, ov);
+                tmem_ld32(o_addr + c * 32, ov);
                 tmem_ld_wait();
                 if (live) {
 #pragma unroll
@@ -408,9 +460,10 @@ __global__ void __launch_bounds__(192, 1) attn_tc5_kernel(const AttnParams P, co
                 }
             }
         }
+        }   // a tile with rows
     }
     }   // units
-    if (warp == 1) {
+    if (warp == 9) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(*tmem_slot), "r"(512u) : "memory");
     }
@@ -464,11 +517,13 @@ static int pool_map(const void* pool, long long rows, int HD, int page, CUtensor
     return 0;
 }
 
+MB_API int mb_attn_tc5_rows() { return T5_ROWS; }
+
 MB_API int mb_attn_tc5_supports(int HD, int page) {
     return HD == 128 && (page == 8 || page == 16 || page == 32 || page == 64 || page == 128);
 }
 
-// items: (sequence, tile of 128 packed rows, 0, 1), heaviest first -- this kernel does not split the keys over blocks.
+// items: (sequence, tile of T5_ROWS = 256 packed rows, 0, 1), heaviest first -- this kernel does not split the keys over blocks.
 // counter: one int of scratch in device memory (the work counter the blocks draw from)
 MB_API int mb_attn_tc5_bf16(const void* q, int q_stride, void* out, const void* kpool, const void* vpool,
                             const void* items, int n_items, const int* q_start, const int* q_len, const int* pos0,
@@ -494,7 +549,7 @@ MB_API int mb_attn_tc5_bf16(const void* q, int q_stride, void* out, const void* 
     if (rc) return rc;
     rc = pool_map(vpool, rows, HD, page, &vmap);
     if (rc) return rc;
-    const size_t smem = 1024 + 6 * T5_HALF + 2 * 2 * T5_TILE + 16 * 8 + 16;
+    const size_t smem = 1024 + T5_QT * 2 * T5_HALF + 4 * T5_TILE + 16 * 8 + 16;
     static bool configured = false;
     static int sms = 0;
     if (!configured) {
@@ -509,20 +564,19 @@ MB_API int mb_attn_tc5_bf16(const void* q, int q_stride, void* out, const void* 
     const int n_units = n_items * KV;
     cudaError_t e = cudaMemsetAsync(counter, 0, sizeof(int), st);       // the work counter starts at zero for every launch
     if (e != cudaSuccess) return (int)e;
-    attn_tc5_kernel<<<n_units < sms ? n_units : sms, 192, smem, st>>>(P, kmap, vmap, n_units, counter);
+    attn_tc5_kernel<<<n_units < sms ? n_units : sms, T5_THREADS, smem, st>>>(P, kmap, vmap, n_units, counter);
     MB_LAUNCH_CHECK();
     return 0;
 }
 
 #ifdef T5_TRACE
+// -> the number of event slots copied (4 roles x 1024); unused slots hold zeros; the device array is cleared
 MB_API int mb_attn_tc5_trace(long long* host, int max_events) {
-    int n = 0;
-    cudaMemcpyFromSymbol(&n, t5_trace_n, sizeof(int));
-    if (n > max_events) n = max_events;
-    if (n > 4096) n = 4096;
+    int n = max_events < 4096 ? max_events : 4096;
     cudaMemcpyFromSymbol(host, t5_trace, (size_t)n * 3 * sizeof(long long));
-    int zero = 0;
-    cudaMemcpyToSymbol(t5_trace_n, &zero, sizeof(int));
+    void* p = nullptr;
+    cudaGetSymbolAddress(&p, t5_trace);
+    cudaMemset(p, 0, sizeof(long long) * 3 * 4096);
     return n;
 }
 #endif

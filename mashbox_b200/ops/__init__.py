@@ -329,9 +329,17 @@ def attention_tc5_supports(HD, page):
     return HD == 128 and page in (8, 16, 32, 64, 128)
 
 
+def attention_tc5_rows():
+    """packed query rows of one work item of the tcgen05 attention kernel"""
+    lib = load_library("attention_tc5")
+    lib.mb_attn_tc5_rows.restype = c_int
+    return lib.mb_attn_tc5_rows()
+
+
 def attention_tc5(q, q_stride, out, kpool, vpool, items, n_items, q_start, q_len, pos0, seq_row, table, H, KV, HD, page,
                   num_pages, window, scale, err):
-    """Prompt-form attention on tcgen05: items are (sequence, tile of 128 packed rows, 0, 1); head size 128."""
+    """Prompt-form attention on tcgen05: items are (sequence, tile of attention_tc5_rows() packed rows, 0, 1); head
+    size 128."""
     _cuda(q, out, kpool, vpool, items, q_start, q_len, pos0, seq_row, table)
     key = str(q.device)
     if key not in _tc5_counters:

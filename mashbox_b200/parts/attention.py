@@ -70,7 +70,8 @@ class Attention:
             "plain_attention", False)
 
     def uses_tc5(self, ctx):
-        """prompt-form tiles go to the tcgen05 kernel (128 packed rows per block, no splits) when it takes the sizes"""
+        """prompt-form tiles go to the tcgen05 kernel (its own number of packed rows per block, no splits) when it takes
+        the sizes"""
         return (ctx.options.get("attention_prefill_kernel", "tc5") == "tc5"
                 and ctx.ops.attention_tc5_supports(self.HD, ctx.cache.page_size))
 
@@ -91,7 +92,7 @@ class Attention:
         max_splits = int(ctx.options.get("attention_max_splits", 32))
         S = ctx.S
         tc5 = self.uses_tc5(ctx)
-        pre_rows = 128 if tc5 else PREFILL_ROWS
+        pre_rows = ctx.ops.attention_tc5_rows() if tc5 else PREFILL_ROWS
         decode_form = [ctx.q_len[s] * G <= DECODE_ROWS for s in range(S)]
         tiles = [1 if decode_form[s] else -(-ctx.q_len[s] * G // pre_rows) for s in range(S)]
         # the two forms are two launches: each is cut into splits by its own number of blocks

@@ -220,7 +220,7 @@ def run_mma(seqs, window, splits, kind="mma"):
     flash = K.attention_mma if kind == "mma" else K.attention_tma
     H, KV, HD, page = seqs.H, seqs.KV, seqs.HD, seqs.page
     Gq = H // KV
-    dec, pre, part_base, part_tok = G.mma_items(seqs, Gq, splits, prefill_rows=128 if kind == "tc5" else 64,
+    dec, pre, part_base, part_tok = G.mma_items(seqs, Gq, splits, prefill_rows=K.attention_tc5_rows() if kind == "tc5" else 64,
                                                 split_prefill=kind != "tc5")
     out = torch.full((seqs.N, H * HD), float("nan"), device=G.DEV, dtype=torch.bfloat16)
     err = K.new_error_word(G.DEV)
@@ -228,7 +228,7 @@ def run_mma(seqs, window, splits, kind="mma"):
     ms = max(splits, 1)
     part_o = torch.full((max(1, n_part) * H * ms, HD), float("nan"), device=G.DEV)
     part_ml = torch.full((max(1, n_part) * H * ms, 2), float("nan"), device=G.DEV)
-    if kind == "tc5" and pre:        # prompt-form tiles of 128 rows on tcgen05; decode-form items stay on the TMA kernel
+    if kind == "tc5" and pre:        # prompt-form tiles on tcgen05; decode-form items stay on the TMA kernel
         K.attention_tc5(seqs.q_dev, H * HD, out, seqs.kpool, seqs.vpool, G.i32(np.asarray(pre).reshape(-1)), len(pre),
                         seqs.q_start, seqs.q_len, seqs.pos0, seqs.seq_row, seqs.table, H, KV, HD, page, seqs.num_pages,
                         window, HD ** -0.5, err)
