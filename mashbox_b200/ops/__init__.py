@@ -341,15 +341,12 @@ def attention_tc5(q, q_stride, out, kpool, vpool, items, n_items, q_start, q_len
     """Prompt-form attention on tcgen05: items are (sequence, tile of attention_tc5_rows() packed rows, 0, 1); head
     size 128."""
     _cuda(q, out, kpool, vpool, items, q_start, q_len, pos0, seq_row, table)
-    key = str(q.device)
-    if key not in _tc5_counters:
-        _tc5_counters[key] = torch.zeros(1, dtype=torch.int32, device=q.device)
     f = _fn("attention_tc5", "mb_attn_tc5_bf16",
             [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-             c_void_p, c_int] + [c_int] * 6 + [c_float, c_void_p, c_void_p, c_void_p])
+             c_void_p, c_int] + [c_int] * 6 + [c_float, c_void_p, c_void_p])
     _check(f(_p(q), q_stride, _p(out), _p(kpool), _p(vpool), _p(items), n_items, _p(q_start), _p(q_len), _p(pos0),
              _p(seq_row), _p(table), table.shape[1], H, KV, HD, page, num_pages, window or 0, float(scale),
-             _p(_tc5_counters[key]), _p(err), _stream()), "attention_tc5")
+             _p(err), _stream()), "attention_tc5")
 
 
 def attention_merge(part_o, part_ml, part_tok, n_part, out, H, HD, max_splits):
