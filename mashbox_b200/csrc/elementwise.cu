@@ -228,6 +228,95 @@ __global__ void rope_kv_write_kernel(T* __restrict__ qkv, const float* __restric
     }
 }
 
+// The same for bf16 with eight values (16 bytes) per thread and the token's cosines and sines computed once per block:
+// HD a multiple of 8, RD a multiple of 16.  A q head that is neither rotated nor biased is left alone; with the halves
+// pairing a thread takes a chunk of the first half together with its partner chunk in the second.
+__global__ void rope_kv_write_vec_kernel(__nv_bfloat16* __restrict__ qkv, const float* __restrict__ bias,
+                                         const int* __restrict__ positions, const int* __restrict__ tok_seq,
+                                         const int* __restrict__ table, int max_blocks, __nv_bfloat16* __restrict__ kpool,
+                                         __nv_bfloat16* __restrict__ vpool, const float* __restrict__ freqs, int H, int KV,
+                                         int HD, int RD, int pairing, int page, int num_pages, int* err) {
+    extern __shared__ float2 rope_cs[];                              // (cos, sin) of the token's RD/2 pairs
+    const int n = blockIdx.x, pos = positions[n];
+    __nv_bfloat16* row = qkv + (size_t)n * (H + 2 * KV) * HD;
+    size_t slot = 0;
+    bool store = kpool != nullptr;
+    if (store) {
+        const int pg = table[(size_t)tok_seq[n] * max_blocks + pos / page];
+        if (pg < 0 || pg >= num_pages) {
+            if (threadIdx.x == 0 && blockIdx.y == 0) mb_set_error(err, pg < 0 ? MB_ERR_PAGE_MISSING : MB_ERR_PAGE_RANGE);
+            store = false;
+        } else {
+            slot = (size_t)pg * KV * page + (pos % page);
+        }
+    }
+    const bool rot = freqs != nullptr;
+    if (rot) {
+        for (int i = threadIdx.x; i < RD / 2; i += blockDim.x) {
+            float s, c;
+            sincosf((float)pos * freqs[i], &s, &c);
+            rope_cs[i] = make_float2(c, s);
+        }
+        __syncthreads();
+    }
+    const int cph = HD / 8, rhalf = RD / 2, total = (H + 2 * KV) * cph;
+    for (int w = threadIdx.x + blockIdx.y * blockDim.x; w < total; w += blockDim.x * gridDim.y) {
+        const int h = w / cph, e0 = (w % cph) * 8;
+        const bool is_q = h < H, is_v = h >= H + KV;
+        const bool rotates = rot && !is_v && e0 < RD;
+        if (is_q ? (!rotates && !bias) : !store) continue;
+        const bool paired = rotates && pairing == 1;
+        if (paired && e0 >= rhalf) continue;                         // done by the thread of the partner chunk
+        __nv_bfloat16* src = row + (size_t)h * HD + e0;
+        __nv_bfloat16* dst = src;
+        if (!is_q) dst = (is_v ? vpool : kpool) + (slot + (size_t)((h - H) % KV) * page) * HD + e0;
+        float a[8], b[8];
+        {
+            const uint4 v = *reinterpret_cast<const uint4*>(src);
+            const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+            for (int i = 0; i < 4; i++) { const float2 x = __bfloat1622float2(p2[i]); a[2 * i] = x.x; a[2 * i + 1] = x.y; }
+        }
+        if (bias) {
+#pragma unroll
+            for (int i = 0; i < 8; i++) a[i] += bias[(size_t)h * HD + e0 + i];
+        }
+        if (paired) {
+            const uint4 v = *reinterpret_cast<const uint4*>(src + rhalf);
+            const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+            for (int i = 0; i < 4; i++) { const float2 x = __bfloat1622float2(p2[i]); b[2 * i] = x.x; b[2 * i + 1] = x.y; }
+            if (bias) {
+#pragma unroll
+                for (int i = 0; i < 8; i++) b[i] += bias[(size_t)h * HD + e0 + rhalf + i];
+            }
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const float2 cs = rope_cs[e0 + i];
+                const float ra = a[i] * cs.x - b[i] * cs.y, rb = a[i] * cs.y + b[i] * cs.x;
+                a[i] = ra; b[i] = rb;
+            }
+            uint4 o;
+            __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+            for (int i = 0; i < 4; i++) o2[i] = __floats2bfloat162_rn(b[2 * i], b[2 * i + 1]);
+            *reinterpret_cast<uint4*>(dst + rhalf) = o;
+        } else if (rotates) {
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float2 cs = rope_cs[e0 / 2 + i];
+                const float ra = a[2 * i] * cs.x - a[2 * i + 1] * cs.y, rb = a[2 * i] * cs.y + a[2 * i + 1] * cs.x;
+                a[2 * i] = ra; a[2 * i + 1] = rb;
+            }
+        }
+        uint4 o;
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int i = 0; i < 4; i++) o2[i] = __floats2bfloat162_rn(a[2 * i], a[2 * i + 1]);
+        *reinterpret_cast<uint4*>(dst) = o;
+    }
+}
+
 // ------------------------------------------------------------------------------------------------ SwiGLU
 // gu[n] = [gate (F) | up (F)] -> out[n, f] = silu(gate) * up
 template <typename T>
@@ -297,6 +386,17 @@ static int rope_kv_write_launch(void* qkv, const float* bias, const int* positio
                                 cudaStream_t st) {
     if (N == 0) return 0;
     if (HD % 2 || RD % 2 || RD > HD || HD / 2 > 1024) return -2;
+    if (sizeof(T) == 2 && HD % 8 == 0 && RD % 16 == 0 && N <= 0x7fffffff / ((H + 2 * KV) * HD) &&
+        (((uintptr_t)qkv | (uintptr_t)kpool | (uintptr_t)vpool) & 15) == 0) {
+        const int items = (H + 2 * KV) * (HD / 8);
+        int split = N >= 512 ? 1 : (items + 255) / 256;
+        if (split > 16) split = 16;
+        rope_kv_write_vec_kernel<<<dim3(N, split), 256, (RD / 2) * sizeof(float2), st>>>(
+            (__nv_bfloat16*)qkv, bias, positions, tok_seq, table, max_blocks, (__nv_bfloat16*)kpool, (__nv_bfloat16*)vpool,
+            freqs, H, KV, HD, RD, pairing, page, num_pages, err);
+        MB_LAUNCH_CHECK();
+        return 0;
+    }
     int threads = 256;
     if (HD / 2 > threads) threads = ((HD / 2 + 31) / 32) * 32;
     const int per = threads / (HD / 2);

@@ -114,7 +114,8 @@ def test_bf16_product_accumulates_in_float32():
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("pairing,HD,RD", [("adjacent", 48, 48), ("adjacent", 32, 16), ("halves", 64, 64), ("halves", 80, 32)])
+@pytest.mark.parametrize("pairing,HD,RD", [("adjacent", 48, 48), ("adjacent", 32, 16), ("halves", 64, 64), ("halves", 80, 32),
+                                           ("adjacent", 20, 12), ("halves", 24, 8), ("halves", 128, 128)])
 def test_rope_and_cache_write(dtype, pairing, HD, RD):
     K = ops()
     g = torch.Generator().manual_seed(5)
@@ -211,7 +212,7 @@ def test_attention_plain_kernel_window_edge(dtype):
 
 
 MMA_CASES = [  # HD, H, KV, page, window, splits
-    (128, 8, 2, 16, None, 1), (128, 8, 2, 16, None, 4), (64, 6, 2, 8, None, 3), (32, 6, 1, 8, 50, 2),
+    (128, 6, 2, 16, None, 1), (128, 5, 5, 32, 300, 1), (128, 8, 2, 16, None, 1), (128, 8, 2, 16, None, 4), (64, 6, 2, 8, None, 3), (32, 6, 1, 8, 50, 2),
     (16, 4, 2, 4, None, 1), (128, 32, 8, 32, 700, 8), (64, 5, 5, 16, None, 2), (128, 16, 1, 16, None, 2)]
 
 
