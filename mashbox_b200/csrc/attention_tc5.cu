@@ -248,6 +248,9 @@ __global__ void __launch_bounds__(T5_THREADS, 1) attn_tc5_kernel(const AttnParam
                    s_full0 = k_full0 + 64, p_full0 = k_full0 + 80, o_done0 = k_full0 + 96, q_ready0 = k_full0 + 112;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#ifdef T5_TRACE
+    if (tid == 0 && blockIdx.x < 256) t5_blocks[768 + blockIdx.x] = t5_now();
+#endif
     if (tid == 8 * 32) {
         asm volatile("prefetch.tensormap [%0];\n" ::"l"(&kmap) : "memory");
         asm volatile("prefetch.tensormap [%0];\n" ::"l"(&vmap) : "memory");
