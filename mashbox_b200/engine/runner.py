@@ -6,8 +6,11 @@ are laid end to end, every kernel runs over all of them, and attention tells the
 descriptors.  Pages are taken from the cache manager before the step and the request's length is committed after it.
 The scheduler, generate() and the trace replay all go through this one function.
 
-Decode-only steps (every entry one token, every token wanted) are captured in CUDA graphs, keyed by the lengths of the
-step's integer arrays, and replayed: the arrays live in one device buffer that is refilled before each replay.
+Steps are captured in CUDA graphs, keyed by the lengths of the step's integer arrays (every launch dimension follows
+from them), and replayed: the arrays live in one device buffer that is refilled before each replay.  A shape is
+captured when it comes a second time -- decode batches, and the equal portions a long prompt is cut into -- and the
+least recently captured graph goes when there are MAX_GRAPHS of them.  Models with a part that does not declare itself
+graph_safe run without graphs.
 """
 import numpy as np
 import torch
@@ -19,6 +22,8 @@ from ..parts import Env, StepContext, StepInputs, Workspace
 
 
 class ModelRunner:
+    MAX_GRAPHS = 64
+
     def __init__(self, model, engine_config, options=None):
         from .loading import torch_dtype
         self.model, self.cfg = model, engine_config
@@ -36,7 +41,8 @@ class ModelRunner:
         self.inputs = StepInputs(self.device)
         self.err = kernels.error_word(self.device)
         self.graphs, self.seen_signatures = {}, {}
-        self.use_graphs = bool(engine_config.cuda_graphs) and not self.options.get("no_graphs", False)
+        self.use_graphs = (bool(engine_config.cuda_graphs) and not self.options.get("no_graphs", False)
+                           and getattr(model, "graph_safe", False))
         self.stats = dict(steps=0, tokens=0, graph_replays=0, graph_captures=0)
 
     # -------------------------------------------------------------------------------------------- the step
@@ -52,8 +58,7 @@ class ModelRunner:
         graph for decode-only steps) and commits the entries.  -> logits"""
         self.inputs.upload()
         self.cache.flush_tables()
-        decode_only = self.use_graphs and ctx.N == ctx.S and ctx.n_out == ctx.S
-        logits = self._run_graph(ctx) if decode_only else self.model.forward(ctx)
+        logits = self._run_graph(ctx) if self.use_graphs else self.model.forward(ctx)
         self.commit(entries)
         return logits
 
@@ -150,6 +155,10 @@ class ModelRunner:
             logits = self.model.forward(ctx)
         captured = kernels.COUNTERS["launches"] - before
         graph.replay()
+        while len(self.graphs) >= self.MAX_GRAPHS:
+            self.graphs.pop(next(iter(self.graphs)))
+        if len(self.seen_signatures) > 64 * self.MAX_GRAPHS:
+            self.seen_signatures = {s: n for s, n in self.seen_signatures.items() if s in self.graphs}
         self.graphs[sig] = (graph, logits, captured)
         self.stats["graph_captures"] += 1
         return logits

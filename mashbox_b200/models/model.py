@@ -16,6 +16,14 @@ class Model:
             if not 0 <= run.layer < len(self.layers):
                 raise ConfigError(f"the schedule names layer {run.layer}, the model has {len(self.layers)}")
         self.hidden, self.vocab = spec.hidden, spec.vocab
+        # A step can be replayed from a captured graph only if no part's forward() looks at host values of the batch
+        # (sequence lengths, positions): parts say so themselves, and one that does not say it keeps graphs off.
+        self.graph_safe = all(getattr(p, "graph_safe", False) for p in self.parts() + self.layers)
+        for b in self.layers:
+            for p in b.parts():
+                pos = getattr(p, "position", None)
+                if pos is not None and not getattr(pos, "graph_safe", False):
+                    self.graph_safe = False
 
     def parts(self):
         out = [self.embedding]

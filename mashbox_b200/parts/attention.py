@@ -23,6 +23,7 @@ DECODE_ROWS, PREFILL_ROWS, KEY_TILE = 16, 64, 64
 
 
 class Attention:
+    graph_safe = True       # forward() depends on the batch only through the lengths of the step's arrays
     def __init__(self, hidden, heads, kv_heads, head_dim, bias=False, position=None, window=None, scale=None,
                  prefix="", names=None):
         self.D, self.H, self.KV, self.HD = int(hidden), int(heads), int(kv_heads), int(head_dim)

@@ -17,6 +17,11 @@ Interfaces (all tensors on the device; N = tokens of the step, D = the part's wi
                 it writes it.
   FeedForward   wants(prefix);  bind;  forward(ctx, h) -> (delta, bias or None)
   Block         built from its parts;  forward(ctx, x, pending, run) -> pending
+
+A part may set the class attribute graph_safe = True: its forward() then reads the batch from the device arrays of
+ctx.inputs only, and everything it decides on the host (which kernels, how many blocks, buffer sizes) follows from the
+LENGTHS of those arrays and from ctx.N, ctx.S, ctx.n_out -- never from ctx.q_len, ctx.pos0 and the other host lists,
+which are for prepare().  Steps of a model whose parts all say so are captured in CUDA graphs and replayed.
 """
 from dataclasses import dataclass, field
 

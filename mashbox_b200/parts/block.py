@@ -8,6 +8,7 @@ from .base import make, register
 
 
 class PreNormBlock:
+    graph_safe = True       # forward() depends on the batch only through the lengths of the step's arrays
     def __init__(self, layer):
         p = layer.prefix
         self.norm1 = make("norm", layer.norm, name=p + "attn_norm.weight")

@@ -5,6 +5,7 @@ from .base import register
 
 
 class Embedding:
+    graph_safe = True       # forward() depends on the batch only through the lengths of the step's arrays
     def __init__(self, vocab, hidden, name="token_embd.weight"):
         self.V, self.D, self.name = int(vocab), int(hidden), name
         self.table = None
@@ -20,6 +21,7 @@ class Embedding:
 
 
 class LinearHead:
+    graph_safe = True       # forward() depends on the batch only through the lengths of the step's arrays
     def __init__(self, vocab, hidden, tied, name="output.weight", tied_to="token_embd.weight"):
         self.V, self.D, self.tied, self.name, self.tied_to = int(vocab), int(hidden), bool(tied), name, tied_to
         self.weight = None

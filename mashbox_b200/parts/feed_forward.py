@@ -5,6 +5,7 @@ from .base import register
 
 
 class SwiGLU:
+    graph_safe = True       # forward() depends on the batch only through the lengths of the step's arrays
     def __init__(self, hidden, intermediate, prefix="", names=None):
         self.D, self.F = int(hidden), int(intermediate)
         n = dict(gate="ffn_gate", up="ffn_up", down="ffn_down")

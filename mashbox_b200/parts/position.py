@@ -40,6 +40,7 @@ def base_frequencies(theta, rotary_dim):
 
 
 class RotaryEncoding:
+    graph_safe = True       # forward() depends on the batch only through the lengths of the step's arrays
     def __init__(self, head_dim, rotary_dim, theta, scaling=None, pairing="adjacent", factors_name=None):
         """scaling: None | ("linear", factor) | ("llama3", factor, low, high, original).  factors_name: canonical name
         of an optional tensor of per-pair divisors that replaces the computed llama3 factors when the file has it."""
