@@ -317,6 +317,20 @@ __global__ void rope_kv_write_vec_kernel(__nv_bfloat16* __restrict__ qkv, const 
     }
 }
 
+// ------------------------------------------------------------------------------------------------ token feedback
+// dst[pairs[2i]] = src[pairs[2i + 1]]: the ids sampled in one step become input tokens of the next without a trip
+// through the host (the next step is laid out and queued while this one still runs).
+__global__ void patch_tokens_kernel(int* __restrict__ dst, const int* __restrict__ src, const int* __restrict__ pairs, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) dst[pairs[2 * i]] = src[pairs[2 * i + 1]];
+}
+MB_API int mb_patch_tokens(int* dst, const int* src, const int* pairs, int n, cudaStream_t st) {
+    if (n <= 0) return 0;
+    patch_tokens_kernel<<<(n + 127) / 128, 128, 0, st>>>(dst, src, pairs, n);
+    MB_LAUNCH_CHECK();
+    return 0;
+}
+
 // ------------------------------------------------------------------------------------------------ SwiGLU
 // gu[n] = [gate (F) | up (F)] -> out[n, f] = silu(gate) * up
 template <typename T>

@@ -19,6 +19,15 @@ from .runner import ModelRunner
 from .scheduler import Scheduler
 
 
+class _Flight:
+    """A step that is queued on the GPU: its plan, the entries that sample, where each sampled token goes in its
+    request's `generated`, the handle of the ids on their way to the host, and the requests that end with this step
+    because they reach max_new."""
+
+    def __init__(self, plan, picks, index, pending, ended):
+        self.plan, self.picks, self.index, self.pending, self.ended = plan, picks, index, pending, ended
+
+
 class Engine:
     def __init__(self, model, engine_config=None, options=None, log=None):
         self.cfg = engine_config or EngineConfig()
@@ -29,8 +38,8 @@ class Engine:
         self.sampler = Sampler(model.vocab, self.cfg.max_requests, self.runner.device)
         self.log = log
         self.counter = 0
-        self._prepared = None          # the next step, planned and laid out while the one before it ran
-        self.stats = dict(steps=0, prompt_tokens=0, generated_tokens=0)
+        self._flight = None            # the step that is queued on the GPU and not booked yet
+        self.stats = dict(steps=0, prompt_tokens=0, generated_tokens=0, deferred=0)
 
     @classmethod
     def from_folder(cls, folder, dtype="bfloat16", device="cuda:0", options=None, log=None, **engine_options):
@@ -61,7 +70,6 @@ class Engine:
         """reqs: list of dict(ids, max_new, samp=None) -> one row per request, in order.  A request that fails
         check() gets a row with finish "error" and the reason in .error, and changes nothing else."""
         from .scheduler import Request
-        self._prepared = None          # a prepared step does not know the new requests
         rows = []
         for q in reqs:
             why = self.check(q)
@@ -77,90 +85,111 @@ class Engine:
         return rows
 
     def busy(self):
-        return self.scheduler.busy()
+        return self.scheduler.busy() or self._flight is not None
 
     def cancel(self, rows):
         for r in rows:
-            self._prepared = None
+            if r.finish is not None:
+                continue
             self.scheduler.cancel(r)
+            while r.generated and r.generated[-1] == self.PLACEHOLDER:      # tokens of steps still in flight: dropped
+                r.generated.pop()
 
-    PLACEHOLDER = -1        # stands for a token that is being sampled while the next step is prepared
+    PLACEHOLDER = -1        # stands for a token that is being sampled while the next step is prepared and queued
 
-    def _prepare(self):
-        """Plans the next step and lays its arrays out on the host.  -> (plan, entries, ctx) or None"""
+    def _prepare(self, before=None):
+        """Plans the next step and lays its arrays out on the host.  -> (plan, entries, ctx), None when nothing is
+        left to run, or DEFER.  before: the step still in flight; a request's token that it is sampling stands in the
+        request as a placeholder, and the plan says where the device has to fill it in.  DEFER: this step cannot be
+        laid out before those ids are on the host (a penalty state would have to be rebuilt from them)."""
         plan = self.scheduler.plan()
         if not plan:
             if self.scheduler.busy():
                 raise RequestError("the scheduler has requests but nothing can run (the cache pool is too small)")
             return None
-        entries = [(p.request.rid, p.request.tokens[p.start:p.start + p.count], [p.count - 1] if p.sample else [])
-                   for p in plan]
-        return plan, entries, self.runner.prepare(entries)
+        source = {id(p.request): j for j, p in enumerate(before.picks)} if before is not None else {}
+        entries, patches, at = [], [], 0
+        for p in plan:
+            r = p.request
+            tokens = r.tokens[p.start:p.start + p.count]
+            last = len(r.prompt) + len(r.generated) - 1
+            if r.generated and r.generated[-1] == self.PLACEHOLDER:
+                if p.sample and r.sampling.penalised and r.needs_penalty_start:
+                    self.stats["deferred"] += 1
+                    return self.DEFER
+                if p.start <= last < p.start + p.count:
+                    patches.append((at + last - p.start, source[id(r)]))
+            entries.append((r.rid, tokens, [p.count - 1] if p.sample else []))
+            at += p.count
+        return plan, entries, self.runner.prepare(entries, patches)
+
+    DEFER = "defer"
+
+    def _launch(self, prep, before=None):
+        """Queues a prepared step and its sampling, and books it with a placeholder for every token being sampled.
+        -> the step in flight."""
+        plan, entries, ctx = prep
+        logits = self.runner.launch(ctx, entries, self.sampler.ret if before is not None else None)
+        picks = [p for p in plan if p.sample]
+        rows = []
+        for p in picks:
+            r = p.request
+            slot = self.cache.get(r.rid).state_slot
+            if r.sampling.penalised and r.needs_penalty_start:
+                self.sampler.start_row(slot, r.prompt, r.generated)
+            r.needs_penalty_start = False
+            rows.append((r.sampling, len(r.generated), slot))
+        pending = self.sampler.sample_async(logits, rows, self.runner.err)
+        ended = self.scheduler.advance(plan, [self.PLACEHOLDER] * len(picks))
+        return _Flight(plan, picks, [len(p.request.generated) - 1 for p in picks], pending, ended)
 
     def step(self):
         """One scheduler step: one batched model step, sampling, bookkeeping.  -> requests that ended.
 
-        The host work of the NEXT step (planning, page bookkeeping, laying out its arrays) is done while the GPU runs
-        this one: the step is booked with a placeholder for every token being sampled, the next step is prepared from
-        that state, and when the sampled ids arrive they are patched into the requests and into the prepared arrays.
-        A sampled stop token is the one thing the placeholder cannot foresee: the request then ends as it should and
-        the prepared step is thrown away."""
+        Two steps are in flight at a time.  A step is queued (model, sampling, the copy of the ids to the host) and
+        booked with a placeholder for every token being sampled; the next step is planned and laid out from that state
+        and queued as well -- the device copies the sampled ids into its input tokens -- and only then does the host
+        wait for the ids of the first, book them and return.  So the GPU never waits for the host between steps.  What
+        a placeholder cannot foresee is a stop token: the request then ends as it should, one step late for the GPU:
+        the step already queued carries a token of it whose result is dropped."""
         try:
-            prep = self._prepared if self._prepared is not None else self._prepare()
-            self._prepared = None
-            if prep is None:
-                return []
-            plan, entries, ctx = prep
-            logits = self.runner.launch(ctx, entries)
-            picks = [p for p in plan if p.sample]
-            rows = []
-            for p in picks:
-                r = p.request
-                slot = self.cache.get(r.rid).state_slot
-                if r.sampling.penalised and r.needs_penalty_start:
-                    self.sampler.start_row(slot, r.prompt, r.generated)
-                r.needs_penalty_start = False
-                rows.append((r.sampling, len(r.generated), slot))
-            pending = self.sampler.sample_async(logits, rows, self.runner.err)
-            # book the step with placeholders and prepare the next one while the GPU works
-            ended = self.scheduler.advance(plan, [self.PLACEHOLDER] * len(picks))
-            nxt = self._prepare() if self.scheduler.busy() else None
-            tokens = self.sampler.wait(pending)
+            if self._flight is None:
+                prep = self._prepare()
+                if prep is None:
+                    return []
+                self._flight = self._launch(prep)
+            cur, nxt = self._flight, None
+            if self.scheduler.busy():
+                prep = self._prepare(cur)
+                if prep is not None and prep is not self.DEFER:
+                    nxt = self._launch(prep, cur)
+            tokens = self.sampler.wait(cur.pending)
         except BaseException:
-            self._prepared = None
+            self._flight = None
             self._drop_live()
             raise
+        self._flight = nxt
         now = time.perf_counter()
-        redo = False
-        for p, t in zip(picks, tokens):
+        ended = list(cur.ended)
+        for p, i, t in zip(cur.picks, cur.index, tokens):
             r = p.request
+            if r.finish not in (None, "length") or i >= len(r.generated):
+                continue                        # cancelled or stopped since the step was queued: the token is dropped
             if r.t_first is None:
                 r.t_first = now
             if t in r.stop_ids:                 # the stop token is not emitted; the request ends here
-                r.generated.pop()
+                del r.generated[i:]             # its placeholder, and that of the step queued after it
                 if r.finish is None:
                     self.scheduler.finish(r, "stop")
                     ended.append(r)
-                    redo = True                 # the prepared step still holds this request
                 else:
                     r.finish = "stop"           # it had also reached max_new: the stop token wins, as in the reference
                 continue
-            r.generated[-1] = t
-        if nxt is not None and not redo:
-            nplan, nentries, nctx = nxt
-            at = 0
-            for p, e in zip(nplan, nentries):
-                r = p.request
-                last = len(r.prompt) + len(r.generated) - 1          # the place of the token sampled just now
-                if p.start <= last < p.start + p.count and e[1][last - p.start] == self.PLACEHOLDER:
-                    self.runner.patch_token(at + last - p.start, r.generated[-1])
-                    e[1][last - p.start] = r.generated[-1]
-                at += p.count
-            self._prepared = nxt
+            r.generated[i] = t
         for r in ended:
             r.t_end = now
         self.stats["steps"] += 1
-        self.stats["prompt_tokens"] += sum(p.count for p in plan if p.count > 1 or not p.sample)
+        self.stats["prompt_tokens"] += sum(p.count for p in cur.plan if p.count > 1 or not p.sample)
         self.stats["generated_tokens"] += len(tokens)
         return ended
 
@@ -194,7 +223,9 @@ class Engine:
             self.step()
             calls += 1
             if on_step is not None:
-                self.cancel([rows[i] for i in on_step([r.generated for r in rows], [r.finish for r in rows]) or ()])
+                seen = [r.generated[:-1] if r.generated and r.generated[-1] == self.PLACEHOLDER else r.generated
+                        for r in rows]
+                self.cancel([rows[i] for i in on_step(seen, [r.finish for r in rows]) or ()])
         t2 = time.perf_counter()
         t1 = max([r.t_first for r in rows if r.t_first is not None] or [t2])
         return dict(ids=[list(r.generated) for r in rows], finish=[r.finish for r in rows],

@@ -53,10 +53,17 @@ class ModelRunner:
             return None
         return self.launch(self.prepare(entries), entries)
 
-    def launch(self, ctx, entries):
+    def launch(self, ctx, entries, sampled=None):
         """Sends a prepared step's arrays and the changed block-table entries to the device, runs the model (a captured
-        graph for decode-only steps) and commits the entries.  -> logits"""
+        graph when the shape has come before) and commits the entries.  -> logits.  sampled: the device tensor of the
+        ids sampled by the step before, for the (place, index) pairs given to prepare(): they are copied into the
+        step's tokens on the device, so this step can be queued before those ids have reached the host."""
         self.inputs.upload()
+        pairs = self.inputs.get("patch")
+        if pairs is not None:
+            if sampled is None:
+                raise RequestError("the step has tokens to be filled in on the device, but no sampled ids were given")
+            kernels.patch_tokens(self.inputs.get("token_ids"), sampled, pairs, pairs.numel() // 2)
         self.cache.flush_tables()
         logits = self._run_graph(ctx) if self.use_graphs else self.model.forward(ctx)
         self.commit(entries)
@@ -69,10 +76,12 @@ class ModelRunner:
         self.cache.flush_tables()
         return ctx
 
-    def prepare(self, entries):
+    def prepare(self, entries, patches=()):
         """Takes the pages the entries need, lays the step's integer arrays out on the host and lets the mixers plan.
         Nothing is sent to the device yet, so a step can be prepared while the step before it still runs, and token
-        ids that are not known yet can be patched in (patch_token) before launch().  -> StepContext"""
+        ids that are not known yet can be patched in on the host (patch_token) before launch(), or on the device:
+        patches = (place among the step's tokens, index among the ids the step before samples) pairs.
+        -> StepContext"""
         cache = self.cache
         seen = set()
         need = [0] * len(cache.groups)
@@ -122,6 +131,7 @@ class ModelRunner:
         inp.add("pos0", pos0)
         inp.add("seq_row", rows)
         inp.add("state_slot", ctx.state_slots)
+        inp.add("patch", np.asarray([v for pair in patches for v in pair], np.int32))
         self.model.prepare(ctx)
         return ctx
 

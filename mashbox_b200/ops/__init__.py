@@ -131,6 +131,13 @@ def rope_kv_write(qkv, bias, positions, tok_seq, table, kpool, vpool, freqs, H, 
              N, H, KV, HD, RD, pairing, page, num_pages, _p(err), _stream()), "rope_kv_write")
 
 
+def patch_tokens(dst, src, pairs, n):
+    """dst[pairs[2i]] = src[pairs[2i+1]] for i < n (int32 tensors on the device)"""
+    _cuda(dst, src, pairs)
+    f = _fn("elementwise", "mb_patch_tokens", [c_void_p, c_void_p, c_void_p, c_int, c_void_p])
+    _check(f(_p(dst), _p(src), _p(pairs), int(n), _stream()), "patch_tokens")
+
+
 def swiglu(gu, out):
     """gu (N, 2F) = [gate | up] -> out (N, F) = silu(gate) * up"""
     _cuda(gu, out)

@@ -94,6 +94,8 @@ def test_pages_run_out_preemption_keeps_the_answers(tmp_path_factory, mode):
     tmp = tmp_path_factory.mktemp("m")
     prompts = H.prompts_for("A", (20, 24, 17, 30), seed=6)
     samp = [dict(temperature=0.7, seed=11 + i) for i in range(4)]
+    samp[1]["repetition_penalty"] = 1.3          # its penalty state is rebuilt after a preemption: that step waits for
+    samp[3]["frequency_penalty"] = 0.4           # the ids still in flight instead of being queued ahead
     _, roomy = engine(tmp, "A", mode, max_tokens=1024)
     want = roomy.generate(prompts, max_new=40, samp=samp)
     assert want["preemptions"] == [0, 0, 0, 0]
@@ -115,6 +117,60 @@ def test_pages_run_out_preemption_keeps_the_answers(tmp_path_factory, mode):
     while tight.busy():
         tight.step()
     assert rows[1].finish == "length" and len(rows[1].generated) == 2
+
+
+def test_stop_tokens_while_the_next_step_is_already_queued(tmp_path_factory):
+    """Two steps are in flight, so a stop token is seen one step late: the request must still end exactly there, the
+    token queued after it must be dropped, a request waiting for its slot must come in, and nothing may leak.  One
+    request stops on its first token, one on the token that is also its max_new-th, one in the middle, one never."""
+    _, eng = engine(tmp_path_factory.mktemp("m"), "A", "f32", max_requests=2)
+    prompts = H.prompts_for("A", (9, 14, 6, 11), seed=12)
+    # tokens that differ from step to step make the test sharper than greedy loops: sample with fixed seeds
+    samp = [dict(temperature=0.9, seed=40 + i) for i in range(4)]
+    free = eng.generate(prompts, max_new=24, samp=samp)
+    assert free["finish"] == ["length"] * 4
+    stops = [free["ids"][0][7], free["ids"][1][23], None, free["ids"][3][0]]
+    reqs = [dict(ids=p, max_new=24, samp=s, stop_ids=() if st is None else (st,)) for p, s, st in zip(prompts, samp, stops)]
+    rows = eng.admit(reqs)
+    ended, calls = [], 0
+    while eng.busy():
+        ended += eng.step()
+        calls += 1
+        assert calls < 400
+    assert sorted(id(r) for r in ended) == sorted(id(r) for r in rows)
+    for r, ids, st in zip(rows, free["ids"], stops):
+        want = ids if st is None else ids[:ids.index(st)]
+        assert r.generated == want and r.finish == ("length" if st is None else "stop"), (r.generated, want, r.finish)
+        assert -1 not in r.generated
+    eng.cache.check()
+    assert eng.cache.free_pages() == [eng.cache.num_pages]
+    # and again through generate(), with a token every request stops on somewhere or never
+    common = free["ids"][2][10]
+    cut = eng.generate(prompts, max_new=24, samp=samp, stop_ids=(common,))
+    for got, ids, fin in zip(cut["ids"], free["ids"], cut["finish"]):
+        want = ids[:ids.index(common)] if common in ids else ids
+        assert got == want and fin == ("stop" if common in ids else "length")
+    assert eng.cache.free_pages() == [eng.cache.num_pages]
+
+
+def test_a_step_that_needs_ids_still_in_flight_waits_for_them(tmp_path_factory):
+    """A request whose penalty state has to be rebuilt (what a preemption leaves behind) while its newest token is still
+    being sampled cannot be queued ahead: the engine books the step in flight first.  The answer does not change."""
+    _, eng = engine(tmp_path_factory.mktemp("m"), "A", "f32")
+    prompt = H.prompts_for("A", (8,), seed=3)[0]
+    samp = dict(temperature=0.8, seed=5, repetition_penalty=1.4, presence_penalty=0.3)
+    want = eng.generate([prompt], max_new=20, samp=[samp])["ids"][0]
+    assert eng.stats["deferred"] == 0
+    rows = eng.admit([dict(ids=prompt, max_new=20, samp=samp)])
+    marked = set()
+    while eng.busy():
+        n = len(rows[0].generated)
+        if n in (5, 11) and n not in marked:
+            marked.add(n)
+            rows[0].needs_penalty_start = True
+        eng.step()
+    assert rows[0].generated == want and eng.stats["deferred"] == 2
+    assert eng.cache.free_pages() == [eng.cache.num_pages]
 
 
 def test_cancel_through_on_step(tmp_path_factory):
