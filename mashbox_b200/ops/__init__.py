@@ -169,8 +169,8 @@ def linear(a, w, out=None, out_dtype=None):
         want = a.dtype if out_dtype is None else out_dtype
         if out is None:
             out = torch.empty((N, M), dtype=want, device=a.device)
-        if out.is_contiguous() and out.dtype == want and want in (torch.bfloat16, torch.float32):
-            return linear_gemv(a, w, out, "plain" if want == torch.bfloat16 else "float")
+        if out.is_contiguous() and out.dtype == want and want == torch.bfloat16:      # the output head stays with the library
+            return linear_gemv(a, w, out, "plain")
     if stream_supports(N, K) and a.is_contiguous() and w.is_contiguous() and a.dtype == torch.bfloat16 and M % 8 == 0:
         want = a.dtype if out_dtype is None else out_dtype
         if out is None:
@@ -209,14 +209,16 @@ def linear_tc5(a, w, out, mode="plain"):
     return out
 
 
-# Matrix-vector products for decode steps of at most 4 tokens (one warp per two rows of W, no tensor core).  Measured at
-# one token on the Llama-3.1-8B shapes: the fused gate/up form reads W at 5.8 TB/s and saves the separate gate kernel
-# (40.4 us against 40.6 + 2.5 us), the plain form loses to the library on the small matrices (3.6 against 4.3 TB/s).
-GEMV = {"swiglu": True, "plain": False}
+# Matrix-vector products (one warp per two rows of W, or a block per two long rows; no tensor core): the kernels take up
+# to 4 tokens, the engine uses them where they beat the library, which is at ONE token.  Measured inside captured
+# graphs on the Llama-3.1-8B shapes at one token, own / library: output product 10.8 / 13.0 us, QKV 12.2 / 11.7, down
+# 21.2 / 24.9, fused gate/up + SwiGLU 39.0 / 39.2 + 2.3; at two tokens the arithmetic (bf16 to float conversions on
+# the FMA pipe) already costs more than the stream.  GEMV[mode] = the most tokens the engine gives the kernel (0: never).
+GEMV = {"swiglu": 1, "plain": 1}
 
 
 def gemv_supports(N, K, mode="plain"):
-    return GEMV["swiglu" if mode == "swiglu" else "plain"] and 1 <= N <= 4 and K >= 8 and K % 8 == 0
+    return 1 <= N <= min(4, GEMV["swiglu" if mode == "swiglu" else "plain"]) and K >= 8 and K % 8 == 0
 
 
 def linear_gemv(a, w, out, mode="plain"):

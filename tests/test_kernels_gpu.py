@@ -447,7 +447,7 @@ def test_tcgen05_product(N, M, K):
         K_.linear_tc5(a[:, :K - 4].contiguous(), w[:, :K - 4].contiguous(), out, "plain")
 
 
-@pytest.mark.parametrize("N,M,K", [(1, 4096, 4096), (4, 6144, 4096), (2, 509, 320), (3, 4096, 14336), (1, 57, 72)])
+@pytest.mark.parametrize("N,M,K", [(1, 4096, 4096), (4, 6144, 4096), (2, 509, 320), (3, 4096, 14336), (1, 57, 72), (2, 37, 8200)])
 def test_matrix_vector_product(N, M, K):
     """at most 4 tokens: one warp per two rows of W, float32 sums; plain, float32 out and fused SwiGLU"""
     K_ = ops()
