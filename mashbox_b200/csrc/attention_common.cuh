@@ -14,6 +14,7 @@ struct AttnParams {
     const int* seq_row;                     // row of the block table of each sequence
     const int* table; int max_blocks;
     float* part_o; float* part_ml; int max_splits;
+    int* counters;                          // one per (first item of a split group, kv head), zero between launches; or null
     int H, KV, G, page, num_pages, window;
     int page_shift;                         // log2(page) when the page size is a power of two, else -1
     float scale_log2;

@@ -691,7 +691,7 @@ MB_API int mb_attn_tc5_bf16(const void* q, int q_stride, void* out, const void* 
     P.items = (const int4*)items;
     P.q_start = q_start; P.q_len = q_len; P.pos0 = pos0; P.part_base = nullptr; P.seq_row = seq_row;
     P.table = table; P.max_blocks = max_blocks;
-    P.part_o = nullptr; P.part_ml = nullptr; P.max_splits = 1;
+    P.part_o = nullptr; P.part_ml = nullptr; P.max_splits = 1; P.counters = nullptr;
     P.H = H; P.KV = KV; P.G = H / KV; P.page = page; P.num_pages = num_pages; P.window = window;
     P.page_shift = -1;
     for (int sft = 0; sft < 31; sft++) if ((1 << sft) == page) P.page_shift = sft;

@@ -318,6 +318,67 @@ __global__ void __launch_bounds__(160, 2) attn_tma_kernel(const AttnParams P, co
             }
         }
     }
+    // The splits of a tile are merged by whichever of their blocks finishes last: every block publishes its partial
+    // result, then draws a ticket; the one that draws the last ticket reads all of them back (in the order of the
+    // splits, so the sum does not depend on who came last), writes the rows and sets the counter back to zero for the
+    // next launch.  Without counters a separate kernel does the merge.
+    if (n_splits > 1 && P.counters != nullptr) {
+        int* flag = reinterpret_cast<int*>(bars + 2 * STAGES);
+        __threadfence();
+        consumer_sync();
+        if (tid == 0) {
+            int* counter = P.counters + (size_t)(blockIdx.x - split) * P.KV + kvh;
+            const int ticket = atomicAdd(counter, 1);
+            *flag = ticket == n_splits - 1;
+            if (ticket == n_splits - 1) *counter = 0;
+        }
+        consumer_sync();
+        if (*flag) {
+            __threadfence();
+            // the K/V stages are free by now: the splits' (maximum, sum) pairs go there, then their weights
+            float* sm_w = reinterpret_cast<float*>(kvs);              // [rows][n_splits]: maxima, then weights 2^(m - M)
+            float* sm_l = sm_w + BM * n_splits;                       // [rows][n_splits]: sums
+            float* sm_tot = sm_l + BM * n_splits;                     // [rows]: the total of a row
+            const int rows = min(BM, R - row0);
+            for (int i = tid; i < rows * n_splits; i += 128) {
+                const int r = row0 + i / n_splits, s = i % n_splits;
+                const size_t base = ((size_t)(P.part_base[seq] + r / G) * H + kvh * G + r % G) * P.max_splits + s;
+                const float2 ml = __ldcg(reinterpret_cast<const float2*>(P.part_ml + base * 2));
+                sm_w[i] = ml.x;
+                sm_l[i] = ml.y;
+            }
+            consumer_sync();
+            if (tid < rows) {
+                float M = -INFINITY, L = 0.0f;
+                for (int s = 0; s < n_splits; s++) M = fmaxf(M, sm_w[tid * n_splits + s]);
+                for (int s = 0; s < n_splits; s++) {
+                    const float ms = sm_w[tid * n_splits + s];
+                    const float sc = (ms == -INFINITY) ? 0.0f : exp2f(ms - M);
+                    sm_w[tid * n_splits + s] = sc;
+                    L += sm_l[tid * n_splits + s] * sc;
+                }
+                sm_tot[tid] = L;
+            }
+            consumer_sync();
+            for (int it = tid; it < rows * (HD / 4); it += 128) {
+                const int row = it / (HD / 4), d = (it % (HD / 4)) * 4, r = row0 + row;
+                const int tq = r / G, h = kvh * G + r % G;
+                const float* src = P.part_o + ((size_t)(P.part_base[seq] + tq) * H + h) * P.max_splits * HD + d;
+                float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll 8
+                for (int s = 0; s < n_splits; s++) {                  // in the order of the splits, whoever came last
+                    const float4 v = __ldcg(reinterpret_cast<const float4*>(src + (size_t)s * HD));
+                    const float sc = sm_w[row * n_splits + s];
+                    acc.x += v.x * sc; acc.y += v.y * sc; acc.z += v.z * sc; acc.w += v.w * sc;
+                }
+                const float L = sm_tot[row], inv = L > 0.0f ? 1.0f / L : 0.0f;
+                uint2 o;
+                o.x = pack_bf16(acc.x * inv, acc.y * inv);
+                o.y = pack_bf16(acc.z * inv, acc.w * inv);
+                *reinterpret_cast<uint2*>(P.out + ((size_t)(tok0 + tq) * H + h) * HD + d) = o;
+            }
+        }
+    }
 }
 
 // ------------------------------------------------------------------------------------------------ host side
@@ -373,7 +434,7 @@ static int pool_map(const void* pool, long long rows, int HD, int page, CUtensor
 template <int HD, bool DECODE, int STAGES>
 static int launch_tma(const AttnParams& P, const CUtensorMap& kmap, const CUtensorMap& vmap, int n_items, cudaStream_t st) {
     constexpr int BM = DECODE ? 16 : 64;
-    const size_t smem = 1024 + (size_t)STAGES * 2 * 64 * HD * 2 + (size_t)BM * HD * 2 + 2 * STAGES * 8;
+    const size_t smem = 1024 + (size_t)STAGES * 2 * 64 * HD * 2 + (size_t)BM * HD * 2 + 2 * STAGES * 8 + 16;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_tma_kernel<HD, DECODE, STAGES>,
@@ -397,7 +458,7 @@ MB_API int mb_attn_tma_bf16(const void* q, int q_stride, void* out, const void* 
                             const void* items, int n_items, int decode, const int* q_start, const int* q_len,
                             const int* pos0, const int* part_base, const int* seq_row, const int* table, int max_blocks,
                             float* part_o, float* part_ml, int max_splits, int H, int KV, int HD, int page, int num_pages,
-                            int window, float scale, int* err, cudaStream_t st) {
+                            int window, float scale, int* counters, int* err, cudaStream_t st) {
     if (n_items == 0) return 0;
     if (!mb_attn_tma_supports(HD, page) || KV < 1 || H % KV || KV > 65535) return -2;
     AttnParams P;
@@ -406,7 +467,7 @@ MB_API int mb_attn_tma_bf16(const void* q, int q_stride, void* out, const void* 
     P.items = (const int4*)items;
     P.q_start = q_start; P.q_len = q_len; P.pos0 = pos0; P.part_base = part_base; P.seq_row = seq_row;
     P.table = table; P.max_blocks = max_blocks;
-    P.part_o = part_o; P.part_ml = part_ml; P.max_splits = max_splits;
+    P.part_o = part_o; P.part_ml = part_ml; P.max_splits = max_splits; P.counters = counters;
     P.H = H; P.KV = KV; P.G = H / KV; P.page = page; P.num_pages = num_pages; P.window = window;
     P.page_shift = -1;
     for (int sft = 0; sft < 31; sft++) if ((1 << sft) == page) P.page_shift = sft;

@@ -316,22 +316,38 @@ def attention_tma_supports(HD, page):
     return HD in (64, 128) and page in (8, 16, 32, 64)
 
 
+_merge_counters = {}
+MERGE_COUNTERS = 1 << 16
+
+
+def attention_tma_merges(n_items, KV):
+    """True when attention_tma can merge the splits of its items itself (it has a counter for every group)"""
+    return n_items * KV <= MERGE_COUNTERS
+
+
 def attention_tma(q, q_stride, out, kpool, vpool, items, n_items, decode, q_start, q_len, pos0, part_base, seq_row,
-                  table, part_o, part_ml, max_splits, H, KV, HD, page, num_pages, window, scale, err):
-    """The same contract as attention_mma, with K/V tiles loaded by TMA (head sizes 64 and 128, pages of 8 to 64)."""
+                  table, part_o, part_ml, max_splits, H, KV, HD, page, num_pages, window, scale, err, merge=False):
+    """The same contract as attention_mma, with K/V tiles loaded by TMA (head sizes 64 and 128, pages of 8 to 64).
+    merge: the last block of every split group merges the group's partial results and writes `out`, so no
+    attention_merge is needed afterwards (only when attention_tma_merges(n_items, KV))."""
     _cuda(q, out, kpool, vpool, items, q_start, q_len, pos0, part_base, table, part_o, part_ml)
+    counters = None
+    if merge:
+        if not attention_tma_merges(n_items, KV):
+            raise KernelError("attention_tma: more split groups than merge counters")
+        key = str(q.device)
+        if key not in _merge_counters:
+            _merge_counters[key] = torch.zeros(MERGE_COUNTERS, dtype=torch.int32, device=q.device)
+        counters = _merge_counters[key]
     f = _fn("attention_tma", "mb_attn_tma_bf16",
             [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
-             c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p] + [c_int] * 7 + [c_float, c_void_p, c_void_p])
+             c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p] + [c_int] * 7 + [c_float, c_void_p, c_void_p, c_void_p])
     code = f(_p(q), q_stride, _p(out), _p(kpool), _p(vpool), _p(items), n_items, 1 if decode else 0, _p(q_start),
              _p(q_len), _p(pos0), _p(part_base), _p(seq_row), _p(table), table.shape[1], _p(part_o), _p(part_ml),
-             max_splits, H, KV, HD, page, num_pages, window or 0, float(scale), _p(err), _stream())
+             max_splits, H, KV, HD, page, num_pages, window or 0, float(scale), _p(counters), _p(err), _stream())
     if code == -6:
         raise KernelError("attention_tma: the driver refused the tensor map of the cache pool")
     _check(code, "attention_tma")
-
-
-_tc5_counters = {}
 
 
 def attention_tc5_supports(HD, page):

@@ -158,7 +158,12 @@ class Attention:
                 part_o = ctx.ws.get("attn_part_o", n_part * H * ms, (HD,), torch.float32, reserve=0)
                 part_ml = ctx.ws.get("attn_part_ml", n_part * H * ms, (2,), torch.float32, reserve=0)
             kind = ctx.options.get("attention_kernel", "tma")
-            flash = ops.attention_tma if kind == "tma" and ops.attention_tma_supports(HD, page) else ops.attention_mma
+            tma = kind == "tma" and ops.attention_tma_supports(HD, page)
+            flash = ops.attention_tma if tma else ops.attention_mma
+            # the TMA kernel merges the splits itself (the last block of a group does it); the other needs the merge kernel
+            fused = (tma and n_part > 0 and ctx.options.get("attention_fused_merge", True)
+                     and ops.attention_tma_merges(max(plan["n_pre"], plan["n_dec"]), KV))
+            extra = dict(merge=True) if fused else {}
             if plan["tc5"] and plan["n_pre"]:
                 ops.attention_tc5(qkv, width, out, kpool, vpool, ctx.dev(nm + "pre"), plan["n_pre"], ctx.dev("q_start"),
                                   ctx.dev("q_len"), ctx.dev("pos0"), ctx.dev("seq_row"), table, H, KV, HD, page, pages,
@@ -168,8 +173,8 @@ class Attention:
                 if n_items:
                     flash(qkv, width, out, kpool, vpool, ctx.dev(form), n_items, decode, ctx.dev("q_start"),
                           ctx.dev("q_len"), ctx.dev("pos0"), ctx.dev(nm + "part_base"), ctx.dev("seq_row"),
-                          table, part_o, part_ml, ms, H, KV, HD, page, pages, self.window, self.scale, ctx.err)
-            if n_part:
+                          table, part_o, part_ml, ms, H, KV, HD, page, pages, self.window, self.scale, ctx.err, **extra)
+            if n_part and not fused:
                 ops.attention_merge(part_o, part_ml, ctx.dev(nm + "part_tok"), n_part, out, H, HD, ms)
         else:
             ops.attention_simple(qkv, width, out, ctx.dev("positions"), ctx.dev("tok_row"), table, kpool, vpool, H, KV,

@@ -234,18 +234,19 @@ def run_mma(seqs, window, splits, kind="mma"):
                         seqs.q_start, seqs.q_len, seqs.pos0, seqs.seq_row, seqs.table, H, KV, HD, page, seqs.num_pages,
                         window, HD ** -0.5, err)
         pre = []
+    extra = dict(merge=True) if kind == "tma-merging" else {}
     for items, decode in ((pre, False), (dec, True)):
         if items:
             flash(seqs.q_dev, H * HD, out, seqs.kpool, seqs.vpool, G.i32(np.asarray(items).reshape(-1)),
                   len(items), decode, seqs.q_start, seqs.q_len, seqs.pos0, G.i32(part_base), seqs.seq_row,
-                  seqs.table, part_o, part_ml, ms, H, KV, HD, page, seqs.num_pages, window, HD ** -0.5, err)
-    if n_part:
+                  seqs.table, part_o, part_ml, ms, H, KV, HD, page, seqs.num_pages, window, HD ** -0.5, err, **extra)
+    if n_part and not extra:
         K.attention_merge(part_o, part_ml, G.i32(part_tok), n_part, out, H, HD, ms)
     K.check_error_word(err)
     return out
 
 
-@pytest.mark.parametrize("kind", ["mma", "tma", "tc5"])
+@pytest.mark.parametrize("kind", ["mma", "tma", "tma-merging", "tc5"])
 @pytest.mark.parametrize("HD,H,KV,page,window,splits", MMA_CASES)
 def test_attention_tensor_core_kernel(HD, H, KV, page, window, splits, kind):
     """prompt portions (one starting at position 0, one in the middle of a long context), single decode tokens with
@@ -257,7 +258,7 @@ def test_attention_tensor_core_kernel(HD, H, KV, page, window, splits, kind):
     seqs.round().build()
     if kind == "tc5" and not ops().attention_tc5_supports(HD, page):
         pytest.skip("the tcgen05 kernel takes head size 128 only")
-    if kind == "tma" and not ops().attention_tma_supports(HD, page):
+    if kind.startswith("tma") and not ops().attention_tma_supports(HD, page):
         with pytest.raises(Exception, match="does not take these sizes"):
             run_mma(seqs, window, splits, kind)
         return
@@ -267,7 +268,7 @@ def test_attention_tensor_core_kernel(HD, H, KV, page, window, splits, kind):
     assert float((out[0].double().cpu() - want).abs().max()) < 0.05 * float(want.abs().max()) + 1e-2
 
 
-@pytest.mark.parametrize("kind,HD", [("mma", 64), ("tma", 64), ("tma", 128), ("tc5", 128)])
+@pytest.mark.parametrize("kind,HD", [("mma", 64), ("tma", 64), ("tma", 128), ("tma-merging", 128), ("tc5", 128)])
 @pytest.mark.parametrize("splits", [1, 4])
 def test_attention_tensor_core_kernel_window_edge(splits, kind, HD):
     H, KV, page, window = 8, 2, 16, 130
