@@ -32,14 +32,75 @@ __device__ __forceinline__ float dot8(const uint4& w, const uint4& x, float acc)
     return acc;
 }
 
-// NT tokens (1..4).  MODE 0: bf16 out (N, M); 1: SwiGLU, W has 2 * M rows, bf16 out (N, M); 2: float out.
-template <int NT, int MODE>
+// What a decode step of one token is made of beside the products is folded into them, so that a layer is six kernels
+// instead of ten:
+//   NORM   the activations are not read but made: every block normalises the token's row of the float32 residual
+//          stream (x * rsqrt(mean(x^2) + eps) * w, as the norm kernel does, rounded to bf16) into shared memory once
+//          and then walks its share of the rows of W;
+//   MODE 3 the product is added into the float32 residual stream in place (plus a bias), every element by the one
+//          thread that owns it.
+struct GemvNorm { const float* x; const float* w; float eps; };
+
+// the activations: from global memory through the read-only path, or from the block's shared memory
+template <bool SHARED> __device__ __forceinline__ uint4 gv_act(const bf16* p) {
+    return SHARED ? *reinterpret_cast<const uint4*>(p) : __ldg(reinterpret_cast<const uint4*>(p));
+}
+
+__device__ __forceinline__ void gv_load8(const float* p, float (&v)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+
+// NT tokens (1..4).  MODE 0: bf16 out (N, M); 1: SwiGLU, W has 2 * M rows, bf16 out (N, M); 2: float out; 3: out is
+// the float32 residual stream (N, M), added to.
+template <int NT, int MODE, bool NORM>
 __global__ void __launch_bounds__(GV_WARPS * 32) gemv_kernel(const bf16* __restrict__ act, const bf16* __restrict__ W,
-                                                             void* __restrict__ out, int M, int K) {
+                                                             void* __restrict__ out, int M, int K, GemvNorm nrm,
+                                                             const float* __restrict__ bias) {
+    extern __shared__ __align__(16) unsigned char gv_smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int unit = blockIdx.x * GV_WARPS + warp;                   // MODE 1: one feature (two rows); else two rows
-    const int m0 = MODE == 1 ? unit : unit * GV_ROWS;
-    if (m0 >= M) return;
+    if (NORM) {
+        __shared__ float scratch[32];
+        bf16* hs = reinterpret_cast<bf16*>(gv_smem);                 // [NT][K]
+        const int chunks8 = K / 8;
+#pragma unroll
+        for (int n = 0; n < NT; n++) {
+            float v[4][8];                                           // K <= 8,192: at most four chunks of eight per thread
+            float ss = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int c = threadIdx.x + j * GV_WARPS * 32;
+                if (c < chunks8) {
+                    gv_load8(nrm.x + (size_t)n * K + c * 8, v[j]);
+#pragma unroll
+                    for (int e = 0; e < 8; e++) ss = fmaf(v[j][e], v[j][e], ss);
+                }
+            }
+            ss = mb_block_sum(ss, scratch);
+            const float inv = rsqrtf(ss / (float)K + nrm.eps);
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int c = threadIdx.x + j * GV_WARPS * 32;
+                if (c < chunks8) {
+                    float g[8];
+                    gv_load8(nrm.w + c * 8, g);
+                    uint4 o;
+                    uint32_t* ow = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        const __nv_bfloat162 p = __floats2bfloat162_rn(v[j][2 * e] * inv * g[2 * e], v[j][2 * e + 1] * inv * g[2 * e + 1]);
+                        ow[e] = *reinterpret_cast<const uint32_t*>(&p);
+                    }
+                    *reinterpret_cast<uint4*>(hs + (size_t)n * K + c * 8) = o;
+                }
+            }
+        }
+        __syncthreads();
+        act = hs;
+    }
+    const int units = MODE == 1 ? M : (M + GV_ROWS - 1) / GV_ROWS;
+    for (int unit = blockIdx.x * GV_WARPS + warp; unit < units; unit += gridDim.x * GV_WARPS) {
+    const int m0 = MODE == 1 ? unit : unit * GV_ROWS;               // MODE 1: one feature (two rows); else two rows
     const bf16* rows[GV_ROWS];
     rows[0] = W + (size_t)m0 * K;
     rows[1] = MODE == 1 ? W + (size_t)(M + m0) * K : W + (size_t)min(m0 + 1, M - 1) * K;
@@ -62,7 +123,7 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_kernel(const bf16* __restr
         for (int u = 0; u < 8; u++)
 #pragma unroll
             for (int n = 0; n < NT; n++) {
-                const uint4 x = __ldg(reinterpret_cast<const uint4*>(act + (size_t)n * K + (size_t)(c + 32 * u) * 8));
+                const uint4 x = gv_act<NORM>(act + (size_t)n * K + (size_t)(c + 32 * u) * 8);
 #pragma unroll
                 for (int r = 0; r < GV_ROWS; r++) acc[r][n] = dot8(w[u][r], x, acc[r][n]);
             }
@@ -77,7 +138,7 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_kernel(const bf16* __restr
         for (int u = 0; u < 4; u++)
 #pragma unroll
             for (int n = 0; n < NT; n++) {
-                const uint4 x = __ldg(reinterpret_cast<const uint4*>(act + (size_t)n * K + (size_t)(c + 32 * u) * 8));
+                const uint4 x = gv_act<NORM>(act + (size_t)n * K + (size_t)(c + 32 * u) * 8);
 #pragma unroll
                 for (int r = 0; r < GV_ROWS; r++) acc[r][n] = dot8(w[u][r], x, acc[r][n]);
             }
@@ -88,7 +149,7 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_kernel(const bf16* __restr
         for (int r = 0; r < GV_ROWS; r++) w[r] = ld_stream16(rows[r] + (size_t)c * 8);
 #pragma unroll
         for (int n = 0; n < NT; n++) {
-            const uint4 x = __ldg(reinterpret_cast<const uint4*>(act + (size_t)n * K + (size_t)c * 8));
+            const uint4 x = gv_act<NORM>(act + (size_t)n * K + (size_t)c * 8);
 #pragma unroll
             for (int r = 0; r < GV_ROWS; r++) acc[r][n] = dot8(w[r], x, acc[r][n]);
         }
@@ -97,7 +158,7 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_kernel(const bf16* __restr
     for (int r = 0; r < GV_ROWS; r++)
 #pragma unroll
         for (int n = 0; n < NT; n++) acc[r][n] = mb_warp_sum(acc[r][n]);
-    if (lane != 0) return;
+    if (lane != 0) continue;
 #pragma unroll
     for (int n = 0; n < NT; n++) {
         if (MODE == 1) {
@@ -108,11 +169,13 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_kernel(const bf16* __restr
 #pragma unroll
             for (int r = 0; r < GV_ROWS; r++) {
                 if (m0 + r >= M) continue;
-                if (MODE == 2) reinterpret_cast<float*>(out)[(size_t)n * M + m0 + r] = acc[r][n];
+                if (MODE == 3) reinterpret_cast<float*>(out)[(size_t)n * M + m0 + r] += acc[r][n] + (bias ? bias[m0 + r] : 0.0f);
+                else if (MODE == 2) reinterpret_cast<float*>(out)[(size_t)n * M + m0 + r] = acc[r][n];
                 else reinterpret_cast<bf16*>(out)[(size_t)n * M + m0 + r] = __float2bfloat16_rn(acc[r][n]);
             }
         }
     }
+    }   // units
 }
 
 // The same product for matrices of long rows (K >= GV_LONG_K): the eight warps of a block share two rows, warp w
@@ -121,7 +184,8 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_kernel(const bf16* __restr
 // matrix streamed at 3.8 TB/s against 6 TB/s for 28,672 x 4,096.)
 template <int NT, int MODE>
 __global__ void __launch_bounds__(GV_WARPS * 32) gemv_long_kernel(const bf16* __restrict__ act, const bf16* __restrict__ W,
-                                                                  void* __restrict__ out, int M, int K) {
+                                                                  void* __restrict__ out, int M, int K,
+                                                                  const float* __restrict__ bias) {
     __shared__ float part[GV_WARPS][GV_ROWS][NT];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int unit = blockIdx.x;
@@ -184,49 +248,81 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_long_kernel(const bf16* __
             reinterpret_cast<bf16*>(out)[(size_t)n * M + m0] = __float2bfloat16_rn((g / (1.0f + expf(-g))) * up);
         }
     } else if (m0 + r < M) {
-        if (MODE == 2) reinterpret_cast<float*>(out)[(size_t)n * M + m0 + r] = s;
+        if (MODE == 3) reinterpret_cast<float*>(out)[(size_t)n * M + m0 + r] += s + (bias ? bias[m0 + r] : 0.0f);
+        else if (MODE == 2) reinterpret_cast<float*>(out)[(size_t)n * M + m0 + r] = s;
         else reinterpret_cast<bf16*>(out)[(size_t)n * M + m0 + r] = __float2bfloat16_rn(s);
     }
 }
 
 #define GV_LONG_K 8192
 
-template <int MODE>
-static int gemv_launch(const void* act, const void* W, void* out, int N, int M, int K, cudaStream_t st) {
+template <int MODE, bool NORM>
+static int gemv_launch(const void* act, const void* W, void* out, int N, int M, int K, GemvNorm nrm, const float* bias,
+                       cudaStream_t st) {
     if (N == 0 || M == 0) return 0;
-    if (N > GV_MAX_TOKENS || K % 8 || K < 8 || (reinterpret_cast<uintptr_t>(W) & 15) || (reinterpret_cast<uintptr_t>(act) & 15))
+    if (N > GV_MAX_TOKENS || K % 8 || K < 8 || (reinterpret_cast<uintptr_t>(W) & 15) ||
+        (!NORM && (reinterpret_cast<uintptr_t>(act) & 15)))
         return -2;
     const int units = MODE == 1 ? M : (M + GV_ROWS - 1) / GV_ROWS;
-    const unsigned grid = (unsigned)((units + GV_WARPS - 1) / GV_WARPS);
     const bf16* a = (const bf16*)act;
     const bf16* w = (const bf16*)W;
     if (K >= GV_LONG_K) {
+        if (NORM) return -2;                                         // the normalised row is kept for K < GV_LONG_K only
         const unsigned g2 = (unsigned)units;
         switch (N) {
-            case 1: gemv_long_kernel<1, MODE><<<g2, GV_WARPS * 32, 0, st>>>(a, w, out, M, K); break;
-            case 2: gemv_long_kernel<2, MODE><<<g2, GV_WARPS * 32, 0, st>>>(a, w, out, M, K); break;
-            case 3: gemv_long_kernel<3, MODE><<<g2, GV_WARPS * 32, 0, st>>>(a, w, out, M, K); break;
-            default: gemv_long_kernel<4, MODE><<<g2, GV_WARPS * 32, 0, st>>>(a, w, out, M, K); break;
+            case 1: gemv_long_kernel<1, MODE><<<g2, GV_WARPS * 32, 0, st>>>(a, w, out, M, K, bias); break;
+            case 2: gemv_long_kernel<2, MODE><<<g2, GV_WARPS * 32, 0, st>>>(a, w, out, M, K, bias); break;
+            case 3: gemv_long_kernel<3, MODE><<<g2, GV_WARPS * 32, 0, st>>>(a, w, out, M, K, bias); break;
+            default: gemv_long_kernel<4, MODE><<<g2, GV_WARPS * 32, 0, st>>>(a, w, out, M, K, bias); break;
         }
         MB_LAUNCH_CHECK();
         return 0;
     }
+    unsigned grid = (unsigned)((units + GV_WARPS - 1) / GV_WARPS);
+    size_t smem = 0;
+    if (NORM) {
+        // every block normalises the row once: a few blocks per SM that walk the rows, not one block per 16 rows
+        if ((reinterpret_cast<uintptr_t>(nrm.x) & 15) || (reinterpret_cast<uintptr_t>(nrm.w) & 15)) return -2;
+        smem = (size_t)N * K * sizeof(bf16);
+        if (smem > 48 * 1024) return -2;
+        static int sms = 0;
+        if (!sms) {
+            int dev = 0;
+            cudaGetDevice(&dev);
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+            if (sms <= 0) sms = 148;
+        }
+        if (grid > (unsigned)(4 * sms)) grid = (unsigned)(4 * sms);
+    }
     switch (N) {
-        case 1: gemv_kernel<1, MODE><<<grid, GV_WARPS * 32, 0, st>>>(a, w, out, M, K); break;
-        case 2: gemv_kernel<2, MODE><<<grid, GV_WARPS * 32, 0, st>>>(a, w, out, M, K); break;
-        case 3: gemv_kernel<3, MODE><<<grid, GV_WARPS * 32, 0, st>>>(a, w, out, M, K); break;
-        default: gemv_kernel<4, MODE><<<grid, GV_WARPS * 32, 0, st>>>(a, w, out, M, K); break;
+        case 1: gemv_kernel<1, MODE, NORM><<<grid, GV_WARPS * 32, smem, st>>>(a, w, out, M, K, nrm, bias); break;
+        case 2: gemv_kernel<2, MODE, NORM><<<grid, GV_WARPS * 32, smem, st>>>(a, w, out, M, K, nrm, bias); break;
+        case 3: gemv_kernel<3, MODE, NORM><<<grid, GV_WARPS * 32, smem, st>>>(a, w, out, M, K, nrm, bias); break;
+        default: gemv_kernel<4, MODE, NORM><<<grid, GV_WARPS * 32, smem, st>>>(a, w, out, M, K, nrm, bias); break;
     }
     MB_LAUNCH_CHECK();
     return 0;
 }
 
 MB_API int mb_gemv_bf16(const void* act, const void* W, void* out, int N, int M, int K, cudaStream_t st) {
-    return gemv_launch<0>(act, W, out, N, M, K, st);
+    return gemv_launch<0, false>(act, W, out, N, M, K, GemvNorm{nullptr, nullptr, 0.0f}, nullptr, st);
 }
 MB_API int mb_gemv_swiglu_bf16(const void* act, const void* W, void* out, int N, int M, int K, cudaStream_t st) {
-    return gemv_launch<1>(act, W, out, N, M, K, st);
+    return gemv_launch<1, false>(act, W, out, N, M, K, GemvNorm{nullptr, nullptr, 0.0f}, nullptr, st);
 }
 MB_API int mb_gemv_f32out(const void* act, const void* W, void* out, int N, int M, int K, cudaStream_t st) {
-    return gemv_launch<2>(act, W, out, N, M, K, st);
+    return gemv_launch<2, false>(act, W, out, N, M, K, GemvNorm{nullptr, nullptr, 0.0f}, nullptr, st);
+}
+// x (N, M) float32 += act W^T + bias (bias may be null)
+MB_API int mb_gemv_residual(const void* act, const void* W, float* x, const float* bias, int N, int M, int K, cudaStream_t st) {
+    return gemv_launch<3, false>(act, W, x, N, M, K, GemvNorm{nullptr, nullptr, 0.0f}, bias, st);
+}
+// out = rmsnorm(x; norm_w, eps) W^T, x (N, K) float32; the SwiGLU form as mb_gemv_swiglu_bf16.  K < 8,192.
+MB_API int mb_gemv_normed_bf16(const float* x, const float* norm_w, float eps, const void* W, void* out, int N, int M,
+                               int K, cudaStream_t st) {
+    return gemv_launch<0, true>(nullptr, W, out, N, M, K, GemvNorm{x, norm_w, eps}, nullptr, st);
+}
+MB_API int mb_gemv_normed_swiglu_bf16(const float* x, const float* norm_w, float eps, const void* W, void* out, int N,
+                                      int M, int K, cudaStream_t st) {
+    return gemv_launch<1, true>(nullptr, W, out, N, M, K, GemvNorm{x, norm_w, eps}, nullptr, st);
 }

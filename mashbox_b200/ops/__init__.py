@@ -213,12 +213,41 @@ def linear_tc5(a, w, out, mode="plain"):
 # to 4 tokens, the engine uses them where they beat the library, which is at ONE token.  Measured inside captured
 # graphs on the Llama-3.1-8B shapes at one token, own / library: output product 10.8 / 13.0 us, QKV 12.2 / 11.7, down
 # 21.2 / 24.9, fused gate/up + SwiGLU 39.0 / 39.2 + 2.3; at two tokens the arithmetic (bf16 to float conversions on
-# the FMA pipe) already costs more than the stream.  GEMV[mode] = the most tokens the engine gives the kernel (0: never).
-GEMV = {"swiglu": 1, "plain": 1}
+# the FMA pipe) already costs more than the stream.  GEMV[mode] = the most tokens the engine gives the kernel (0: never);
+# "fused": the forms that normalise the residual stream themselves or add their product into it (see small_fused_supports).
+GEMV = {"swiglu": 1, "plain": 1, "fused": 1}
 
 
 def gemv_supports(N, K, mode="plain"):
     return 1 <= N <= min(4, GEMV["swiglu" if mode == "swiglu" else "plain"]) and K >= 8 and K % 8 == 0
+
+
+def small_fused_supports(N, K, dtype):
+    """True when a step of N tokens of width K can run its layers on the folded matrix-vector kernels: the product that
+    follows a norm normalises the float32 residual stream itself (linear_gemv_normed), the product that ends a
+    sublayer adds into it (linear_gemv_residual)."""
+    return (dtype == torch.bfloat16 and 1 <= N <= min(4, GEMV["fused"]) and K % 8 == 0 and 8 <= K < 8192
+            and N * K * 2 <= 48 * 1024)
+
+
+def linear_gemv_normed(x, norm_w, eps, w, out, mode="plain"):
+    """x (N <= 4, K) float32 residual stream, norm_w (K) float32 -> out (N, M) bf16 = rmsnorm(x) W^T ("swiglu": W is
+    (2M, K) and out = silu(gate) * up), the normalised row rounded to bf16 as the norm kernel would store it."""
+    _cuda(x, norm_w, w, out)
+    N, K = x.shape
+    name = {"plain": "mb_gemv_normed_bf16", "swiglu": "mb_gemv_normed_swiglu_bf16"}[mode]
+    f = _fn("gemv", name, [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_p(x), _p(norm_w), float(eps), _p(w), _p(out), N, out.shape[1], K, _stream()), "gemv_normed")
+    return out
+
+
+def linear_gemv_residual(a, w, x, bias=None):
+    """x (N <= 4, M) float32 += a (N, K) bf16 @ w (M, K)^T (+ bias (M) float32), in place"""
+    _cuda(a, w, x, bias)
+    N, K = a.shape
+    f = _fn("gemv", "mb_gemv_residual", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_p(a), _p(w), _p(x), _p(bias), N, x.shape[1], K, _stream()), "gemv_residual")
+    return x
 
 
 def linear_gemv(a, w, out, mode="plain"):

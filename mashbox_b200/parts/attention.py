@@ -126,13 +126,20 @@ class Attention:
                              max_splits=max_splits, tc5=tc5)
 
     # ------------------------------------------------------------------------------------------ forward
-    def forward(self, ctx, h, run):
+    fuses_small = True      # forward() takes normed= and residual= (see PreNormBlock)
+
+    def forward(self, ctx, h, run, normed=None, residual=None):
         import torch
         ops, N = ctx.ops, ctx.N
         H, KV, HD = self.H, self.KV, self.HD
         width = (H + 2 * KV) * HD
         qkv = ctx.ws.get("qkv", N, (width,), ctx.dtype)
-        ops.linear(h, self.wqkv, out=qkv)
+        if normed is not None:
+            x, norm = normed
+            w, eps = norm.fusable()
+            ops.linear_gemv_normed(x, w, eps, self.wqkv, qkv)
+        else:
+            ops.linear(h, self.wqkv, out=qkv)
         group, kpool, vpool = ctx.cache.layer_cache(run.cache)
         table = group.device_table
         page, pages = ctx.cache.page_size, ctx.cache.num_pages
@@ -179,6 +186,9 @@ class Attention:
         else:
             ops.attention_simple(qkv, width, out, ctx.dev("positions"), ctx.dev("tok_row"), table, kpool, vpool, H, KV,
                                  HD, page, pages, self.window, self.scale, ctx.err)
+        if residual is not None:
+            ops.linear_gemv_residual(out, self.wo, residual, self.bo)
+            return None
         y = ctx.ws.get("delta", N, (self.D,), ctx.dtype)
         ops.linear(out, self.wo, out=y)
         return y, self.bo

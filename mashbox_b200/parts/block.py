@@ -20,10 +20,20 @@ class PreNormBlock:
         return [self.norm1, self.mixer, self.norm2, self.ffn]
 
     def forward(self, ctx, x, pending, run):
-        h = self.norm1.forward(ctx, x, pending)
-        y = self.mixer.forward(ctx, h, run)
-        h = self.norm2.forward(ctx, x, y)
-        return self.ffn.forward(ctx, h)
+        # A step of very few tokens is a chain of short kernels.  Parts that say `fuses_small` take two of them in:
+        # with normed=(x, norm) their first product normalises the residual stream itself (x must be up to date:
+        # nothing pending), with residual=x their last product adds into the stream and nothing is left pending.
+        small = ctx.ops.small_fused_supports(ctx.N, x.shape[1], ctx.dtype) and not ctx.options.get("no_small_fusion", False)
+        pending = self._sublayer(ctx, x, pending, self.norm1, self.mixer, small, run)
+        return self._sublayer(ctx, x, pending, self.norm2, self.ffn, small)
+
+    @staticmethod
+    def _sublayer(ctx, x, pending, norm, part, small, *run):
+        if not (small and getattr(part, "fuses_small", False) and hasattr(norm, "fusable")):
+            return part.forward(ctx, norm.forward(ctx, x, pending), *run)
+        if pending is not None:
+            return part.forward(ctx, norm.forward(ctx, x, pending), *run, residual=x)
+        return part.forward(ctx, None, *run, normed=(x, norm), residual=x)
 
 
 register("block", "prenorm", PreNormBlock)

@@ -22,16 +22,25 @@ class SwiGLU:
         self.wgu = torch.cat([tensors[self.names["gate"]], tensors[self.names["up"]]], 0).contiguous()
         self.wd = tensors[self.names["down"]]
 
-    def forward(self, ctx, h):
+    fuses_small = True      # forward() takes normed= and residual= (see PreNormBlock)
+
+    def forward(self, ctx, h, normed=None, residual=None):
         import torch
         N = ctx.N
         a = ctx.ws.get("ffn_act", N, (self.F,), ctx.dtype)
-        if ctx.dtype == torch.bfloat16 and ctx.ops.fused_swiglu_supports(N, self.F, self.D):
+        if normed is not None:
+            x, norm = normed
+            w, eps = norm.fusable()
+            ctx.ops.linear_gemv_normed(x, w, eps, self.wgu, a, "swiglu")
+        elif ctx.dtype == torch.bfloat16 and ctx.ops.fused_swiglu_supports(N, self.F, self.D):
             ctx.ops.linear_swiglu(h, self.wgu, a)           # both products and the gate in one kernel
         else:
             gu = ctx.ws.get("gate_up", N, (2 * self.F,), ctx.dtype)
             ctx.ops.linear(h, self.wgu, out=gu)
             ctx.ops.swiglu(gu, a)
+        if residual is not None:
+            ctx.ops.linear_gemv_residual(a, self.wd, residual)
+            return None
         y = ctx.ws.get("delta", N, (self.D,), ctx.dtype)
         ctx.ops.linear(a, self.wd, out=y)
         return y, None

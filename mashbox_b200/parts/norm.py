@@ -20,6 +20,10 @@ class RMSNorm:
     def bind(self, tensors, env):
         self.weight = tensors[self.name]
 
+    def fusable(self):
+        """(weight, eps) for a product kernel that normalises the residual stream itself"""
+        return self.weight, self.eps
+
     def forward(self, ctx, x, pending=None, rows=None):
         n_out = x.shape[0] if rows is None else rows.shape[0]
         out = ctx.ws.get("normed" if rows is None else "normed_rows", n_out, (self.width,), ctx.dtype,

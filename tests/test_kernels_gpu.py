@@ -448,6 +448,46 @@ def test_tcgen05_product(N, M, K):
         K_.linear_tc5(a[:, :K - 4].contiguous(), w[:, :K - 4].contiguous(), out, "plain")
 
 
+@pytest.mark.parametrize("N,M,K", [(1, 6144, 4096), (1, 57, 72), (3, 1000, 2504), (2, 64, 8184)])
+def test_matrix_vector_product_that_normalises_and_one_that_adds_to_the_stream(N, M, K):
+    """the two folded forms of a one-token step: rmsnorm inside the product that follows it, the residual add inside
+    the product that ends a sublayer (also through the long-row kernel)"""
+    K_ = ops()
+    g = torch.Generator().manual_seed(21)
+    x = (3.0 * torch.randn(N, K, generator=g)).to(G.DEV)
+    nw = (1.0 + 0.2 * torch.randn(K, generator=g)).to(G.DEV)
+    w = (torch.randn(M, K, generator=g) / K ** 0.5).bfloat16().to(G.DEV)
+    eps = 1e-5
+    h = (x.double() * torch.rsqrt((x.double() ** 2).mean(-1, keepdim=True) + eps) * nw.double()).float().bfloat16()
+    out = torch.full((N, M), float("nan"), device=G.DEV, dtype=torch.bfloat16)
+    K_.linear_gemv_normed(x, nw, eps, w, out, "plain")
+    close(out, h.double() @ w.double().T, torch.bfloat16, "normalising matrix-vector product")
+    F = M // 2
+    act = torch.full((N, F), float("nan"), device=G.DEV, dtype=torch.bfloat16)
+    wgu = torch.cat([w[:F], w[M - F:]]).contiguous()
+    K_.linear_gemv_normed(x, nw, eps, wgu, act, "swiglu")
+    gt = (h.double() @ wgu[:F].double().T).float().bfloat16().double()
+    up = (h.double() @ wgu[F:].double().T).float().bfloat16().double()
+    close(act, gt * torch.sigmoid(gt) * up, torch.bfloat16, "normalising gate/up product")
+    # the same rows as the norm kernel followed by the plain product
+    hh = torch.empty(N, K, device=G.DEV, dtype=torch.bfloat16)
+    K_.add_rmsnorm(x.clone(), None, None, nw, eps, hh, None)
+    two = torch.empty(N, M, device=G.DEV, dtype=torch.bfloat16)
+    K_.linear_gemv(hh, w, two, "plain")
+    assert float((out.double() - two.double()).abs().max()) <= 2.0 ** -7 * float(two.double().abs().max())
+    # adding into the stream: a (N, K) bf16 against W2 (M, K), x2 (N, M) float32, with and without a bias
+    a = torch.randn(N, K, generator=g).bfloat16().to(G.DEV)
+    x2 = torch.randn(N, M, generator=g).to(G.DEV)
+    bias = torch.randn(M, generator=g).to(G.DEV)
+    want = x2.double() + a.double() @ w.double().T
+    got = x2.clone()
+    K_.linear_gemv_residual(a, w, got)
+    close(got, want, torch.float32, "residual add in the product")
+    got = x2.clone()
+    K_.linear_gemv_residual(a, w, got, bias)
+    close(got, want + bias.double(), torch.float32, "residual add with a bias")
+
+
 @pytest.mark.parametrize("N,M,K", [(1, 4096, 4096), (4, 6144, 4096), (2, 509, 320), (3, 4096, 14336), (1, 57, 72), (2, 37, 8200)])
 def test_matrix_vector_product(N, M, K):
     """at most 4 tokens: one warp per two rows of W, float32 sums; plain, float32 out and fused SwiGLU"""
