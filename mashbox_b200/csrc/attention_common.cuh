@@ -47,13 +47,17 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// element offset of 16-byte chunk c of row `row` in a tile whose rows hold HD bf16 values (swizzled against bank conflicts)
+// Rows of a tile in shared memory hold HD bf16 values in 16-byte chunks, swizzled against bank conflicts by XOR with
+// row bits.  2 and 4 chunks (head sizes 16, 32) have swizzles of their own; every other head size is laid out in
+// groups of 8 chunks, the row padded to a whole number of groups (the XOR stays inside a group).
+template <int HD> __host__ __device__ constexpr int tile_row() {               // elements of a row in shared memory
+    return (HD / 8 == 2 || HD / 8 == 4) ? HD : ((HD / 8 + 7) / 8) * 64;
+}
+// element offset of 16-byte chunk c of row `row`
 template <int HD> __device__ __forceinline__ int swz(int row, int c) {
     constexpr int CH = HD / 8;
-    int pc;
-    if (CH >= 8) pc = c ^ (row & 7);
-    else if (CH == 4) pc = c ^ ((row >> 1) & 3);
-    else pc = c ^ ((row >> 2) & 1);
-    return (row * CH + pc) * 8;
+    if (CH == 4) return (row * CH + (c ^ ((row >> 1) & 3))) * 8;
+    if (CH == 2) return (row * CH + (c ^ ((row >> 2) & 1))) * 8;
+    return row * tile_row<HD>() + (c ^ (row & 7)) * 8;
 }
 

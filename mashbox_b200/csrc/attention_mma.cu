@@ -48,9 +48,11 @@ __global__ void __launch_bounds__(128) attn_mma_kernel(const AttnParams P) {
     constexpr int NT = DECODE ? 2 : 8;      // 8-key tiles per warp per key tile
     constexpr int KS = HD / 16;             // k steps of q k^T
     constexpr int DT = HD / 8;              // 8-wide tiles of the output
+    constexpr int ROW = tile_row<HD>();     // elements of a tile's row in shared memory
+    constexpr bool QREG = HD <= 128;        // the query fragments stay in registers (above: read again for every key tile)
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* qs = reinterpret_cast<bf16*>(smem_raw);
-    bf16* kvs = qs + BM * HD;
+    bf16* kvs = qs + BM * ROW;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tig = lane & 3;
     const int4 item = P.items[blockIdx.x];
@@ -83,7 +85,7 @@ __global__ void __launch_bounds__(128) attn_mma_kernel(const AttnParams P) {
 #pragma unroll
     for (int s = 0; s < STAGES - 1; s++) {
         if (t_begin + s < t_end)
-            load_kv_tile<HD, BN>(kvs + (size_t)s * 2 * BN * HD, kvs + (size_t)s * 2 * BN * HD + BN * HD, P, tb, kvh,
+            load_kv_tile<HD, BN>(kvs + (size_t)s * 2 * BN * ROW, kvs + (size_t)s * 2 * BN * ROW + BN * ROW, P, tb, kvh,
                                  lo_al + (t_begin + s) * BN, lo, hi, tid);
         cp_async_commit();
     }
@@ -108,10 +110,12 @@ __global__ void __launch_bounds__(128) attn_mma_kernel(const AttnParams P) {
 
     cp_async_wait<STAGES - 1>();
     __syncthreads();
-    uint32_t qf[KS][4];
+    uint32_t qf[QREG ? KS : 1][4];
+    if (QREG) {
 #pragma unroll
-    for (int ks = 0; ks < KS; ks++)
-        ldmatrix_x4(qf[ks], qs + swz<HD>(m0 + (lane & 7) + ((lane >> 3) & 1) * 8, ks * 2 + (lane >> 4)));
+        for (int ks = 0; ks < KS; ks++)
+            ldmatrix_x4(qf[QREG ? ks : 0], qs + swz<HD>(m0 + (lane & 7) + ((lane >> 3) & 1) * 8, ks * 2 + (lane >> 4)));
+    }
 
     for (int t = t_begin; t < t_end; t++) {
         cp_async_wait<STAGES - 2>();
@@ -119,13 +123,13 @@ __global__ void __launch_bounds__(128) attn_mma_kernel(const AttnParams P) {
         {
             const int tn = t + STAGES - 1;
             if (tn < t_end) {
-                bf16* st = kvs + (size_t)((tn - t_begin) % STAGES) * 2 * BN * HD;
-                load_kv_tile<HD, BN>(st, st + BN * HD, P, tb, kvh, lo_al + tn * BN, lo, hi, tid);
+                bf16* st = kvs + (size_t)((tn - t_begin) % STAGES) * 2 * BN * ROW;
+                load_kv_tile<HD, BN>(st, st + BN * ROW, P, tb, kvh, lo_al + tn * BN, lo, hi, tid);
             }
             cp_async_commit();
         }
-        const bf16* kt = kvs + (size_t)((t - t_begin) % STAGES) * 2 * BN * HD;
-        const bf16* vt = kt + BN * HD;
+        const bf16* kt = kvs + (size_t)((t - t_begin) % STAGES) * 2 * BN * ROW;
+        const bf16* vt = kt + BN * ROW;
         const int kb = lo_al + t * BN;
 
         float s[NT][4];
@@ -133,12 +137,13 @@ __global__ void __launch_bounds__(128) attn_mma_kernel(const AttnParams P) {
         for (int j = 0; j < NT; j++) { s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f; }
 #pragma unroll
         for (int ks = 0; ks < KS; ks++) {
+            if (!QREG) ldmatrix_x4(qf[0], qs + swz<HD>(m0 + (lane & 7) + ((lane >> 3) & 1) * 8, ks * 2 + (lane >> 4)));
 #pragma unroll
             for (int np = 0; np < NT / 2; np++) {
                 uint32_t b[4];
                 ldmatrix_x4(b, kt + swz<HD>(nbase + np * 16 + (lane & 7) + (lane >> 4) * 8, ks * 2 + ((lane >> 3) & 1)));
-                mma_bf16(s[2 * np], qf[ks], b[0], b[1]);
-                mma_bf16(s[2 * np + 1], qf[ks], b[2], b[3]);
+                mma_bf16(s[2 * np], qf[QREG ? ks : 0], b[0], b[1]);
+                mma_bf16(s[2 * np + 1], qf[QREG ? ks : 0], b[2], b[3]);
             }
         }
         float tmax[2] = {-INFINITY, -INFINITY};
@@ -284,8 +289,9 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_o, const float*
 template <int HD, bool DECODE, int STAGES>
 static int launch_one(const AttnParams& P, int n_items, cudaStream_t st) {
     constexpr int BM = DECODE ? 16 : 64;
-    size_t smem = (size_t)BM * HD * 2 + (size_t)STAGES * 2 * 64 * HD * 2;
-    const size_t merge = (size_t)(4 * 16 * HD + 2 * 4 * 16) * 4 + (size_t)BM * HD * 2;
+    constexpr int ROW = tile_row<HD>();
+    size_t smem = (size_t)BM * ROW * 2 + (size_t)STAGES * 2 * 64 * ROW * 2;
+    const size_t merge = (size_t)(4 * 16 * HD + 2 * 4 * 16) * 4 + (size_t)BM * ROW * 2;
     if (DECODE && merge > smem) smem = merge;
     static bool configured = false;
     if (!configured) {
@@ -300,7 +306,15 @@ static int launch_one(const AttnParams& P, int n_items, cudaStream_t st) {
 }
 
 // 1 when the tensor-core kernel takes this head size
-MB_API int mb_attn_mma_supports(int HD) { return HD == 16 || HD == 32 || HD == 64 || HD == 128; }
+// 1 when this library's tensor-core kernel takes the head size.  The source builds two libraries: the common head
+// sizes (16, 32, 64, 128), and with -DMB_ATTN_WIDE every other multiple of 16 up to 256 (a model needs one of them,
+// and each takes a while to compile).
+static bool common_head_size(int HD) { return HD == 16 || HD == 32 || HD == 64 || HD == 128; }
+#ifdef MB_ATTN_WIDE
+MB_API int mb_attn_mma_supports(int HD) { return HD >= 16 && HD <= 256 && HD % 16 == 0 && !common_head_size(HD); }
+#else
+MB_API int mb_attn_mma_supports(int HD) { return common_head_size(HD); }
+#endif
 
 // decode != 0: items are tiles of at most 16 rows; else tiles of 64 rows.
 MB_API int mb_attn_mma_bf16(const void* q, int q_stride, void* out, const void* kpool, const void* vpool,
@@ -323,14 +337,17 @@ MB_API int mb_attn_mma_bf16(const void* q, int q_stride, void* out, const void* 
     for (int sft = 0; sft < 31; sft++) if ((1 << sft) == page) P.page_shift = sft;
     P.scale_log2 = scale * 1.4426950408889634f;
     P.err = err;
+    // head sizes in steps of 16 up to 256; above 128 two stages of K/V tiles (a stage is 64 KB at 256)
 #define MB_ATTN_CASE(hd)                                                                   \
     case hd:                                                                               \
-        return decode ? launch_one<hd, true, 3>(P, n_items, st) : launch_one<hd, false, 2>(P, n_items, st);
+        return decode ? launch_one<hd, true, (hd > 128 ? 2 : 3)>(P, n_items, st) : launch_one<hd, false, 2>(P, n_items, st);
     switch (HD) {
-        MB_ATTN_CASE(16)
-        MB_ATTN_CASE(32)
-        MB_ATTN_CASE(64)
-        MB_ATTN_CASE(128)
+#ifdef MB_ATTN_WIDE
+        MB_ATTN_CASE(48) MB_ATTN_CASE(80) MB_ATTN_CASE(96) MB_ATTN_CASE(112) MB_ATTN_CASE(144) MB_ATTN_CASE(160)
+        MB_ATTN_CASE(176) MB_ATTN_CASE(192) MB_ATTN_CASE(208) MB_ATTN_CASE(224) MB_ATTN_CASE(240) MB_ATTN_CASE(256)
+#else
+        MB_ATTN_CASE(16) MB_ATTN_CASE(32) MB_ATTN_CASE(64) MB_ATTN_CASE(128)
+#endif
     }
     return -2;
 }

@@ -326,14 +326,19 @@ def attention_simple(q, q_stride, out, positions, tok_seq, table, kpool, vpool, 
 
 
 def attention_mma_supports(HD):
-    return HD in (16, 32, 64, 128)
+    """head sizes in steps of 16 up to 256 (16, 32, 64, 128 in one library, the others in a second one)"""
+    return 16 <= HD <= 256 and HD % 16 == 0
+
+
+def _mma_library(HD):
+    return "attention_mma" if HD in (16, 32, 64, 128) else "attention_mma_wide"
 
 
 def attention_mma(q, q_stride, out, kpool, vpool, items, n_items, decode, q_start, q_len, pos0, part_base, seq_row,
                   table,
                   part_o, part_ml, max_splits, H, KV, HD, page, num_pages, window, scale, err):
     _cuda(q, out, kpool, vpool, items, q_start, q_len, pos0, part_base, table, part_o, part_ml)
-    f = _fn("attention_mma", "mb_attn_mma_bf16",
+    f = _fn(_mma_library(HD), "mb_attn_mma_bf16",
             [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
              c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p] + [c_int] * 7 + [c_float, c_void_p, c_void_p])
     _check(f(_p(q), q_stride, _p(out), _p(kpool), _p(vpool), _p(items), n_items, 1 if decode else 0, _p(q_start),

@@ -23,13 +23,14 @@ CSRC = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 FLAGS = ["-O3", "-lineinfo", "-std=c++17", "-shared", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
 HEADERS = ["common.cuh", "attention_common.cuh"]
-LIBRARIES = {            # library name -> (source file, extra link flags)
+LIBRARIES = {            # library name -> (source file, extra compiler flags)
     "elementwise": ("elementwise.cu", []),
     "gemm_f32": ("gemm_f32.cu", []),
     "gemm_tc5": ("gemm_tc5.cu", []),
     "gemv": ("gemv.cu", []),
     "attention_simple": ("attention_simple.cu", []),
-    "attention_mma": ("attention_mma.cu", []),
+    "attention_mma": ("attention_mma.cu", []),                         # head sizes 16, 32, 64, 128
+    "attention_mma_wide": ("attention_mma.cu", ["-DMB_ATTN_WIDE"]),    # the other multiples of 16 up to 256
     "attention_tma": ("attention_tma.cu", []),
     "attention_tc5": ("attention_tc5.cu", []),
     "sampling": ("sampling.cu", []),

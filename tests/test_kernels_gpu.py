@@ -212,6 +212,7 @@ def test_attention_plain_kernel_window_edge(dtype):
 
 
 MMA_CASES = [  # HD, H, KV, page, window, splits
+    (256, 8, 4, 16, None, 2), (96, 6, 2, 8, 70, 1), (80, 4, 1, 16, None, 4), (48, 3, 3, 4, None, 1),
     (128, 6, 2, 16, None, 1), (128, 5, 5, 32, 300, 1), (128, 8, 2, 16, None, 1), (128, 8, 2, 16, None, 4), (64, 6, 2, 8, None, 3), (32, 6, 1, 8, 50, 2),
     (16, 4, 2, 4, None, 1), (128, 32, 8, 32, 700, 8), (64, 5, 5, 16, None, 2), (128, 16, 1, 16, None, 2)]
 
@@ -282,8 +283,8 @@ def test_attention_tensor_core_kernel_window_edge(splits, kind, HD):
 
 def test_attention_kernel_refuses_head_sizes_it_does_not_take():
     K = ops()
-    assert [K.attention_mma_supports(h) for h in (16, 32, 48, 64, 96, 128, 256)] == [True, True, False, True, False, True, False]
-    seqs = G.PagedSequences([20], [1], 2, 1, 48, 8, torch.bfloat16).round().build()
+    assert [K.attention_mma_supports(h) for h in (16, 32, 48, 64, 96, 128, 256, 8, 40, 272)] == [True] * 7 + [False] * 3
+    seqs = G.PagedSequences([20], [1], 2, 1, 40, 8, torch.bfloat16).round().build()
     with pytest.raises(Exception, match="does not take these sizes"):
         run_mma(seqs, None, 1)
     big = G.PagedSequences([20], [1], 1, 1, 512, 8, torch.float32).build()

@@ -110,7 +110,8 @@ def test_norm_feed_forward_embedding_and_head_alone(dtype):
 @pytest.mark.parametrize("dtype,options", [("float32", {}), ("bfloat16", {}), ("bfloat16", {"plain_attention": True}),
                                            ("bfloat16", {"attention_target_blocks": 100000})])
 @pytest.mark.parametrize("HD,H,KV,window,bias,pairing", [(32, 6, 2, None, True, "adjacent"), (64, 4, 4, 23, False, "halves"),
-                                                         (48, 3, 1, None, False, "adjacent")])
+                                                         (48, 3, 1, None, False, "adjacent"),
+                                                         (256, 2, 1, 40, False, "halves")])
 def test_attention_mixer_alone_in_three_cuts(dtype, options, HD, H, KV, window, bias, pairing):
     """the mixer over its own paged cache: a whole sequence at once, in portions, and token by token beside another
     sequence, against the plain functions (projections, rotation, attention) over the whole sequence"""
