@@ -422,9 +422,32 @@ def sample_params_size():
     return lib.mb_sample_params_size()
 
 
-def sample(logits, work, params, cnt, seen, n_rows, out):
+_sample_scratch = {}
+
+
+def sample(logits, work, params, cnt, seen, n_rows, out, any_cut=True, keep_work=True):
     """logits (R, V) float32; work (n_rows, V) float32 scratch; params: uint8 tensor of n_rows packed RowParams;
-    cnt (slots, V) int32 / seen (slots, V) uint8 penalty state or None; out (n_rows,) int32."""
+    cnt (slots, V) int32 / seen (slots, V) uint8 penalty state or None; out (n_rows,) int32.  any_cut: False when no
+    row has a top_k, top_p or min_p (the kernel that finds the cuts is skipped).  keep_work: leave the processed
+    logits after the cuts (cut values -inf) in `work`, which costs a write of every row."""
+    _cuda(logits, work, params, cnt, seen, out)
+    key = str(logits.device)
+    sc = _sample_scratch.get(key)
+    if sc is None or sc[0].shape[0] < n_rows * 32:
+        cap = max(n_rows, 64)
+        sc = (torch.empty(cap * 32, dtype=torch.float32, device=logits.device),
+              torch.empty(cap * 32, dtype=torch.int32, device=logits.device),
+              torch.empty(cap * 2, dtype=torch.int32, device=logits.device))
+        _sample_scratch[key] = sc
+    f = _fn("sampling", "mb_sample_fast", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
+                                           c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p])
+    _check(f(_p(logits), _p(work), _p(params), _p(cnt), _p(seen), n_rows, logits.shape[1], _p(sc[2]), _p(sc[0]), _p(sc[1]),
+             _p(work) if keep_work else None, 1 if any_cut else 0, _p(out), _stream()), "sample")
+
+
+def sample_one_kernel(logits, work, params, cnt, seen, n_rows, out):
+    """The same sampler as one kernel with a block per row that bisects the whole row (a millisecond for a batch at a
+    vocabulary of 128k): what the entry point without allocations runs, kept callable for comparison."""
     _cuda(logits, work, params, cnt, seen, out)
     f = _fn("sampling", "mb_sample", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p])
     _check(f(_p(logits), _p(work), _p(params), _p(cnt), _p(seen), n_rows, logits.shape[1], _p(out), _stream()), "sample")

@@ -67,7 +67,8 @@ class Sampler:
             params = torch.from_numpy(packed.view(np.uint8).copy()).to(self.device)
             if self.work is None or self.work.shape[0] < n:
                 self.work = torch.empty((max(n, self.max_slots), self.V), dtype=torch.float32, device=self.device)
-            kernels.sample(logits, self.work, params, self.cnt, self.seen, n, out)
+            cuts = any(p.temperature > 0 and (p.top_k > 0 or p.top_p < 1.0 or p.min_p > 0.0) for p, _, _ in rows)
+            kernels.sample(logits, self.work, params, self.cnt, self.seen, n, out, any_cut=cuts, keep_work=False)
         if err is not None:
             self.ret[n:n + 1].copy_(err)
         self.turn ^= 1

@@ -343,6 +343,47 @@ def test_cuts_keep_exactly_the_allowed_set_ties_included():
     assert (work[4] > -np.inf).sum() == (lg[4] == lg[4].max()).sum()      # top_k 1 keeps the maximum and its ties
 
 
+@pytest.mark.parametrize("kind", ["peaked", "flat", "ties"])
+def test_three_kernel_sampler_equals_the_one_kernel_sampler_at_a_large_vocabulary(kind):
+    """the serving path (thresholds found among gathered candidates, draw over chunks) against the kernel that bisects
+    whole rows, at the vocabulary of the 8B model: the same kept sets and the same tokens.  Peaked rows take the
+    candidate path, flat rows have more candidates than fit and fall back, rows of few distinct values are all ties."""
+    K = ops()
+    from mashbox_b200.sampling.sampler import ROW
+    g = torch.Generator().manual_seed(31)
+    V = 128256
+    if kind == "peaked":
+        lg = torch.randn(8, V, generator=g)
+        lg[:, :500] += 6.0 * torch.rand(8, 500, generator=g) + 4.0
+    elif kind == "flat":
+        lg = 0.5 * torch.randn(8, V, generator=g)
+    else:
+        lg = torch.randint(0, 4, (8, V), generator=g).float()
+    rows = [dict(temperature=0.8, top_p=0.9, seed=1), dict(temperature=1.0, top_k=40, seed=2),
+            dict(temperature=0.7, top_k=50, top_p=0.8, min_p=0.01, seed=3), dict(temperature=1.2, min_p=0.05, seed=4),
+            dict(temperature=0.9, seed=5), dict(), dict(temperature=0.6, top_p=0.3, seed=7),
+            dict(temperature=1.0, top_k=2000, top_p=0.95, seed=8)]
+    packed = np.zeros(8, ROW)
+    for i, r in enumerate(rows):
+        packed[i] = (r.get("temperature", 0.0), r.get("top_p", 1.0), r.get("min_p", 0.0), 1.0, 0.0, 0.0, r.get("top_k", 0), -1,
+                     r.get("seed", 0), 0, 3, i)
+    params = torch.from_numpy(packed.view(np.uint8).copy()).to(G.DEV)
+    dev = lg.to(G.DEV)
+    w1, w2 = torch.empty(8, V, device=G.DEV), torch.empty(8, V, device=G.DEV)
+    o1, o2 = torch.empty(8, dtype=torch.int32, device=G.DEV), torch.empty(8, dtype=torch.int32, device=G.DEV)
+    K.sample(dev, w1, params, None, None, 8, o1)
+    K.sample_one_kernel(dev, w2, params, None, None, 8, o2)
+    a, b = w1.cpu().numpy(), w2.cpu().numpy()
+    for i in range(8):
+        if rows[i].get("temperature", 0.0) > 0:
+            assert ((a[i] > -np.inf) == (b[i] > -np.inf)).all(), (kind, i, (a[i] > -np.inf).sum(), (b[i] > -np.inf).sum())
+            assert 0 < (a[i] > -np.inf).sum()
+    assert o1.tolist() == o2.tolist()
+    o3 = torch.empty(8, dtype=torch.int32, device=G.DEV)
+    K.sample(dev, w1, params, None, None, 8, o3, any_cut=True, keep_work=False)
+    assert o3.tolist() == o1.tolist()
+
+
 def test_draws_equal_the_plain_generator_and_depend_on_seed_and_token_index_only():
     g = torch.Generator().manual_seed(12)
     V = 300
