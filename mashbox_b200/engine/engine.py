@@ -121,25 +121,28 @@ class Engine:
                     patches.append((at + last - p.start, source[id(r)]))
             entries.append((r.rid, tokens, [p.count - 1] if p.sample else []))
             at += p.count
-        return plan, entries, self.runner.prepare(entries, patches)
+        # the sampler's settings of the rows that sample go to the device with the step's arrays
+        rows = [(p.request.sampling, len(p.request.generated), self.cache.get(p.request.rid).state_slot)
+                for p in plan if p.sample]
+        packed = self.sampler.pack(rows) if rows else None
+        ctx = self.runner.prepare(entries, patches, {"sample_rows": packed} if packed is not None else None)
+        return plan, entries, ctx, rows
 
     DEFER = "defer"
 
     def _launch(self, prep, before=None):
         """Queues a prepared step and its sampling, and books it with a placeholder for every token being sampled.
         -> the step in flight."""
-        plan, entries, ctx = prep
+        plan, entries, ctx, rows = prep
         logits = self.runner.launch(ctx, entries, self.sampler.ret if before is not None else None)
         picks = [p for p in plan if p.sample]
-        rows = []
-        for p in picks:
+        for p, (_, _, slot) in zip(picks, rows):
             r = p.request
-            slot = self.cache.get(r.rid).state_slot
             if r.sampling.penalised and r.needs_penalty_start:
                 self.sampler.start_row(slot, r.prompt, r.generated)
             r.needs_penalty_start = False
-            rows.append((r.sampling, len(r.generated), slot))
-        pending = self.sampler.sample_async(logits, rows, self.runner.err)
+        params = self.runner.inputs.get("sample_rows") if self.runner.inputs.has("sample_rows") else None
+        pending = self.sampler.sample_async(logits, rows, self.runner.err, params)
         ended = self.scheduler.advance(plan, [self.PLACEHOLDER] * len(picks))
         return _Flight(plan, picks, [len(p.request.generated) - 1 for p in picks], pending, ended)
 

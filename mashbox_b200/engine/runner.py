@@ -76,11 +76,12 @@ class ModelRunner:
         self.cache.flush_tables()
         return ctx
 
-    def prepare(self, entries, patches=()):
+    def prepare(self, entries, patches=(), extra=None):
         """Takes the pages the entries need, lays the step's integer arrays out on the host and lets the mixers plan.
         Nothing is sent to the device yet, so a step can be prepared while the step before it still runs, and token
         ids that are not known yet can be patched in on the host (patch_token) before launch(), or on the device:
         patches = (place among the step's tokens, index among the ids the step before samples) pairs.
+        extra: {name: int32 array} that travel to the device with the step's own arrays (the sampler's row settings).
         -> StepContext"""
         cache = self.cache
         seen = set()
@@ -132,6 +133,8 @@ class ModelRunner:
         inp.add("seq_row", rows)
         inp.add("state_slot", ctx.state_slots)
         inp.add("patch", np.asarray([v for pair in patches for v in pair], np.int32))
+        for name, array in (extra or {}).items():
+            inp.add(name, array)
         self.model.prepare(ctx)
         return ctx
 

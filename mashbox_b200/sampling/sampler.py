@@ -42,9 +42,23 @@ class Sampler:
         logits in order.  -> list of token ids (one device-to-host copy)."""
         return self.wait(self.sample_async(logits, rows, err))
 
-    def sample_async(self, logits, rows, err=None):
+    @staticmethod
+    def pack(rows):
+        """The rows' settings as the kernels read them (one ROW each), as an int32 array; None when every row is plainly
+        greedy (the argmax kernel needs none)."""
+        if all(p.plain_greedy for p, _, _ in rows):
+            return None
+        packed = np.zeros(len(rows), ROW)
+        for i, (p, step, slot) in enumerate(rows):
+            packed[i] = (p.temperature, p.top_p, p.min_p, p.repetition_penalty, p.frequency_penalty,
+                         p.presence_penalty, p.top_k, slot if p.penalised else -1, p.seed & 0xFFFFFFFF,
+                         (p.seed >> 32) & 0xFFFFFFFF, step, i)
+        return packed.view(np.int32)
+
+    def sample_async(self, logits, rows, err=None, params=None):
         """Launches the sampling kernels and starts the copy of the ids (and of the kernels' error word, when given)
-        to pinned host memory.  -> a handle for wait()."""
+        to pinned host memory.  -> a handle for wait().  params: pack(rows) already on the device (the engine sends it
+        with the step's arrays; a copy from pageable memory here would make the host wait for the GPU)."""
         n = len(rows)
         if n == 0:
             return None
@@ -57,14 +71,10 @@ class Sampler:
         if all(p.plain_greedy for p, _, _ in rows):
             kernels.argmax(logits[:n], out)
         else:
-            packed = np.zeros(n, ROW)
-            for i, (p, step, slot) in enumerate(rows):
-                packed[i] = (p.temperature, p.top_p, p.min_p, p.repetition_penalty, p.frequency_penalty,
-                             p.presence_penalty, p.top_k, slot if p.penalised else -1, p.seed & 0xFFFFFFFF,
-                             (p.seed >> 32) & 0xFFFFFFFF, step, i)
+            if params is None:
+                params = torch.from_numpy(self.pack(rows)).to(self.device)
             if any(p.penalised for p, _, _ in rows):
                 self._penalty_state()
-            params = torch.from_numpy(packed.view(np.uint8).copy()).to(self.device)
             if self.work is None or self.work.shape[0] < n:
                 self.work = torch.empty((max(n, self.max_slots), self.V), dtype=torch.float32, device=self.device)
             cuts = any(p.temperature > 0 and (p.top_k > 0 or p.top_p < 1.0 or p.min_p > 0.0) for p, _, _ in rows)
