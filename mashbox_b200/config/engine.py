@@ -14,7 +14,7 @@ class EngineConfig:
     max_tokens_per_step: int = 2048    # token budget of one step (decode tokens first, then prompt portions)
     chunk: int = 2048                  # most prompt tokens of one request in one step
     max_context: int = 0               # most tokens of one request (prompt + new); 0 = what the pool holds
-    cuda_graphs: bool = True           # replay captured graphs for decode-only steps
+    cuda_graphs: bool = True           # capture a step shape that comes a second time and replay it from then on
     device: str = "cuda:0"
 
     def __post_init__(self):
