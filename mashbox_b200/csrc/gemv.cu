@@ -41,6 +41,16 @@ __device__ __forceinline__ float dot8(const uint4& w, const uint4& x, float acc)
 //          thread that owns it.
 struct GemvNorm { const float* x; const float* w; float eps; };
 
+// MODE 4: the rows of W are the q, k and v heads of an attention layer.  The product's epilogue is the rotate-and-store
+// step: bias, rotation of the q and k heads by the token's position, q into the output, k and v into their cache pages.
+// A warp takes the two rows of a rotated pair, so the pair meets in one lane.
+struct GemvRope {
+    const int* positions; const int* tok_row; const int* table; int max_blocks;
+    bf16* kpool; bf16* vpool; const float* freqs; const float* bias;
+    int H, KV, HD, RD, pairing, page, num_pages;
+    int* err;
+};
+
 // the activations: from global memory through the read-only path, or from the block's shared memory
 template <bool SHARED> __device__ __forceinline__ uint4 gv_act(const bf16* p) {
     return SHARED ? *reinterpret_cast<const uint4*>(p) : __ldg(reinterpret_cast<const uint4*>(p));
@@ -56,7 +66,7 @@ __device__ __forceinline__ void gv_load8(const float* p, float (&v)[8]) {
 template <int NT, int MODE, bool NORM>
 __global__ void __launch_bounds__(GV_WARPS * 32) gemv_kernel(const bf16* __restrict__ act, const bf16* __restrict__ W,
                                                              void* __restrict__ out, int M, int K, GemvNorm nrm,
-                                                             const float* __restrict__ bias) {
+                                                             const float* __restrict__ bias, GemvRope rope) {
     extern __shared__ __align__(16) unsigned char gv_smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (NORM) {
@@ -100,10 +110,21 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_kernel(const bf16* __restr
     }
     const int units = MODE == 1 ? M : (M + GV_ROWS - 1) / GV_ROWS;
     for (int unit = blockIdx.x * GV_WARPS + warp; unit < units; unit += gridDim.x * GV_WARPS) {
-    const int m0 = MODE == 1 ? unit : unit * GV_ROWS;               // MODE 1: one feature (two rows); else two rows
+    int m0 = MODE == 1 ? unit : unit * GV_ROWS;                     // MODE 1: one feature (two rows); else two rows
+    int m1 = MODE == 1 ? M + m0 : min(m0 + 1, M - 1);
+    int pair = 0;                                                    // MODE 4: index of the rotated pair, -1: not rotated
+    if (MODE == 4) {
+        const int hh = rope.HD / 2, rh = rope.RD / 2, head = unit / hh, i = unit % hh;
+        int e0, e1;
+        if (rope.pairing == 0) { e0 = 2 * i; e1 = e0 + 1; pair = i < rh ? i : -1; }
+        else if (i < rh) { e0 = i; e1 = i + rh; pair = i; }
+        else { e0 = rope.RD + 2 * (i - rh); e1 = e0 + 1; pair = -1; }
+        m0 = head * rope.HD + e0;
+        m1 = head * rope.HD + e1;
+    }
     const bf16* rows[GV_ROWS];
     rows[0] = W + (size_t)m0 * K;
-    rows[1] = MODE == 1 ? W + (size_t)(M + m0) * K : W + (size_t)min(m0 + 1, M - 1) * K;
+    rows[1] = W + (size_t)m1 * K;
     float acc[GV_ROWS][NT];
 #pragma unroll
     for (int r = 0; r < GV_ROWS; r++)
@@ -161,7 +182,33 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_kernel(const bf16* __restr
     if (lane != 0) continue;
 #pragma unroll
     for (int n = 0; n < NT; n++) {
-        if (MODE == 1) {
+        if (MODE == 4) {
+            // as the separate kernels do it: the product rounded to bf16, then bias and rotation in float, then bf16
+            float a = __bfloat162float(__float2bfloat16_rn(acc[0][n])), b = __bfloat162float(__float2bfloat16_rn(acc[1][n]));
+            if (rope.bias) { a += rope.bias[m0]; b += rope.bias[m1]; }
+            const int head = m0 / rope.HD, pos = rope.positions[n];
+            if (pair >= 0 && rope.freqs && head < rope.H + rope.KV) {
+                float s, c;
+                sincosf((float)pos * rope.freqs[pair], &s, &c);
+                const float ra = a * c - b * s, rb = a * s + b * c;
+                a = ra; b = rb;
+            }
+            if (head < rope.H) {
+                reinterpret_cast<bf16*>(out)[(size_t)n * M + m0] = __float2bfloat16_rn(a);
+                reinterpret_cast<bf16*>(out)[(size_t)n * M + m1] = __float2bfloat16_rn(b);
+            } else if (rope.kpool) {
+                const int pg = rope.table[(size_t)rope.tok_row[n] * rope.max_blocks + pos / rope.page];
+                if (pg < 0 || pg >= rope.num_pages) {
+                    mb_set_error(rope.err, pg < 0 ? MB_ERR_PAGE_MISSING : MB_ERR_PAGE_RANGE);
+                } else {
+                    const int kvh = (head - rope.H) % rope.KV;
+                    bf16* pool = head < rope.H + rope.KV ? rope.kpool : rope.vpool;
+                    bf16* dst = pool + (((size_t)pg * rope.KV + kvh) * rope.page + pos % rope.page) * rope.HD;
+                    dst[m0 % rope.HD] = __float2bfloat16_rn(a);
+                    dst[m1 % rope.HD] = __float2bfloat16_rn(b);
+                }
+            }
+        } else if (MODE == 1) {
             // gate and up pass through bf16 as they do when the products are separate kernels
             const float g = __bfloat162float(__float2bfloat16_rn(acc[0][n])), up = __bfloat162float(__float2bfloat16_rn(acc[1][n]));
             reinterpret_cast<bf16*>(out)[(size_t)n * M + m0] = __float2bfloat16_rn((g / (1.0f + expf(-g))) * up);
@@ -258,7 +305,7 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_long_kernel(const bf16* __
 
 template <int MODE, bool NORM>
 static int gemv_launch(const void* act, const void* W, void* out, int N, int M, int K, GemvNorm nrm, const float* bias,
-                       cudaStream_t st) {
+                       cudaStream_t st, GemvRope rope = GemvRope{}) {
     if (N == 0 || M == 0) return 0;
     if (N > GV_MAX_TOKENS || K % 8 || K < 8 || (reinterpret_cast<uintptr_t>(W) & 15) ||
         (!NORM && (reinterpret_cast<uintptr_t>(act) & 15)))
@@ -267,7 +314,7 @@ static int gemv_launch(const void* act, const void* W, void* out, int N, int M, 
     const bf16* a = (const bf16*)act;
     const bf16* w = (const bf16*)W;
     if (K >= GV_LONG_K) {
-        if (NORM) return -2;                                         // the normalised row is kept for K < GV_LONG_K only
+        if (NORM || MODE == 4) return -2;                            // the normalised row is kept for K < GV_LONG_K only
         const unsigned g2 = (unsigned)units;
         switch (N) {
             case 1: gemv_long_kernel<1, MODE><<<g2, GV_WARPS * 32, 0, st>>>(a, w, out, M, K, bias); break;
@@ -295,10 +342,10 @@ static int gemv_launch(const void* act, const void* W, void* out, int N, int M, 
         if (grid > (unsigned)(4 * sms)) grid = (unsigned)(4 * sms);
     }
     switch (N) {
-        case 1: gemv_kernel<1, MODE, NORM><<<grid, GV_WARPS * 32, smem, st>>>(a, w, out, M, K, nrm, bias); break;
-        case 2: gemv_kernel<2, MODE, NORM><<<grid, GV_WARPS * 32, smem, st>>>(a, w, out, M, K, nrm, bias); break;
-        case 3: gemv_kernel<3, MODE, NORM><<<grid, GV_WARPS * 32, smem, st>>>(a, w, out, M, K, nrm, bias); break;
-        default: gemv_kernel<4, MODE, NORM><<<grid, GV_WARPS * 32, smem, st>>>(a, w, out, M, K, nrm, bias); break;
+        case 1: gemv_kernel<1, MODE, NORM><<<grid, GV_WARPS * 32, smem, st>>>(a, w, out, M, K, nrm, bias, rope); break;
+        case 2: gemv_kernel<2, MODE, NORM><<<grid, GV_WARPS * 32, smem, st>>>(a, w, out, M, K, nrm, bias, rope); break;
+        case 3: gemv_kernel<3, MODE, NORM><<<grid, GV_WARPS * 32, smem, st>>>(a, w, out, M, K, nrm, bias, rope); break;
+        default: gemv_kernel<4, MODE, NORM><<<grid, GV_WARPS * 32, smem, st>>>(a, w, out, M, K, nrm, bias, rope); break;
     }
     MB_LAUNCH_CHECK();
     return 0;
@@ -325,4 +372,17 @@ MB_API int mb_gemv_normed_bf16(const float* x, const float* norm_w, float eps, c
 MB_API int mb_gemv_normed_swiglu_bf16(const float* x, const float* norm_w, float eps, const void* W, void* out, int N,
                                       int M, int K, cudaStream_t st) {
     return gemv_launch<1, true>(nullptr, W, out, N, M, K, GemvNorm{x, norm_w, eps}, nullptr, st);
+}
+// out (N, M) = the q part of rmsnorm(x) W^T + bias, rotated; the k and v parts go rotated / as they are into the pages
+// of the tokens' positions (kpool null: they are dropped).  M = (H + 2 KV) HD, K < 8,192.
+MB_API int mb_gemv_normed_qkv_bf16(const float* x, const float* norm_w, float eps, const void* W, void* out, int N, int M,
+                                   int K, const float* bias, const int* positions, const int* tok_row, const int* table,
+                                   int max_blocks, void* kpool, void* vpool, const float* freqs, int H, int KV, int HD,
+                                   int RD, int pairing, int page, int num_pages, int* err, cudaStream_t st) {
+    if (HD % 2 || RD % 2 || RD > HD || M != (H + 2 * KV) * HD || page < 1) return -2;
+    GemvRope r;
+    r.positions = positions; r.tok_row = tok_row; r.table = table; r.max_blocks = max_blocks;
+    r.kpool = (bf16*)kpool; r.vpool = (bf16*)vpool; r.freqs = freqs; r.bias = bias;
+    r.H = H; r.KV = KV; r.HD = HD; r.RD = RD; r.pairing = pairing; r.page = page; r.num_pages = num_pages; r.err = err;
+    return gemv_launch<4, true>(nullptr, W, out, N, M, K, GemvNorm{x, norm_w, eps}, nullptr, st, r);
 }

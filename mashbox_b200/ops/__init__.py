@@ -241,6 +241,22 @@ def linear_gemv_normed(x, norm_w, eps, w, out, mode="plain"):
     return out
 
 
+def linear_gemv_normed_qkv(x, norm_w, eps, w, out, bias, positions, tok_seq, table, kpool, vpool, freqs, H, KV, HD, RD,
+                           pairing, page, num_pages, err):
+    """x (N <= 4, K) float32 residual stream -> the fused q/k/v product of rmsnorm(x) with the rotate-and-store step in
+    its epilogue: out (N, (H + 2 KV) HD) bf16 receives the rotated q heads, the rotated k and the v heads go into the
+    pages of the tokens' positions (kpool None: dropped), as rope_kv_write would leave them."""
+    _cuda(x, norm_w, w, out, bias, positions, tok_seq, table, kpool, vpool, freqs)
+    N, K = x.shape
+    f = _fn("gemv", "mb_gemv_normed_qkv_bf16",
+            [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+             c_int, c_void_p, c_void_p, c_void_p] + [c_int] * 7 + [c_void_p, c_void_p])
+    _check(f(_p(x), _p(norm_w), float(eps), _p(w), _p(out), N, out.shape[1], K, _p(bias), _p(positions), _p(tok_seq),
+             _p(table), table.shape[1], _p(kpool), _p(vpool), _p(freqs), H, KV, HD, RD, pairing, page, num_pages,
+             _p(err), _stream()), "gemv_normed_qkv")
+    return out
+
+
 def linear_gemv_residual(a, w, x, bias=None):
     """x (N <= 4, M) float32 += a (N, K) bf16 @ w (M, K)^T (+ bias (M) float32), in place"""
     _cuda(a, w, x, bias)

@@ -134,27 +134,35 @@ class Attention:
         H, KV, HD = self.H, self.KV, self.HD
         width = (H + 2 * KV) * HD
         qkv = ctx.ws.get("qkv", N, (width,), ctx.dtype)
-        if normed is not None:
-            x, norm = normed
-            w, eps = norm.fusable()
-            ops.linear_gemv_normed(x, w, eps, self.wqkv, qkv)
-        else:
-            ops.linear(h, self.wqkv, out=qkv)
         group, kpool, vpool = ctx.cache.layer_cache(run.cache)
         table = group.device_table
         page, pages = ctx.cache.page_size, ctx.cache.num_pages
-        freqs, rd, pairing = (None, HD, 0)
-        if self.position is not None:
-            rot = self.position.rotation()
+        rot = self.position.rotation() if self.position is not None else (None, HD, 0)
+        if normed is not None and rot is not None:
+            # a step of very few tokens: norm, product, rotation and the cache write in one kernel
+            x, norm = normed
+            w, eps = norm.fusable()
+            freqs, rd, pairing = rot
+            ops.linear_gemv_normed_qkv(x, w, eps, self.wqkv, qkv, self.bqkv, ctx.dev("positions"), ctx.dev("tok_row"),
+                                       table, kpool if run.write else None, vpool if run.write else None, freqs, H, KV,
+                                       HD, rd, pairing, page, pages, ctx.err)
+        else:
+            if normed is not None:
+                x, norm = normed
+                w, eps = norm.fusable()
+                ops.linear_gemv_normed(x, w, eps, self.wqkv, qkv)
+            else:
+                ops.linear(h, self.wqkv, out=qkv)
+            freqs, rd, pairing = (None, HD, 0)
             if rot is None:
                 if self.bias:
                     raise ConfigError("a position encoding with its own kernel cannot be combined with q/k/v biases")
                 self.position.apply(ctx, qkv, H, KV, HD)
             else:
                 freqs, rd, pairing = rot
-        ops.rope_kv_write(qkv, self.bqkv, ctx.dev("positions"), ctx.dev("tok_row"), table,
-                          kpool if run.write else None, vpool if run.write else None, freqs, H, KV, HD, rd, pairing,
-                          page, pages, ctx.err)
+            ops.rope_kv_write(qkv, self.bqkv, ctx.dev("positions"), ctx.dev("tok_row"), table,
+                              kpool if run.write else None, vpool if run.write else None, freqs, H, KV, HD, rd, pairing,
+                              page, pages, ctx.err)
         out = ctx.ws.get("attn_out", N, (H * HD,), ctx.dtype)
         if self.uses_mma(ctx):
             plan = ctx.memo[self.plan_key()]

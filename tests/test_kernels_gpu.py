@@ -530,6 +530,42 @@ def test_matrix_vector_product_that_normalises_and_one_that_adds_to_the_stream(N
     close(got, want + bias.double(), torch.float32, "residual add with a bias")
 
 
+@pytest.mark.parametrize("pairing,HD,RD,H,KV,bias", [("adjacent", 64, 64, 4, 2, True), ("halves", 32, 16, 3, 1, False),
+                                                     ("halves", 128, 128, 2, 2, True), ("adjacent", 48, 32, 2, 1, False)])
+def test_qkv_product_with_rotation_and_cache_write_in_its_epilogue(pairing, HD, RD, H, KV, bias):
+    """norm + q/k/v product + rotation + cache write as one kernel (one-token steps) leaves exactly what the normalising
+    product followed by the rotate-and-store kernel leaves: q in the buffer, k and v in their pages"""
+    K_ = ops()
+    g = torch.Generator().manual_seed(23)
+    D, page = 256, 8
+    seqs = G.PagedSequences([37, 5, 90], [1, 1, 1], H, KV, HD, page, torch.bfloat16, seed=6).build()
+    N, M = seqs.N, (H + 2 * KV) * HD
+    x = (2.0 * torch.randn(N, D, generator=g)).to(G.DEV)
+    nw = (1.0 + 0.2 * torch.randn(D, generator=g)).to(G.DEV)
+    w = (torch.randn(M, D, generator=g) / D ** 0.5).bfloat16().to(G.DEV)
+    b = (0.5 * torch.randn(M, generator=g)).to(G.DEV) if bias else None
+    freqs = torch.from_numpy(plain.rope_frequencies(10000.0, RD, None)).to(G.DEV)
+    pr = 0 if pairing == "adjacent" else 1
+    err = K_.new_error_word(G.DEV)
+    k1, v1 = torch.zeros_like(seqs.kpool), torch.zeros_like(seqs.vpool)
+    one = torch.zeros(N, M, device=G.DEV, dtype=torch.bfloat16)
+    K_.linear_gemv_normed_qkv(x, nw, 1e-5, w, one, b, seqs.positions, seqs.tok_row, seqs.table, k1, v1, freqs, H, KV, HD, RD,
+                              pr, page, seqs.num_pages, err)
+    k2, v2 = torch.zeros_like(seqs.kpool), torch.zeros_like(seqs.vpool)
+    two = torch.empty(N, M, device=G.DEV, dtype=torch.bfloat16)
+    K_.linear_gemv_normed(x, nw, 1e-5, w, two, "plain")
+    K_.rope_kv_write(two, b, seqs.positions, seqs.tok_row, seqs.table, k2, v2, freqs, H, KV, HD, RD, pr, page,
+                     seqs.num_pages, err)
+    K_.check_error_word(err)
+    assert torch.equal(one[:, :H * HD], two[:, :H * HD])
+    assert torch.equal(k1, k2) and torch.equal(v1, v2) and float(k1.float().abs().sum()) > 0
+    # without pools nothing is stored, q is the same
+    three = torch.zeros(N, M, device=G.DEV, dtype=torch.bfloat16)
+    K_.linear_gemv_normed_qkv(x, nw, 1e-5, w, three, b, seqs.positions, seqs.tok_row, seqs.table, None, None, freqs, H, KV,
+                              HD, RD, pr, page, seqs.num_pages, err)
+    assert torch.equal(three[:, :H * HD], one[:, :H * HD])
+
+
 @pytest.mark.parametrize("N,M,K", [(1, 4096, 4096), (4, 6144, 4096), (2, 509, 320), (3, 4096, 14336), (1, 57, 72), (2, 37, 8200)])
 def test_matrix_vector_product(N, M, K):
     """at most 4 tokens: one warp per two rows of W, float32 sums; plain, float32 out and fused SwiGLU"""
