@@ -6,6 +6,7 @@ there, the call fails.  The only library call is the bf16 matrix product (cuBLAS
 the reference engine, too, hands its contractions to a library (src/mashbox/ops/dense16.py:73-75).
 """
 import ctypes
+import os
 
 import torch
 
@@ -216,6 +217,8 @@ def linear_tc5(a, w, out, mode="plain"):
 # the FMA pipe) already costs more than the stream.  GEMV[mode] = the most tokens the engine gives the kernel (0: never);
 # "fused": the forms that normalise the residual stream themselves or add their product into it (see small_fused_supports).
 GEMV = {"swiglu": 1, "plain": 1, "fused": 1}
+if os.environ.get("MASHBOX_GEMV_TOKENS"):          # a tuning knob: the same limit for the three kinds
+    GEMV = {k: int(os.environ["MASHBOX_GEMV_TOKENS"]) for k in GEMV}
 
 
 def gemv_supports(N, K, mode="plain"):
