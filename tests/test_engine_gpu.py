@@ -173,6 +173,64 @@ def test_a_step_that_needs_ids_still_in_flight_waits_for_them(tmp_path_factory):
     assert eng.cache.free_pages() == [eng.cache.num_pages]
 
 
+@pytest.mark.parametrize("seed", [1, 4])
+def test_random_traffic_equals_each_request_alone(tmp_path_factory, seed):
+    """36 requests of random lengths, samplers, stop tokens and arrival times through an engine with three slots, 192
+    tokens of cache and 48 tokens a step (portions, preemptions, a few cancellations, two steps in flight all along):
+    in float32 every answer is the one the request gets alone in a roomy engine, cut at its stop token."""
+    import random
+    rng = random.Random(seed)
+    folder, roomy = engine(tmp_path_factory.mktemp("m"), "A", "f32", max_tokens=512, max_requests=2)
+    vocab = H.TINY["A"][0].vocab
+
+    def samp():
+        if rng.random() < 0.3:
+            return None
+        d = dict(temperature=rng.choice([0.5, 0.9, 1.3]), seed=rng.randrange(1 << 40))
+        if rng.random() < 0.4: d["top_k"] = rng.choice([1, 5, 40])
+        if rng.random() < 0.4: d["top_p"] = rng.choice([0.3, 0.8, 0.95])
+        if rng.random() < 0.2: d["min_p"] = 0.05
+        if rng.random() < 0.3: d["repetition_penalty"] = 1.2
+        if rng.random() < 0.2: d["frequency_penalty"] = 0.3
+        return d
+
+    reqs = [dict(ids=[rng.randrange(vocab) for _ in range(rng.randint(1, 70))], max_new=rng.randint(1, 36), samp=samp())
+            for _ in range(36)]
+    alone = [roomy.generate([q["ids"]], max_new=q["max_new"], samp=[q["samp"]])["ids"][0] for q in reqs]
+    for q, a in zip(reqs, alone):
+        if rng.random() < 0.35 and a:
+            q["stop_ids"] = (a[rng.randrange(len(a))],)
+    want = [a[:a.index(q["stop_ids"][0])] if q.get("stop_ids") else a for q, a in zip(reqs, alone)]
+    from mashbox_b200.engine.engine import Engine
+    tight = Engine.from_folder(folder, dtype="float32", page_size=H.TINY["A"][2], max_tokens=192, max_requests=3,
+                               max_tokens_per_step=48, chunk=32)
+    rows, pending, cancelled, steps = {}, list(range(len(reqs))), set(), 0
+    while pending or tight.busy():
+        if pending and (rng.random() < 0.3 or not tight.busy()):
+            n = rng.randint(1, 4)
+            take, pending = pending[:n], pending[n:]
+            for i, r in zip(take, tight.admit([reqs[i] for i in take])):
+                rows[i] = r
+        if rng.random() < 0.03:
+            live = [i for i, r in rows.items() if r.finish is None and i not in cancelled]
+            if live:
+                i = live[rng.randrange(len(live))]
+                cancelled.add(i)
+                tight.cancel([rows[i]])
+        tight.step()
+        steps += 1
+        assert steps < 20000
+    for i, r in rows.items():
+        assert -1 not in r.generated
+        if r.finish == "cancel":
+            assert r.generated == want[i][:len(r.generated)]
+        else:
+            assert r.generated == want[i], (i, r.finish, reqs[i].get("samp"), reqs[i].get("stop_ids"), r.preemptions)
+            assert r.finish == ("stop" if reqs[i].get("stop_ids") else "length")
+    tight.cache.check()
+    assert tight.cache.free_pages() == [tight.cache.num_pages]
+
+
 def test_cancel_through_on_step(tmp_path_factory):
     _, eng = engine(tmp_path_factory.mktemp("m"), "A", "f32")
     prompts = H.prompts_for("A", (9, 9), seed=7)
