@@ -275,15 +275,55 @@ def run_kernels(a):
     x, w = rnd(T, D), rnd(2 * F, D)
     y = torch.empty(T, F, device=dev, dtype=torch.bfloat16)
     out["prefill_gate_up_swiglu_fused"] = {"own_us": timed(lambda: ops.linear_tc5(x, w, y, "swiglu"))}
-    for name, M, K in (("o", D, D), ("gate_up", 2 * F, D), ("head", V, D)):
-        x, w = rnd(a.batch, K), rnd(M, K)
-        y = torch.empty(a.batch, M, device=dev, dtype=torch.bfloat16)
-        own = timed(lambda: ops.linear_stream(x, w, y, "plain"))
-        lib = timed(lambda: torch.mm(x, w.t(), out=y))
-        out[f"decode_{name}"] = {"own_us": own, "library_us": lib, "own_gbs": M * K * 2 / own / 1e3, "library_gbs": M * K * 2 / lib / 1e3}
+    # decode batch: every product as a captured graph of launches over different weights (more than the L2 holds), so the
+    # figure is the time from launch to launch inside a step; library product against the matrix-vector kernel (at most
+    # 4 tokens) and the weight-streaming kernel with its folded forms
+    def chained(f, n_w):
+        for i in range(n_w):
+            f(i)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(n_w):
+                f(i)
+        g.replay()
+        ts = []
+        for _ in range(5):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) * 1e3 / n_w)
+        return statistics.median(ts)
+
+    B = a.batch
+    for name, M, K in (("o", D, D), ("qkv", QKV, D), ("down", D, F), ("gate_up", 2 * F, D)):
+        n_w = max(8, int(600e6 // (M * K * 2)))
+        ws = [rnd(M, K) for _ in range(n_w)]
+        x, y = rnd(B, K), torch.empty(B, M, device=dev, dtype=torch.bfloat16)
+        h = torch.randn(B, K, device=dev, generator=gen)
+        hs = torch.randn(B, M, device=dev, generator=gen)
+        nw = torch.ones(K, device=dev)
+        sums_in = torch.full(((K + 127) // 128, 16), 128.0, device=dev)
+        sums_out = torch.empty((M + 127) // 128, 16, device=dev)
+        r = {"library_us": chained(lambda i: torch.mm(x, ws[i].t(), out=y), n_w),
+             "stream_us": chained(lambda i: ops.linear_stream(x, ws[i], y, "plain"), n_w),
+             "stream_normed_us": chained(lambda i: ops.linear_stream_normed(h, nw, 1e-5, ws[i], y, "plain", sums_in), n_w),
+             "stream_residual_us": chained(lambda i: ops.linear_stream_residual(x, ws[i], hs, None, sums_out), n_w)}
+        if B <= 4:
+            r["gemv_us"] = chained(lambda i: ops.linear_gemv(x, ws[i], y, "plain"), n_w)
+        if name == "gate_up":
+            act, hh = torch.empty(B, F, device=dev, dtype=torch.bfloat16), torch.empty(B, K, device=dev, dtype=torch.bfloat16)
+            r["stream_normed_swiglu_us"] = chained(lambda i: ops.linear_stream_normed(h, nw, 1e-5, ws[i], act, "swiglu", sums_in), n_w)
+            r["norm_library_gate_us"] = chained(lambda i: (ops.add_rmsnorm(h, None, None, nw, 1e-5, hh, None),
+                                                           torch.mm(hh, ws[i].t(), out=y), ops.swiglu(y, act)), n_w)
+        r["ideal_us_at_peak"] = M * K * 2 / peaks()["hbm_gbs"] / 1e3
+        out[f"decode_b{B}_{name}"] = r
+        del ws
     ops.check_error_word(ops.error_word(dev))
-    print(json.dumps({"impl": "ours", "kernels": out, "note": "CUDA-event time of single launches after an L2 flush; "
-                      "launch gaps of the Python caller are inside these figures"}))
+    print(json.dumps({"impl": "ours", "kernels": out, "note": "prefill: CUDA-event time of single launches after an L2 flush (launch gaps "
+                      "of the Python caller are inside); decode: per launch inside a captured graph of launches over different weights"}))
     return 0
 
 

@@ -225,14 +225,6 @@ def gemv_supports(N, K, mode="plain"):
     return 1 <= N <= min(4, GEMV["swiglu" if mode == "swiglu" else "plain"]) and K >= 8 and K % 8 == 0
 
 
-def small_fused_supports(N, K, dtype):
-    """True when a step of N tokens of width K can run its layers on the folded matrix-vector kernels: the product that
-    follows a norm normalises the float32 residual stream itself (linear_gemv_normed), the product that ends a
-    sublayer adds into it (linear_gemv_residual)."""
-    return (dtype == torch.bfloat16 and 1 <= N <= min(4, GEMV["fused"]) and K % 8 == 0 and 8 <= K < 8192
-            and N * K * 2 <= 48 * 1024)
-
-
 def linear_gemv_normed(x, norm_w, eps, w, out, mode="plain"):
     """x (N <= 4, K) float32 residual stream, norm_w (K) float32 -> out (N, M) bf16 = rmsnorm(x) W^T ("swiglu": W is
     (2M, K) and out = silu(gate) * up), the normalised row rounded to bf16 as the norm kernel would store it."""
@@ -279,38 +271,135 @@ def linear_gemv(a, w, out, mode="plain"):
     return out
 
 
-# The tcgen05 weight-streaming product for decode batches (at most 16 tokens): W is the M side of the product.  Off by
-# default: measured on a B200 it matches the library on the output head (6.3 against 6.7 TB/s) and loses on the layer's
-# own matrices, which have too few row tiles and must be cut along K (1.6 to 3 against 2.9 to 5.8 TB/s).
-STREAM = {"enabled": False}
+# The weight-streaming products for decode batches (at most 16 tokens; gemm_stream.cu): every SM streams the same share
+# of W by TMA whatever the matrix's shape, mma.sync on the tiles, and the forms of the matrix-vector kernels exist here
+# too (normalising, SwiGLU, adding into the residual stream, q/k/v with rotation and cache write), so a layer is five
+# kernels.  Off by default: measured inside captured graphs on the Llama-3.1-8B shapes at 8 tokens, own / library, us:
+# output product 13.0 / 12.0, q/k/v 15.9 / 11.9, down 27.0 / 23.3, gate/up 42.3 / 40.3 -- the library's kernels run at
+# the rate at which TMA copies alone stream these matrices (8.6, 11.2, 21.3, 38.9 us), this kernel 3 to 5 us above it
+# (1.5 us until its first copy is issued, the meeting of the blocks that share a row tile, uneven finishing times of
+# the SMs), which is more than the folded kernels save: the whole decode step at batch 8 runs at 1,432 tokens/s with
+# these products against 1,616 with the library's.  STREAM["tokens"]: the most tokens the engine gives them (0: never).
+STREAM = {"tokens": 0}
+if os.environ.get("MASHBOX_STREAM_TOKENS"):        # a tuning knob
+    STREAM = {"tokens": int(os.environ["MASHBOX_STREAM_TOKENS"])}
 _stream_scratch = {}
 
 
 def stream_supports(N, K):
-    return STREAM["enabled"] and 1 <= N <= 16 and K >= 8 and K % 8 == 0
+    return 1 <= N <= min(16, STREAM["tokens"]) and K >= 8 and K % 8 == 0
+
+
+def _stream_buffers(device, M):
+    """(workspace, counters) of the streaming products on this device: the partial sums of row tiles that blocks
+    share, and a counter per row tile, zero between launches"""
+    lib = load_library("gemm_stream")
+    lib.mb_gemm_stream_workspace.restype = ctypes.c_longlong
+    key = str(device)
+    sc = _stream_scratch.get(key)
+    tiles = (M + 127) // 128
+    if sc is None or sc[1].numel() < tiles:
+        sc = (torch.empty(lib.mb_gemm_stream_workspace(), dtype=torch.float32, device=device),
+              torch.zeros(max(tiles, 8192), dtype=torch.int32, device=device))
+        _stream_scratch[key] = sc
+    return sc
 
 
 def linear_stream(a, w, out, mode="plain"):
-    """a (N <= 16, K) bf16, w (M, K) bf16 ("swiglu": (2M, K)) -> out (N, M), as linear_tc5, for decode batches."""
+    """a (N <= 16, K) bf16, w (M, K) bf16 ("swiglu": (2M, K)) -> out (N, M): bf16, or float32 for mode "float"."""
     _cuda(a, w, out)
     N, K = a.shape
     M = out.shape[1]
-    lib = load_library("gemm_tc5")
-    lib.mb_gemm_tc5_stream_workspace.restype = ctypes.c_longlong
-    lib.mb_gemm_tc5_stream_workspace.argtypes = [c_int, c_int, c_int]
-    need = lib.mb_gemm_tc5_stream_workspace(M, K, 2 if mode == "swiglu" else 1)
-    key = str(a.device)
-    sc = _stream_scratch.get(key)
-    tiles = (M + 127) // 128
-    if sc is None or sc[0].numel() < need or sc[1].numel() < tiles:
-        sc = (torch.empty(max(need, 1 << 20), dtype=torch.float32, device=a.device),
-              torch.zeros(max(tiles, 4096), dtype=torch.int32, device=a.device))
-        _stream_scratch[key] = sc
-    name = {"plain": "mb_gemm_tc5_stream_bf16", "swiglu": "mb_gemm_tc5_stream_swiglu_bf16",
-            "float": "mb_gemm_tc5_stream_f32out"}[mode]
-    f = _fn("gemm_tc5", name, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
-    _check(f(_p(a), _p(w), _p(out), N, M, K, _p(sc[0]), _p(sc[1]), _p(error_word(a.device)), _stream()), "gemm_tc5_stream")
+    ws, cnt = _stream_buffers(a.device, M)
+    f = _fn("gemm_stream", "mb_gemm_stream", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                                              c_void_p, c_void_p])
+    _check(f(_p(a), _p(w), _p(out), N, M, K, {"plain": 0, "swiglu": 1, "float": 2}[mode], _p(ws), _p(cnt),
+             _p(error_word(a.device)), _stream()), "gemm_stream")
     return out
+
+
+def linear_stream_residual(a, w, x, bias=None, sums=None):
+    """x (N <= 16, M) float32 += a (N, K) bf16 @ w (M, K)^T (+ bias (M) float32), in place.  sums (ceil(M / 128), 16)
+    float32, if given, receives the sums of squares of the new rows of x by tile of 128 columns: the normalising product
+    that follows takes them instead of reading the rows again."""
+    _cuda(a, w, x, bias, sums)
+    N, K = a.shape
+    M = x.shape[1]
+    ws, cnt = _stream_buffers(a.device, M)
+    f = _fn("gemm_stream", "mb_gemm_stream_residual", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
+                                                       c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(f(_p(a), _p(w), _p(x), _p(bias), N, M, K, _p(sums), _p(ws), _p(cnt), _p(error_word(a.device)), _stream()),
+           "gemm_stream_residual")
+    return x
+
+
+def linear_stream_normed(x, norm_w, eps, w, out, mode="plain", sums=None):
+    """x (N <= 16, K) float32 residual stream, norm_w (K) float32 -> out (N, M) bf16 = rmsnorm(x) W^T ("swiglu": W is
+    (2M, K) and out = silu(gate) * up).  The product runs on bf16(x * norm_w); 1 / rms scales the float sums.  sums:
+    what linear_stream_residual left for this x (else the kernel adds up the rows' squares itself)."""
+    _cuda(x, norm_w, w, out, sums)
+    N, K = x.shape
+    M = out.shape[1]
+    ws, cnt = _stream_buffers(x.device, M)
+    f = _fn("gemm_stream", "mb_gemm_stream_normed", [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                                     c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(f(_p(x), _p(norm_w), float(eps), _p(sums), _p(w), _p(out), N, M, K, {"plain": 0, "swiglu": 1}[mode], _p(ws), _p(cnt),
+             _p(error_word(x.device)), _stream()), "gemm_stream_normed")
+    return out
+
+
+def linear_stream_normed_qkv(x, norm_w, eps, w, out, bias, positions, tok_seq, table, kpool, vpool, freqs, H, KV, HD, RD,
+                             pairing, page, num_pages, err, sums=None):
+    """As linear_gemv_normed_qkv for up to 16 tokens; the head size must divide 128."""
+    _cuda(x, norm_w, w, out, bias, positions, tok_seq, table, kpool, vpool, freqs, sums)
+    N, K = x.shape
+    M = out.shape[1]
+    ws, cnt = _stream_buffers(x.device, M)
+    f = _fn("gemm_stream", "mb_gemm_stream_normed_qkv",
+            [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+             c_void_p, c_int, c_void_p, c_void_p, c_void_p] + [c_int] * 7 + [c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(f(_p(x), _p(norm_w), float(eps), _p(sums), _p(w), _p(out), N, M, K, _p(bias), _p(positions), _p(tok_seq),
+             _p(table), table.shape[1], _p(kpool), _p(vpool), _p(freqs), H, KV, HD, RD, pairing, page, num_pages, _p(ws),
+             _p(cnt), _p(err), _stream()), "gemm_stream_normed_qkv")
+    return out
+
+
+# ---- what the parts call at few tokens: the matrix-vector kernels where they are enabled, else the streaming products
+def _use_gemv_fused(N, K):
+    return 1 <= N <= min(4, GEMV["fused"]) and K % 8 == 0 and 8 <= K < 8192 and N * K * 2 <= 48 * 1024
+
+
+def small_fused_supports(N, K, dtype):
+    """True when a step of N tokens of width K can run its layers on the folded kernels: the product that follows a
+    norm normalises the float32 residual stream itself (linear_small_normed), the product that ends a sublayer adds
+    into it (linear_small_residual)."""
+    return dtype == torch.bfloat16 and (_use_gemv_fused(N, K) or stream_supports(N, K))
+
+
+def small_qkv_supports(N, K, HD):
+    """True when linear_small_normed_qkv takes this step (else: linear_small_normed, then rope_kv_write)"""
+    return _use_gemv_fused(N, K) or (stream_supports(N, K) and 128 % HD == 0)
+
+
+def linear_small_normed(x, norm_w, eps, w, out, mode="plain", sums=None):
+    if _use_gemv_fused(*x.shape):
+        return linear_gemv_normed(x, norm_w, eps, w, out, mode)
+    return linear_stream_normed(x, norm_w, eps, w, out, mode, sums)
+
+
+def linear_small_normed_qkv(x, *args, sums=None):
+    if _use_gemv_fused(*x.shape):
+        return linear_gemv_normed_qkv(x, *args)
+    return linear_stream_normed_qkv(x, *args, sums=sums)
+
+
+def linear_small_residual(a, w, x, bias=None, sums=None):
+    """-> True when `sums` was filled (see linear_stream_residual)"""
+    if _use_gemv_fused(a.shape[0], x.shape[1]) and a.shape[1] % 8 == 0:
+        linear_gemv_residual(a, w, x, bias)
+        return False
+    linear_stream_residual(a, w, x, bias, sums)
+    return sums is not None
 
 
 def fused_swiglu_supports(N, F, K):
@@ -319,7 +408,7 @@ def fused_swiglu_supports(N, F, K):
 
 def linear_swiglu(a, wgu, out):
     """a (N, K) bf16, wgu (2F, K) = [gate rows | up rows] -> out (N, F) = silu(a Wg^T) * (a Wu^T), one kernel: the
-    tcgen05 product for prompt portions, its weight-streaming form for decode batches (when enabled).
+    tcgen05 product for prompt portions, the matrix-vector or the weight-streaming kernel for decode batches (where enabled).
     Only for shapes fused_swiglu_supports() takes."""
     _cuda(a, wgu, out)
     N, K = a.shape

@@ -212,3 +212,18 @@ class StepContext:
 
     def dev(self, name):
         return self.inputs.get(name)
+
+    # A product that adds into the residual stream x can leave the sums of squares of the new rows (by tile of 128
+    # columns); the normalising product of the next sublayer takes them instead of reading every row again.
+    def row_sums_buffer(self, x):
+        import torch
+        tiles = (x.shape[1] + 127) // 128
+        return self.ws.get("row_sums", tiles, (16,), torch.float32, reserve=tiles)
+
+    def hold_row_sums(self, x, sums):
+        self.memo["row_sums"] = (x.data_ptr(), sums)
+
+    def take_row_sums(self, x):
+        """-> the sums held for x as it is now, or None; they are used up"""
+        held = self.memo.pop("row_sums", None)
+        return held[1] if held is not None and held[0] == x.data_ptr() else None

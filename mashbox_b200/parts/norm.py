@@ -29,6 +29,8 @@ class RMSNorm:
         out = ctx.ws.get("normed" if rows is None else "normed_rows", n_out, (self.width,), ctx.dtype,
                          reserve=None if rows is None else ctx.options.get("logit_rows", 8))
         delta, bias = pending if pending is not None else (None, None)
+        if delta is not None:
+            ctx.take_row_sums(x)                # x changes here: sums held for it no longer describe it
         ctx.ops.add_rmsnorm(x, delta, bias, self.weight, self.eps, out, rows)
         return out
 

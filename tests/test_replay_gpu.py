@@ -113,3 +113,32 @@ def test_mixed_batches_with_page_reuse(tmp_path_factory, name, mode):
         H.check(got, folder, p, mode, f"mixed, request {i}")
     runner.cache.check()
     assert all(f == runner.cache.num_pages for f in runner.cache.free_pages())
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_streaming_products_for_steps_of_few_tokens(tmp_path_factory, name):
+    """the weight-streaming products (off by default) take every step of at most 16 tokens: norm, rotation, cache write,
+    gate and residual add inside the four products of a layer, the sums of squares handed from one to the next"""
+    import mashbox_b200.ops as ops
+    tmp = tmp_path_factory.mktemp("m")
+    before = dict(ops.STREAM)
+    ops.STREAM["tokens"] = 16
+    try:
+        folder, runner = runner_for(tmp, name, "bf16", 4 * 64)
+        p = H.prompts_for(name, (150,), seed=1)[0]
+        cut = len(p) - 32
+        steps = [dict(entries=[dict(id="a", tokens=p[:cut], want=[cut - 1])], end=[])]
+        steps += [dict(entries=[dict(id="a", tokens=[p[i]], want=[0])], end=["a"] if i == len(p) - 1 else [])
+                  for i in range(cut, len(p))]
+        out = replay(runner, steps)
+        H.check(np.concatenate([out[i] for i in range(len(steps))]), folder, p, "bf16", "last 32 decoded", slice(cut - 1, None))
+        prompts = H.prompts_for(name, (50, 33, 64, 20, 61, 47, 9, 58), seed=3)
+        steps, where = mixed_trace(prompts, np.random.default_rng(5), max_live=2)
+        assert sum(1 for s in steps if 2 <= sum(len(e["tokens"]) for e in s["entries"]) <= 16) >= 5
+        out = replay(runner, steps)
+        for i, q in enumerate(prompts):
+            got = np.concatenate([out[s][o:o + n] for s, o, n in where[i]])
+            H.check(got, folder, q, "bf16", f"mixed, request {i}")
+        runner.cache.check()
+    finally:
+        ops.STREAM.update(before)
