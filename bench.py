@@ -304,18 +304,18 @@ def run_kernels(a):
         x, y = rnd(B, K), torch.empty(B, M, device=dev, dtype=torch.bfloat16)
         h = torch.randn(B, K, device=dev, generator=gen)
         hs = torch.randn(B, M, device=dev, generator=gen)
-        nw = torch.ones(K, device=dev)
-        sums_in = torch.full(((K + 127) // 128, 16), 128.0, device=dev)
-        sums_out = torch.empty((M + 127) // 128, 16, device=dev)
+        nw, nw_out = torch.ones(K, device=dev), torch.ones(M, device=dev)
+        sums_in = torch.full(((K + 31) // 32, 16), 32.0, device=dev)
+        sums_out, scaled_out = torch.empty((M + 31) // 32, 16, device=dev), torch.empty(B, M, device=dev, dtype=torch.bfloat16)
         r = {"library_us": chained(lambda i: torch.mm(x, ws[i].t(), out=y), n_w),
              "stream_us": chained(lambda i: ops.linear_stream(x, ws[i], y, "plain"), n_w),
-             "stream_normed_us": chained(lambda i: ops.linear_stream_normed(h, nw, 1e-5, ws[i], y, "plain", sums_in), n_w),
-             "stream_residual_us": chained(lambda i: ops.linear_stream_residual(x, ws[i], hs, None, sums_out), n_w)}
+             "stream_of_normalised_us": chained(lambda i: ops.linear_stream(x, ws[i], y, "plain", sums_in, 1e-5), n_w),
+             "stream_residual_us": chained(lambda i: ops.linear_stream_residual(x, ws[i], hs, None, sums_out, nw_out, scaled_out), n_w)}
         if B <= 4:
             r["gemv_us"] = chained(lambda i: ops.linear_gemv(x, ws[i], y, "plain"), n_w)
         if name == "gate_up":
             act, hh = torch.empty(B, F, device=dev, dtype=torch.bfloat16), torch.empty(B, K, device=dev, dtype=torch.bfloat16)
-            r["stream_normed_swiglu_us"] = chained(lambda i: ops.linear_stream_normed(h, nw, 1e-5, ws[i], act, "swiglu", sums_in), n_w)
+            r["stream_of_normalised_swiglu_us"] = chained(lambda i: ops.linear_stream(x, ws[i], act, "swiglu", sums_in, 1e-5), n_w)
             r["norm_library_gate_us"] = chained(lambda i: (ops.add_rmsnorm(h, None, None, nw, 1e-5, hh, None),
                                                            torch.mm(hh, ws[i].t(), out=y), ops.swiglu(y, act)), n_w)
         r["ideal_us_at_peak"] = M * K * 2 / peaks()["hbm_gbs"] / 1e3

@@ -1,51 +1,49 @@
 // bf16 matrix products for decode batches (at most 16 tokens), bound by reading W once:
 // out[n, m] = sum_k act[n, k] * W[m, k].
 //
-// The work is the list of (row tile of 128 rows, k block of 64) items, row tile major, and block b of G takes the items
-// [T b / G, T (b + 1) / G): every SM streams the same number of bytes whatever the matrix's shape.  A block's range
-// covers the end of one row tile, whole row tiles, and the start of another; a row tile that several blocks share is
-// finished by the block that arrives last (a counter per row tile counts k blocks; it resets itself): every sharer
-// leaves its partial sums in its own slot of a workspace and the last one adds the slots in the order of the blocks,
-// so the result does not depend on which block was last.  A block works on its two shared tiles first, so that its
+// W is cut into row tiles of TH rows (128, 64 or 32: the largest height that still gives most SMs a tile, so that a
+// matrix of 4,096 rows is 128 tiles of 32 rows and no tile is shared) and k blocks of 16,384 / TH, so an item (row
+// tile, k block) is 32 KB of W.  When there are at most as many tiles as SMs the grid is one block per tile.
+// Otherwise the items, row tile major, are dealt in equal shares: block b of G takes [T b / G, T (b + 1) / G), which
+// covers the end of one row tile, whole row tiles, and the start of another; a tile that several blocks share is
+// finished by the block that arrives last (a counter per tile counts k blocks; it resets itself): every sharer leaves
+// its partial sums in its own slot of a workspace and the last one adds the slots in the order of the blocks, so the
+// result does not depend on which block was last.  A block works on its two shared tiles first, so that its
 // neighbours' sums meet while its whole tiles are still streaming.
 //
-// Roles of the 288 threads:
-//   warp 0     producer: one TMA box of W (128 rows x 64 k, 16 KB, 128-byte swizzle; two for SwiGLU: gate rows and up
-//              rows) and the 2 KB of activations that go with it per stage, ten stages in flight (six for SwiGLU); the
-//              first ring is issued before the block has set itself up;
-//   warps 1-4  consumers: ldmatrix from the swizzled tiles, mma.sync m16n8k16 with W as the row operand (32 rows per
-//              warp) and the 16 token columns as the other, sums in registers, then the sharing protocol above and
-//              the form's last step.  The product is a few percent of the tensor pipe at these sizes; the tcgen05
-//              path was measured here too and its tensor-memory allocation alone cost 1 to 2 us per launch, a fifth
-//              of the smaller products;
-//   warps 5-8  (normalising forms) make the activations themselves: x[n, k] * g[k] from the float32 residual stream,
-//              rounded to bf16, written into the stage in the layout the TMA would have produced.
+// Roles of the 192 threads:
+//   warp 0     producer: TMA boxes of W (TH rows x 64 k, 128-byte swizzle; for SwiGLU the gate rows and the up rows)
+//              and the 2 KB of activations that go with each, four to six stages of 36 to 48 KB in flight (three of
+//              68 KB for SwiGLU); the first ring is issued before the block has set itself up;
+//   warps 1-4  consumers: ldmatrix from the swizzled tiles, mma.sync m16n8k16 with W as the row operand and the 16
+//              token columns as the other, sums in registers; side by side along the rows of a tile and, for tiles of
+//              fewer than 128 rows, along k (their sums then meet in shared memory); then the form's last step.  The
+//              product is a few percent of the tensor pipe at these sizes; the tcgen05 path was measured here too and
+//              its tensor-memory allocation alone cost 1 to 2 us per launch, a fifth of the smaller products;
+//   warp 5     (SCALED) turns the sums of squares into every token's 1/rms meanwhile.
 //
 // Forms (EPI): 0 bf16 out; 1 SwiGLU (W = [gate rows | up rows], out = silu(gate) * up); 2 float out; 3 the float32
-// residual stream is added to in place (+ bias); 4 the fused q/k/v product with rotation and the write of k and v into
-// the pages of the cache.  NORM: the input is rmsnorm(x) of the float32 residual stream: the product runs on
-// bf16(x * g) and the token's 1/rms, which the consumer warps compute in float while the first tiles arrive, scales
-// the sums.
+// residual stream is added to in place (+ bias), and on request the product leaves what the norm after it needs: the
+// sums of squares of the new rows by 32 columns and the new rows times that norm's weight, in bf16.  (Rotation and the
+// cache write stay a kernel of their own after the q/k/v product: as an epilogue here, sixteen values per thread on
+// the few warps that finish a tile, they cost 9 to 15 us against its 3.)  SCALED: the input is such a pair (rows
+// times the norm's weight in bf16, sums of squares): the token's 1/rms, computed in float from the sums, scales the
+// float sums of the product, which makes it the product of rmsnorm(x) without a norm kernel.
 //
-// Sizes: K a multiple of 8; N <= 16; any M.  Form 4 wants a head size that divides 128.  Every wait on an mbarrier is
-// bounded; on a timeout the roles fall through to the end of the kernel.
+// Sizes: K a multiple of 8; N <= 16; any M.  Every wait on an mbarrier is bounded; on a timeout the roles fall through
+// to the end of the kernel.
 #include "tcgen05.cuh"
 
 #define S_NT 16                       // token columns of the accumulator
-#define S_BK 128                      // k per item: two 128-byte swizzle spans ("halves") of 64
-#define S_W_BYTES (2 * 128 * 64 * 2)  // a set of W per stage: two boxes of 128 rows x 64 k
-#define S_X_BYTES (2 * S_NT * 64 * 2) // the activations per stage: two tiles of 16 token rows x 64 k
-#define S_THREADS 288
-#define S_CONV_WARPS 4
+#define S_W_BYTES (32 * 1024)         // a set of W per stage: TH rows x (16,384 / TH) k, as boxes of TH rows x 64 k
+#define S_XBOX (S_NT * 64 * 2)        // the activations that go with one box: 16 token rows x 64 k
+#define S_SMEM (225 * 1024)           // what a block may use
+#define S_THREADS 192
 
-// ssq: sums of squares of the rows of x by row tile ([tiles][16], from the product that last added into x), or null
-struct StreamNorm { const float* x; const float* w; float eps; const float* ssq; int ssq_tiles; };
-struct StreamRope {
-    const int* positions; const int* tok_row; const int* table; int max_blocks;
-    bf16* kpool; bf16* vpool; const float* freqs;
-    int H, KV, HD, RD, pairing, page, num_pages;
-};
-
+// the input of a SCALED product: sums of squares of the rows of x by 32 columns ([ssq_tiles][16]) and eps
+struct StreamNorm { const float* ssq; int ssq_tiles; float eps; };
+// what form 3 leaves for the norm after it (all null: nothing): sums of squares, the norm's weight, rows times weight
+struct StreamAfter { float* ssq; const float* w; bf16* scaled; };
 #ifdef S_TRACE
 __device__ unsigned long long* s_trace_buf;
 __device__ __forceinline__ void s_mark(int ev) {
@@ -99,16 +97,32 @@ __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], 
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-template <int EPI, bool NORM>
+// compile-time shape of a kernel: TH rows of W per tile (128, 64 or 32)
+template <int EPI, int TH> struct StreamShape {
+    static constexpr int SETS = EPI == 1 ? 2 : 1;
+    static constexpr int MG = TH / 32;                  // consumer warps side by side along the rows of a tile
+    static constexpr int KG = 4 / MG;                   // ... and along k: warp w takes the boxes b with b % KG == w / MG
+    static constexpr int NB = 2 * KG;                   // boxes of 64 k per set and stage
+    static constexpr int KS = 64 * NB;                  // k per item
+    static constexpr int BOX = TH * 128;                // bytes of a box of W
+    static constexpr int STAGE = SETS * S_W_BYTES + NB * S_XBOX;
+    static constexpr int RED = KG > 1 ? 4 * 32 * SETS * 16 * 4 : 0;        // the warps' sums meet here
+    static constexpr int SMALL = 1024;                  // barriers, flags, 1 / rms, warp sums
+    static constexpr int FIT = (S_SMEM - 1024 - SMALL - RED) / STAGE;
+    static constexpr int STAGES = FIT > 6 ? 6 : FIT;
+    static constexpr size_t BYTES = 1024 + (size_t)STAGES * STAGE + SMALL + RED;
+};
+
+template <int EPI, bool SCALED, int TH>
 __global__ void __launch_bounds__(S_THREADS, 1) gemm_stream_kernel(const __grid_constant__ CUtensorMap wmap,
                                                                     const __grid_constant__ CUtensorMap xmap,
-                                                                    void* __restrict__ out, int N, int M, int K,
+                                                                    void* __restrict__ out, int N, int M, int K, int tiles,
                                                                     float* __restrict__ partial, int* __restrict__ tile_done,
                                                                     StreamNorm nrm, const float* __restrict__ bias,
-                                                                    StreamRope rope, float* __restrict__ ssq_out, int* err) {
-    constexpr int SETS = EPI == 1 ? 2 : 1;
-    constexpr int STAGE = SETS * S_W_BYTES + S_X_BYTES;
-    constexpr int STAGES = EPI == 1 ? 3 : 6;
+                                                                    StreamAfter after, int* err) {
+    using SH = StreamShape<EPI, TH>;
+    constexpr int SETS = SH::SETS, MG = SH::MG, KG = SH::KG, NB = SH::NB, KS = SH::KS, BOX = SH::BOX;
+    constexpr int STAGE = SH::STAGE, STAGES = SH::STAGES;
     extern __shared__ unsigned char smem_unaligned[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(
         (reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -116,25 +130,25 @@ __global__ void __launch_bounds__(S_THREADS, 1) gemm_stream_kernel(const __grid_
     int* last_flag = reinterpret_cast<int*>(bars + 2 * STAGES);
     float* inv_rms = reinterpret_cast<float*>(last_flag + 4);                    // [S_NT]
     float* red = inv_rms + S_NT;                                                   // [4][S_NT] warp sums
-    float* xch = red + 4 * S_NT;                                                   // [S_NT][128], form 4 only
+    float* meet = reinterpret_cast<float*>(smem + (size_t)STAGES * STAGE + SH::SMALL);   // [4 warps][SETS * 16][32 lanes]
     const uint32_t stage0 = smem_u32(smem);
     const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int row_tiles = (M + 127) / 128, kblocks = (K + S_BK - 1) / S_BK;
-    const long long T = (long long)row_tiles * kblocks;
+    const int kblocks = (K + KS - 1) / KS;
+    const long long T = (long long)tiles * kblocks;
     const long long lo = T * blockIdx.x / gridDim.x, hi = T * (blockIdx.x + 1) / gridDim.x;
     const StreamRange range(lo, hi, kblocks);
     const long long items = hi - lo;
-
     auto produce = [&](long long it, int tile, int kb) {              // the TMA copies of an item of this block
-        const int s = (int)(it % STAGES);
+        const int s = (int)(it % STAGES), row = tile * TH;
         const uint32_t fb = full0 + 8 * s, dst = stage0 + s * STAGE;
-        mbar_expect_tx(fb, NORM ? SETS * S_W_BYTES : STAGE);
+        mbar_expect_tx(fb, STAGE);
 #pragma unroll
-        for (int h = 0; h < 2; h++) {
-            tma_load_2d(dst + h * (S_W_BYTES / 2), &wmap, kb * S_BK + h * 64, tile * 128, fb);
-            if (EPI == 1) tma_load_2d(dst + S_W_BYTES + h * (S_W_BYTES / 2), &wmap, kb * S_BK + h * 64, M + tile * 128, fb);
-            if (!NORM) tma_load_2d(dst + SETS * S_W_BYTES + h * (S_X_BYTES / 2), &xmap, kb * S_BK + h * 64, 0, fb);
+        for (int b = 0; b < NB; b++) {
+            const int k = kb * KS + b * 64;
+            tma_load_2d(dst + b * BOX, &wmap, k, row, fb);
+            if (EPI == 1) tma_load_2d(dst + S_W_BYTES + b * BOX, &wmap, k, M + row, fb);
+            tma_load_2d(dst + SETS * S_W_BYTES + b * S_XBOX, &xmap, k, 0, fb);
         }
     };
     StreamWalk pw(range);                                             // the producer's place (thread 0 only)
@@ -142,19 +156,12 @@ __global__ void __launch_bounds__(S_THREADS, 1) gemm_stream_kernel(const __grid_
     if (tid == 0) {
         s_mark(0);
         asm volatile("prefetch.tensormap [%0];\n" ::"l"(&wmap) : "memory");
-        for (int s = 0; s < STAGES; s++) { mbar_init(full0 + 8 * s, NORM ? 3 : 1); mbar_init(empty0 + 8 * s, 4); }
+        for (int s = 0; s < STAGES; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 4); }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
         // the first ring of copies is on its way before the block has set itself up
         for (; p_it < items && p_it < STAGES; p_it++, pw.next()) produce(p_it, pw.tile, pw.kb);
         s_mark(1);
-    }
-    if (NORM && warp >= 5) {
-        // the token rows that no token fills stay zero in every stage
-        for (int s = 0; s < STAGES; s++) {
-            uint32_t* xs = reinterpret_cast<uint32_t*>(smem + (size_t)s * STAGE + SETS * S_W_BYTES);
-            for (int i = tid - 160; i < S_X_BYTES / 4; i += 32 * S_CONV_WARPS) xs[i] = 0u;
-        }
     }
     __syncthreads();
 
@@ -166,39 +173,13 @@ __global__ void __launch_bounds__(S_THREADS, 1) gemm_stream_kernel(const __grid_
             }
         }
     } else if (warp < 5) {
-        // consumers: warp cw owns rows 32 cw .. 32 cw + 31 of every row tile, the sums stay in its registers:
-        // acc[set][mt][nt][i] is row 32 cw + 16 mt + g + 8 (i >> 1), token 8 nt + 2 t + (i & 1)  (g = lane / 4, t = lane % 4)
+        // consumers: warp cw = (mg, kg) owns rows 32 mg .. 32 mg + 31 of a tile and the boxes b with b % KG == kg; sums in
+        // registers: acc[set][mt][nt][i] is row 32 mg + 16 mt + g + 8 (i >> 1), token 8 nt + 2 t + (i & 1)
+        // (g = lane / 4, t = lane % 4).  The warps with kg == 0 finish a tile ("active"); all take part in the barriers.
         const int cw = warp - 1, t128 = cw * 32 + lane, g = lane >> 2, t = lane & 3;
-        const int mi = lane >> 3, l7 = lane & 7;
-        if (NORM) {
-            // 1 / rms of every token's row of the residual stream, in float, summed in a fixed order: from the sums by
-            // row tile that the product before left, or over the rows themselves
-            if (nrm.ssq) {
-                if (t128 < N) {
-                    float ss = 0.0f;
-                    for (int tl = 0; tl < nrm.ssq_tiles; tl++) ss += __ldcg(nrm.ssq + tl * S_NT + t128);
-                    inv_rms[t128] = rsqrtf(ss / (float)K + nrm.eps);
-                }
-            } else {
-                for (int n = 0; n < N; n++) {
-                    float ss = 0.0f;
-                    const float4* row = reinterpret_cast<const float4*>(nrm.x + (size_t)n * K);
-#pragma unroll 8
-                    for (int c = t128; c < K / 4; c += 128) {
-                        const float4 v = __ldg(row + c);
-                        ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
-                    }
-                    ss = mb_warp_sum(ss);
-                    if (lane == 0) red[cw * S_NT + n] = ss;
-                }
-                asm volatile("bar.sync 1, 128;\n" ::: "memory");
-                if (t128 < N) {
-                    const float ss = (red[t128] + red[S_NT + t128]) + (red[2 * S_NT + t128] + red[3 * S_NT + t128]);
-                    inv_rms[t128] = rsqrtf(ss / (float)K + nrm.eps);
-                }
-            }
-            asm volatile("bar.sync 1, 128;\n" ::: "memory");
-        }
+        const int mg = cw % MG, kg = cw / MG, mi = lane >> 3, l7 = lane & 7;
+        const bool active = kg == 0;
+        const int tact = mg * 32 + lane;                              // this thread's column of the slots and of meet
         int it = 0;
         bool ok = true;
         if (t128 == 0) s_mark(2);
@@ -206,8 +187,18 @@ __global__ void __launch_bounds__(S_THREADS, 1) gemm_stream_kernel(const __grid_
             const StreamSeg sg = range.seg(j);
             const int tile = sg.tile, k_lo = sg.k_lo, k_hi = sg.k_hi;
             float acc[SETS][2][2][4];
+            float* accf = &acc[0][0][0][0];
 #pragma unroll
-            for (int a = 0; a < SETS * 16; a++) (&acc[0][0][0][0])[a] = 0.0f;
+            for (int a = 0; a < SETS * 16; a++) accf[a] = 0.0f;
+            float old[16];
+            if (EPI == 3 && active) {
+                // the stream's old values are on their way while the tile's weights arrive
+#pragma unroll
+                for (int a = 0; a < 16; a++) {
+                    const int n = 8 * ((a >> 2) & 1) + 2 * t + (a & 1), m = tile * TH + mg * 32 + ((a >> 3) & 1) * 16 + g + ((a >> 1) & 1) * 8;
+                    old[a] = (m < M && n < N) ? __ldcg(reinterpret_cast<const float*>(out) + (size_t)n * M + m) : 0.0f;
+                }
+            }
             for (int kb = k_lo; kb < k_hi; kb++, it++) {
                 const int s = it % STAGES, round = it / STAGES;
                 if (!mbar_wait(full0 + 8 * s, round & 1, err)) { ok = false; break; }
@@ -215,34 +206,52 @@ __global__ void __launch_bounds__(S_THREADS, 1) gemm_stream_kernel(const __grid_
                 if (t128 == 0 && it == items - 1) s_mark(4);
                 const uint32_t w_addr = stage0 + s * STAGE, x_addr = w_addr + SETS * S_W_BYTES;
 #pragma unroll
-                for (int hk = 0; hk < S_BK / 16; hk++) {
-                    const int h = hk >> 2, ks = hk & 3;               // half of the stage, k step of 16 inside it
-                    uint32_t b[4];
-                    ldsm4(x_addr + h * (S_X_BYTES / 2) + ((mi >> 1) * 8 + l7) * 128 + (((ks * 2 + (mi & 1)) ^ l7) << 4), b);
+                for (int bk = 0; bk < 8; bk++) {                      // this warp's two boxes, four k steps of 16 in each
+                    const int b = (bk >> 2) * KG + kg, ks = bk & 3;
+                    uint32_t xb[4];
+                    ldsm4(x_addr + b * S_XBOX + ((mi >> 1) * 8 + l7) * 128 + (((ks * 2 + (mi & 1)) ^ l7) << 4), xb);
 #pragma unroll
                     for (int set = 0; set < SETS; set++)
 #pragma unroll
                         for (int mt = 0; mt < 2; mt++) {
-                            uint32_t a[4];
-                            ldsm4(w_addr + set * S_W_BYTES + h * (S_W_BYTES / 2) + (cw * 32 + mt * 16 + (mi & 1) * 8 + l7) * 128 +
-                                      (((ks * 2 + (mi >> 1)) ^ l7) << 4), a);
-                            mma16816(acc[set][mt][0], a, b[0], b[1]);
-                            mma16816(acc[set][mt][1], a, b[2], b[3]);
+                            uint32_t wa[4];
+                            ldsm4(w_addr + set * S_W_BYTES + b * BOX + (mg * 32 + mt * 16 + (mi & 1) * 8 + l7) * 128 +
+                                      (((ks * 2 + (mi >> 1)) ^ l7) << 4), wa);
+                            mma16816(acc[set][mt][0], wa, xb[0], xb[1]);
+                            mma16816(acc[set][mt][1], wa, xb[2], xb[3]);
                         }
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(empty0 + 8 * s);           // this warp has read the stage
             }
             if (!ok) break;
-            bool finish = true;
+            if (SCALED && j == 0) asm volatile("bar.sync 2, 160;\n" ::: "memory");      // warp 5 has left 1 / rms
             if (t128 == 0 && j == range.n_seg - 1) s_mark(5);
+            if (KG > 1) {
+                // the warps that shared the k of these rows add their sums, in the order of the warps
+                if (!active) {
+#pragma unroll
+                    for (int a = 0; a < SETS * 16; a++) meet[(cw * SETS * 16 + a) * 32 + lane] = accf[a];
+                }
+                asm volatile("bar.sync 1, 128;\n" ::: "memory");
+                if (active) {
+#pragma unroll
+                    for (int q = 1; q < KG; q++)
+#pragma unroll
+                        for (int a = 0; a < SETS * 16; a++) accf[a] += meet[((q * MG + mg) * SETS * 16 + a) * 32 + lane];
+                }
+                asm volatile("bar.sync 1, 128;\n" ::: "memory");      // meet may be written again
+            }
+            bool finish = true;
             if (k_lo > 0 || k_hi < kblocks) {
                 // this block holds a part of the row tile's sum: slot 0 when the tile is the one its range starts in
                 const int slot = tile == range.t_first ? 0 : 1;
                 float* mine = partial + ((size_t)blockIdx.x * 2 + slot) * (SETS * S_NT * 128);
+                if (active) {
 #pragma unroll
-                for (int a = 0; a < SETS * 16; a++)
-                    if (8 * ((a >> 2) & 1) + 2 * t + (a & 1) < N) mine[a * 128 + t128] = (&acc[0][0][0][0])[a];
+                    for (int a = 0; a < SETS * 16; a++)
+                        if (8 * ((a >> 2) & 1) + 2 * t + (a & 1) < N) mine[a * 128 + tact] = accf[a];
+                }
                 // the warps' stores, then one thread's release: who brings the count to the tile's k blocks acquires
                 // what the others released
                 asm volatile("bar.sync 1, 128;\n" ::: "memory");
@@ -258,14 +267,16 @@ __global__ void __launch_bounds__(S_THREADS, 1) gemm_stream_kernel(const __grid_
                     const int c_first = (int)(((first_item + 1) * gridDim.x + T - 1) / T) - 1;
                     const int c_last = (int)(((last_item + 1) * gridDim.x + T - 1) / T) - 1;
 #pragma unroll
-                    for (int a = 0; a < SETS * 16; a++) (&acc[0][0][0][0])[a] = 0.0f;
+                    for (int a = 0; a < SETS * 16; a++) accf[a] = 0.0f;
+                    if (active) {
 #pragma unroll 4
-                    for (int c = c_first; c <= c_last; c++) {
-                        const int c_slot = (int)((T * c / gridDim.x) / kblocks) == tile ? 0 : 1;
-                        const float* theirs = partial + ((size_t)c * 2 + c_slot) * (SETS * S_NT * 128);
+                        for (int c = c_first; c <= c_last; c++) {
+                            const int c_slot = (int)((T * c / gridDim.x) / kblocks) == tile ? 0 : 1;
+                            const float* theirs = partial + ((size_t)c * 2 + c_slot) * (SETS * S_NT * 128);
 #pragma unroll
-                        for (int a = 0; a < SETS * 16; a++)
-                            if (8 * ((a >> 2) & 1) + 2 * t + (a & 1) < N) (&acc[0][0][0][0])[a] += __ldcg(theirs + a * 128 + t128);
+                            for (int a = 0; a < SETS * 16; a++)
+                                if (8 * ((a >> 2) & 1) + 2 * t + (a & 1) < N) accf[a] += __ldcg(theirs + a * 128 + tact);
+                        }
                     }
                     if (t128 == 0) tile_done[tile] = 0;                // ready for the next launch
                 }
@@ -273,146 +284,92 @@ __global__ void __launch_bounds__(S_THREADS, 1) gemm_stream_kernel(const __grid_
             }
             if (t128 == 0 && j == range.n_seg - 1) s_mark(6);
             if (!finish) continue;
-            if (EPI == 4) {
-                // rotation pairs two rows of a head: the rows of the tile meet in shared memory
+            // row r of the tile and token n of sum a of this thread
+#define S_ROW(a) (mg * 32 + (((a) >> 3) & 1) * 16 + g + (((a) >> 1) & 1) * 8)
+#define S_TOK(a) (8 * (((a) >> 2) & 1) + 2 * t + ((a) & 1))
+            {
+                if (active) {
 #pragma unroll
-                for (int a = 0; a < 16; a++) {
-                    const int r = cw * 32 + ((a >> 3) & 1) * 16 + g + ((a >> 1) & 1) * 8, n = 8 * ((a >> 2) & 1) + 2 * t + (a & 1);
-                    const int m = tile * 128 + r;
-                    // as the separate kernels do it: the product rounded to bf16, then bias and rotation in float
-                    float v = (&acc[0][0][0][0])[a];
-                    if (NORM && n < N) v *= inv_rms[n];
-                    v = bf16_round(v) + ((bias && m < M) ? bias[m] : 0.0f);
-                    (&acc[0][0][0][0])[a] = v;
-                    xch[n * 128 + r] = v;
-                }
-                asm volatile("bar.sync 1, 128;\n" ::: "memory");
-#pragma unroll
-                for (int a = 0; a < 16; a++) {
-                    const int r = cw * 32 + ((a >> 3) & 1) * 16 + g + ((a >> 1) & 1) * 8, n = 8 * ((a >> 2) & 1) + 2 * t + (a & 1);
-                    const int m = tile * 128 + r;
-                    if (m >= M || n >= N) continue;
-                    const int head = m / rope.HD, e = m % rope.HD, rh = rope.RD / 2;
-                    int pe = e, pair = -1;
-                    bool first = true;
-                    if (rope.pairing == 0) { pe = e ^ 1; first = !(e & 1); pair = (e >> 1) < rh ? (e >> 1) : -1; }
-                    else if (e < rope.RD) { first = e < rh; pe = first ? e + rh : e - rh; pair = first ? e : e - rh; }
-                    float v = (&acc[0][0][0][0])[a];
-                    const int pos = rope.positions[n];
-                    if (pair >= 0 && rope.freqs && head < rope.H + rope.KV) {
-                        const float p = xch[n * 128 + r - e + pe];
-                        const float c0 = first ? v : p, c1 = first ? p : v;      // the pair in its order
-                        float sn, cs;
-                        sincosf((float)pos * rope.freqs[pair], &sn, &cs);
-                        const float r0 = c0 * cs - c1 * sn, r1 = c0 * sn + c1 * cs;
-                        v = first ? r0 : r1;
-                    }
-                    if (head < rope.H) {
-                        reinterpret_cast<bf16*>(out)[(size_t)n * M + m] = __float2bfloat16_rn(v);
-                    } else if (rope.kpool) {
-                        const int pg = rope.table[(size_t)rope.tok_row[n] * rope.max_blocks + pos / rope.page];
-                        if (pg < 0 || pg >= rope.num_pages) {
-                            mb_set_error(err, pg < 0 ? MB_ERR_PAGE_MISSING : MB_ERR_PAGE_RANGE);
+                    for (int a = 0; a < 16; a++) {
+                        const int n = S_TOK(a), m = tile * TH + S_ROW(a);
+                        if (m >= M || n >= N) continue;
+                        float v = accf[a];
+                        if (SCALED) v *= inv_rms[n];
+                        if (EPI == 2) {
+                            reinterpret_cast<float*>(out)[(size_t)n * M + m] = v;
+                        } else if (EPI == 3) {
+                            v += old[a] + (bias ? bias[m] : 0.0f);
+                            reinterpret_cast<float*>(out)[(size_t)n * M + m] = v;
+                            if (after.scaled) after.scaled[(size_t)n * M + m] = __float2bfloat16_rn(v * after.w[m]);
+                            accf[a] = v;
+                        } else if (EPI == 1) {
+                            // gate and up pass through bf16 as they do when the products are separate kernels
+                            float up = accf[(SETS - 1) * 16 + a];
+                            if (SCALED) up *= inv_rms[n];
+                            const float gt = bf16_round(v);
+                            reinterpret_cast<bf16*>(out)[(size_t)n * M + m] = __float2bfloat16_rn((gt / (1.0f + expf(-gt))) * bf16_round(up));
                         } else {
-                            const int kvh = (head - rope.H) % rope.KV;
-                            bf16* pool = head < rope.H + rope.KV ? rope.kpool : rope.vpool;
-                            pool[(((size_t)pg * rope.KV + kvh) * rope.page + pos % rope.page) * rope.HD + e] = __float2bfloat16_rn(v);
+                            reinterpret_cast<bf16*>(out)[(size_t)n * M + m] = __float2bfloat16_rn(v);
                         }
                     }
                 }
-                asm volatile("bar.sync 1, 128;\n" ::: "memory");      // xch may be written again
-            } else {
+                if (EPI == 3 && after.ssq) {
+                    // the sums of squares of the new rows over this tile's columns, for the norm that follows
+                    if (active) {
 #pragma unroll
-                for (int a = 0; a < 16; a++) {
-                    const int r = cw * 32 + ((a >> 3) & 1) * 16 + g + ((a >> 1) & 1) * 8, n = 8 * ((a >> 2) & 1) + 2 * t + (a & 1);
-                    const int m = tile * 128 + r;
-                    if (m >= M || n >= N) continue;
-                    float v = acc[0][(a >> 3) & 1][(a >> 2) & 1][a & 3];
-                    if (NORM) v *= inv_rms[n];
-                    if (EPI == 2) {
-                        reinterpret_cast<float*>(out)[(size_t)n * M + m] = v;
-                    } else if (EPI == 3) {
-                        float* dst = reinterpret_cast<float*>(out) + (size_t)n * M + m;
-                        v += *dst + (bias ? bias[m] : 0.0f);
-                        *dst = v;
-                        acc[0][(a >> 3) & 1][(a >> 2) & 1][a & 3] = v;
-                    } else if (EPI == 1) {
-                        // gate and up pass through bf16 as they do when the products are separate kernels
-                        float up = acc[SETS - 1][(a >> 3) & 1][(a >> 2) & 1][a & 3];
-                        if (NORM) up *= inv_rms[n];
-                        const float gt = bf16_round(v);
-                        reinterpret_cast<bf16*>(out)[(size_t)n * M + m] = __float2bfloat16_rn((gt / (1.0f + expf(-gt))) * bf16_round(up));
-                    } else {
-                        reinterpret_cast<bf16*>(out)[(size_t)n * M + m] = __float2bfloat16_rn(v);
-                    }
-                }
-                if (EPI == 3 && ssq_out) {
-                    // the sums of squares of the new rows over this tile's 128 columns, for the norm that follows
-                    float sq[2][2];                                   // [nt][token parity]
+                        for (int q = 0; q < 4; q++) {
+                            const int nt = q >> 1, par = q & 1, n = 8 * nt + 2 * t + par;
+                            float ss = 0.0f;
 #pragma unroll
-                    for (int q = 0; q < 4; q++) {
-                        const int nt = q >> 1, par = q & 1, n = 8 * nt + 2 * t + par;
-                        float ss = 0.0f;
+                            for (int mt = 0; mt < 2; mt++)
 #pragma unroll
-                        for (int mt = 0; mt < 2; mt++)
-#pragma unroll
-                            for (int hi8 = 0; hi8 < 2; hi8++) {
-                                const int m = tile * 128 + cw * 32 + mt * 16 + g + hi8 * 8;
-                                const float v = acc[0][mt][nt][hi8 * 2 + par];
-                                if (m < M && n < N) ss = fmaf(v, v, ss);
-                            }
-                        ss += __shfl_xor_sync(0xffffffffu, ss, 4);
-                        ss += __shfl_xor_sync(0xffffffffu, ss, 8);
-                        ss += __shfl_xor_sync(0xffffffffu, ss, 16);
-                        sq[nt][par] = ss;
-                    }
-                    if (g == 0) {
-#pragma unroll
-                        for (int q = 0; q < 4; q++) red[cw * S_NT + 8 * (q >> 1) + 2 * t + (q & 1)] = sq[q >> 1][q & 1];
+                                for (int hi8 = 0; hi8 < 2; hi8++) {
+                                    const int m = tile * TH + mg * 32 + mt * 16 + g + hi8 * 8;
+                                    const float v = acc[0][mt][nt][hi8 * 2 + par];
+                                    if (m < M && n < N) ss = fmaf(v, v, ss);
+                                }
+                            ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+                            ss += __shfl_xor_sync(0xffffffffu, ss, 8);
+                            ss += __shfl_xor_sync(0xffffffffu, ss, 16);
+                            if (g == 0) red[mg * S_NT + n] = ss;
+                        }
                     }
                     asm volatile("bar.sync 1, 128;\n" ::: "memory");
-                    if (t128 < S_NT)
-                        ssq_out[tile * S_NT + t128] = (red[t128] + red[S_NT + t128]) + (red[2 * S_NT + t128] + red[3 * S_NT + t128]);
+                    // one row of sums per 32 columns of x, whatever the tile's height
+                    if (t128 < MG * S_NT && (tile * MG + t128 / S_NT) * 32 < M)
+                        after.ssq[((size_t)tile * MG + t128 / S_NT) * S_NT + t128 % S_NT] = red[t128];
                     asm volatile("bar.sync 1, 128;\n" ::: "memory");  // red may be written again
                 }
             }
             if (t128 == 0 && j == range.n_seg - 1) s_mark(7);
         }
-    } else if (NORM) {
-        // converter w makes half h = w & 1 of the activations of the items w / 2, w / 2 + 2, ...; the values of its
-        // next item are on their way while it waits for the stage of this one
-        const int cw = warp - 5, h = cw & 1;
-        float2 cur[S_NT], nxt[S_NT];
-        StreamWalk cwalk(range);
-        auto fetch = [&](float2 (&dst)[S_NT]) {
-            const int k = cwalk.kb * S_BK + h * 64 + 2 * lane;
-            float2 gw = make_float2(0.0f, 0.0f);
-            if (k < K) gw = __ldg(reinterpret_cast<const float2*>(nrm.w + k));
-#pragma unroll
-            for (int n = 0; n < S_NT; n++) {
-                float2 x = make_float2(0.0f, 0.0f);
-                if (n < N && k < K) x = __ldg(reinterpret_cast<const float2*>(nrm.x + (size_t)n * K + k));
-                dst[n] = make_float2(x.x * gw.x, x.y * gw.y);
-            }
-        };
-        long long it = cw >> 1;
-        if (it < items) { cwalk.skip((int)it); fetch(cur); }
-        for (; it < items; it += S_CONV_WARPS / 2) {
-            if (it + S_CONV_WARPS / 2 < items) { cwalk.skip(S_CONV_WARPS / 2); fetch(nxt); }
-            const int s = (int)(it % STAGES), round = (int)(it / STAGES);
-            if (round > 0 && !mbar_wait(empty0 + 8 * s, (round - 1) & 1, err)) break;
-            unsigned char* xs = smem + (size_t)s * STAGE + SETS * S_W_BYTES + h * (S_X_BYTES / 2);
-#pragma unroll
-            for (int n = 0; n < S_NT; n++)
-                if (n < N)
-                    *reinterpret_cast<uint32_t*>(xs + n * 128 + (((lane >> 2) ^ (n & 7)) << 4) + ((lane & 3) << 2)) =
-                        pack2(cur[n].x, cur[n].y);
-            __syncwarp();
-            if (lane == 0) mbar_arrive(full0 + 8 * s);
-#pragma unroll
-            for (int n = 0; n < S_NT; n++) cur[n] = nxt[n];
+    } else if (SCALED && warp == 5) {
+        // 1 / rms of every token's row, in float, from the sums of squares by 32 columns in a fixed order, while the
+        // consumers are at work: lane (part, quad) adds the rows part, part + 8, ... of the sums for the tokens
+        // 4 quad .. 4 quad + 3, then the eight parts meet in a tree of shuffles
+        const int quad = lane & 3, part = lane >> 2;
+        float4 ss = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        const float4* rows = reinterpret_cast<const float4*>(nrm.ssq);
+#pragma unroll 8
+        for (int tl = part; tl < nrm.ssq_tiles; tl += 8) {
+            const float4 v = __ldcg(rows + tl * 4 + quad);
+            ss.x += v.x; ss.y += v.y; ss.z += v.z; ss.w += v.w;
         }
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) {
+            ss.x += __shfl_xor_sync(0xffffffffu, ss.x, o); ss.y += __shfl_xor_sync(0xffffffffu, ss.y, o);
+            ss.z += __shfl_xor_sync(0xffffffffu, ss.z, o); ss.w += __shfl_xor_sync(0xffffffffu, ss.w, o);
+        }
+        if (part == 0) {
+            const float k = (float)K;
+            inv_rms[4 * quad] = rsqrtf(ss.x / k + nrm.eps); inv_rms[4 * quad + 1] = rsqrtf(ss.y / k + nrm.eps);
+            inv_rms[4 * quad + 2] = rsqrtf(ss.z / k + nrm.eps); inv_rms[4 * quad + 3] = rsqrtf(ss.w / k + nrm.eps);
+        }
+        __syncwarp();
+        asm volatile("bar.arrive 2, 160;\n" ::: "memory");
     }
+#undef S_ROW
+#undef S_TOK
 }
 
 // ------------------------------------------------------------------------------------------------ host side
@@ -427,87 +384,87 @@ static int stream_sms() {
     return sms;
 }
 
-// floats of workspace (two slots of partial sums per block) and ints of counters (one per 128 rows of W, zero before
+// floats of workspace (two slots of partial sums per block) and ints of counters (one per 32 rows of W, zero before
 // the first call; the kernels leave them zero) that a product with M output features needs
 MB_API long long mb_gemm_stream_workspace() { return (long long)stream_sms() * 2 * 2 * S_NT * 128; }
-MB_API long long mb_gemm_stream_counters(int M) { return (M + 127) / 128; }
+MB_API long long mb_gemm_stream_counters(int M) { return (M + 31) / 32; }
 
-template <int EPI, bool NORM>
-static int stream_launch(const void* act, const void* W, void* out, int N, int M, int K, float* workspace, int* counters,
-                         StreamNorm nrm, const float* bias, StreamRope rope, float* ssq_out, int* err, cudaStream_t st) {
-    if (N == 0 || M == 0) return 0;
-    if (N > S_NT || K % 8 || K < 8 || !workspace || !counters || (reinterpret_cast<uintptr_t>(W) & 15)) return -2;
-    if (NORM ? ((reinterpret_cast<uintptr_t>(nrm.x) & 15) || (reinterpret_cast<uintptr_t>(nrm.w) & 7))
-             : (reinterpret_cast<uintptr_t>(act) & 15) != 0)
-        return -2;
-    if (EPI == 4 && (rope.HD <= 0 || 128 % rope.HD || rope.RD % 2 || rope.RD > rope.HD || M != (rope.H + 2 * rope.KV) * rope.HD))
-        return -2;
-    constexpr int SETS = EPI == 1 ? 2 : 1;
-    constexpr int STAGES = EPI == 1 ? 3 : 6;
+// The height of a row tile: the largest of 128, 64, 32 that gives at least 0.6 tiles per SM, so that a matrix of few
+// rows still has a tile for most SMs and no tile is shared (then the grid is one block per tile); matrices with more
+// tiles than SMs, or too few even at 32 rows, are cut into equal shares of items.  least: the smallest height allowed.
+static int stream_tile_height(int M, int sms, int least) {
+    for (int th = 128; th > least; th /= 2)
+        if ((M + th - 1) / th >= (sms * 3 + 4) / 5) return th;
+    return least;
+}
+
+template <int EPI, bool SCALED, int TH>
+static int stream_launch_th(const void* act, const void* W, void* out, int N, int M, int K, float* workspace, int* counters,
+                            StreamNorm nrm, const float* bias, StreamAfter after, int* err, cudaStream_t st) {
+    using SH = StreamShape<EPI, TH>;
+    static_assert(SH::STAGES >= 2, "a ring of at least two stages");
     CUtensorMap wmap, xmap;
-    int rc = matrix_map(W, (long long)SETS * M, K, 128, &wmap);
+    int rc = matrix_map(W, (long long)SH::SETS * M, K, TH, &wmap);
     if (rc) return rc;
-    if (NORM) xmap = wmap;                                                        // not used
-    else if ((rc = matrix_map(act, N, K, S_NT, &xmap))) return rc;
-    const size_t smem = 1024 + (size_t)STAGES * (SETS * S_W_BYTES + S_X_BYTES) + 2 * STAGES * 8 + 16 +
-                        (S_NT + 4 * S_NT) * 4 + (EPI == 4 ? S_NT * 128 * 4 : 0);
+    if ((rc = matrix_map(act, N, K, S_NT, &xmap))) return rc;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_stream_kernel<EPI, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t e = cudaFuncSetAttribute(gemm_stream_kernel<EPI, SCALED, TH>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SH::BYTES);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    const long long T = (long long)((M + 127) / 128) * ((K + S_BK - 1) / S_BK);
-    const int sms = stream_sms();
-    gemm_stream_kernel<EPI, NORM><<<(unsigned)(T < sms ? T : sms), S_THREADS, smem, st>>>(
-        wmap, xmap, out, N, M, K, workspace, counters, nrm, bias, rope, ssq_out, err);
+    const int tiles = (M + TH - 1) / TH, sms = stream_sms();
+    const long long T = (long long)tiles * ((K + SH::KS - 1) / SH::KS);
+    long long grid = tiles <= sms && tiles >= (sms * 3 + 4) / 5 ? tiles : sms;    // a block per tile, or equal shares
+    if (grid > T) grid = T;
+    gemm_stream_kernel<EPI, SCALED, TH><<<(unsigned)grid, S_THREADS, SH::BYTES, st>>>(
+        wmap, xmap, out, N, M, K, tiles, workspace, counters, nrm, bias, after, err);
     MB_LAUNCH_CHECK();
     return 0;
 }
 
-// mode 0: bf16 out (N, M); 1: SwiGLU, W has 2 * M rows, bf16 out (N, M); 2: float out (N, M)
-MB_API int mb_gemm_stream(const void* act, const void* W, void* out, int N, int M, int K, int mode, float* workspace,
-                          int* counters, int* err, cudaStream_t st) {
-    const StreamNorm nn{};
-    const StreamRope nr{};
+template <int EPI, bool SCALED>
+static int stream_launch(const void* act, const void* W, void* out, int N, int M, int K, float* workspace, int* counters,
+                         StreamNorm nrm, const float* bias, StreamAfter after, int* err, cudaStream_t st) {
+    if (N == 0 || M == 0) return 0;
+    if (N > S_NT || K % 8 || K < 8 || !workspace || !counters || (reinterpret_cast<uintptr_t>(W) & 15) ||
+        (reinterpret_cast<uintptr_t>(act) & 15) || (SCALED && (!nrm.ssq || (reinterpret_cast<uintptr_t>(nrm.ssq) & 15))))
+        return -2;
+    switch (stream_tile_height(M, stream_sms(), 32)) {
+        case 128: return stream_launch_th<EPI, SCALED, 128>(act, W, out, N, M, K, workspace, counters, nrm, bias, after, err, st);
+        case 64: return stream_launch_th<EPI, SCALED, 64>(act, W, out, N, M, K, workspace, counters, nrm, bias, after, err, st);
+        default: return stream_launch_th<EPI, SCALED, 32>(act, W, out, N, M, K, workspace, counters, nrm, bias, after, err, st);
+    }
+}
+
+// mode 0: bf16 out (N, M); 1: SwiGLU, W has 2 * M rows, bf16 out (N, M); 2: float out (N, M).
+// ssq (or null): act holds rows of a residual stream times a norm's weight and ssq ([ceil(K / 32)][16]) the sums of
+// squares of those rows by 32 columns, as mb_gemm_stream_residual leaves them: out is then the product of
+// rmsnorm(x; weight, eps).
+MB_API int mb_gemm_stream(const void* act, const float* ssq, float eps, const void* W, void* out, int N, int M, int K,
+                          int mode, float* workspace, int* counters, int* err, cudaStream_t st) {
+    const StreamNorm nn{ssq, (K + 31) / 32, eps};
+    const StreamAfter na{};
+    if (ssq) {
+        if (mode == 0) return stream_launch<0, true>(act, W, out, N, M, K, workspace, counters, nn, nullptr, na, err, st);
+        if (mode == 1) return stream_launch<1, true>(act, W, out, N, M, K, workspace, counters, nn, nullptr, na, err, st);
+        return -2;
+    }
     switch (mode) {
-        case 0: return stream_launch<0, false>(act, W, out, N, M, K, workspace, counters, nn, nullptr, nr, nullptr, err, st);
-        case 1: return stream_launch<1, false>(act, W, out, N, M, K, workspace, counters, nn, nullptr, nr, nullptr, err, st);
-        case 2: return stream_launch<2, false>(act, W, out, N, M, K, workspace, counters, nn, nullptr, nr, nullptr, err, st);
+        case 0: return stream_launch<0, false>(act, W, out, N, M, K, workspace, counters, nn, nullptr, na, err, st);
+        case 1: return stream_launch<1, false>(act, W, out, N, M, K, workspace, counters, nn, nullptr, na, err, st);
+        case 2: return stream_launch<2, false>(act, W, out, N, M, K, workspace, counters, nn, nullptr, na, err, st);
     }
     return -2;
 }
 
 // x (N, M) float32 += act (N, K) bf16 @ W (M, K)^T (+ bias (M) float32 or null), in place.  ssq_out (or null):
-// [ceil(M / 128)][16] floats that receive, by row tile, the sums of squares of the new rows of x
+// [ceil(M / 32)][16] floats that receive the sums of squares of the new rows of x by 32 columns; next_w and scaled_out
+// (or null): the weight (M) of the norm that reads x next, and (N, M) bf16 that receives the new rows times it
 MB_API int mb_gemm_stream_residual(const void* act, const void* W, float* x, const float* bias, int N, int M, int K,
-                                   float* ssq_out, float* workspace, int* counters, int* err, cudaStream_t st) {
-    return stream_launch<3, false>(act, W, x, N, M, K, workspace, counters, StreamNorm{}, bias, StreamRope{}, ssq_out, err, st);
-}
-
-// out (N, M) bf16 = rmsnorm(x; norm_w, eps) @ W^T for the float32 residual stream x (N, K); mode 1: SwiGLU.
-// ssq (or null): what mb_gemm_stream_residual left for this x, ceil(K / 128) row tiles
-MB_API int mb_gemm_stream_normed(const float* x, const float* norm_w, float eps, const float* ssq, const void* W, void* out,
-                                 int N, int M, int K, int mode, float* workspace, int* counters, int* err, cudaStream_t st) {
-    const StreamNorm nn{x, norm_w, eps, ssq, (K + 127) / 128};
-    const StreamRope nr{};
-    if (mode == 0) return stream_launch<0, true>(nullptr, W, out, N, M, K, workspace, counters, nn, nullptr, nr, nullptr, err, st);
-    if (mode == 1) return stream_launch<1, true>(nullptr, W, out, N, M, K, workspace, counters, nn, nullptr, nr, nullptr, err, st);
-    return -2;
-}
-
-// the fused q/k/v product of rmsnorm(x) with bias, rotation and the cache write in its epilogue: out (N, M) bf16
-// receives the rotated q heads (M = (H + 2 KV) HD), k and v go into the pages of the tokens' positions (kpool null:
-// they are dropped)
-MB_API int mb_gemm_stream_normed_qkv(const float* x, const float* norm_w, float eps, const float* ssq, const void* W,
-                                     void* out, int N, int M, int K, const float* bias, const int* positions,
-                                     const int* tok_row, const int* table, int max_blocks, void* kpool, void* vpool,
-                                     const float* freqs, int H, int KV, int HD, int RD, int pairing, int page,
-                                     int num_pages, float* workspace, int* counters, int* err, cudaStream_t st) {
-    StreamRope r;
-    r.positions = positions; r.tok_row = tok_row; r.table = table; r.max_blocks = max_blocks;
-    r.kpool = (bf16*)kpool; r.vpool = (bf16*)vpool; r.freqs = freqs;
-    r.H = H; r.KV = KV; r.HD = HD; r.RD = RD; r.pairing = pairing; r.page = page; r.num_pages = num_pages;
-    return stream_launch<4, true>(nullptr, W, out, N, M, K, workspace, counters, StreamNorm{x, norm_w, eps, ssq, (K + 127) / 128},
-                                  bias, r, nullptr, err, st);
+                                   float* ssq_out, const float* next_w, void* scaled_out, float* workspace, int* counters,
+                                   int* err, cudaStream_t st) {
+    if ((next_w == nullptr) != (scaled_out == nullptr)) return -2;
+    return stream_launch<3, false>(act, W, x, N, M, K, workspace, counters, StreamNorm{}, bias,
+                                   StreamAfter{ssq_out, next_w, (bf16*)scaled_out}, err, st);
 }

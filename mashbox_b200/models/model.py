@@ -80,7 +80,10 @@ class Model:
         x = ctx.ws.get("residual", ctx.N, (self.hidden,), torch.float32)
         self.embedding.forward(ctx, x)
         pending = None
-        for run in self.schedule:
+        for i, run in enumerate(self.schedule):
+            # the norm that reads the stream after this block, for a block whose last product can prepare its input
+            after = self.layers[self.schedule[i + 1].layer] if i + 1 < len(self.schedule) else None
+            ctx.next_first_norm = after.first_norm() if hasattr(after, "first_norm") else None
             pending = self.layers[run.layer].forward(ctx, x, pending, run)
         if ctx.n_out == 0:
             if pending is not None:         # keep the stream whole even when nobody asks for logits

@@ -271,16 +271,16 @@ def linear_gemv(a, w, out, mode="plain"):
     return out
 
 
-# The weight-streaming products for decode batches (at most 16 tokens; gemm_stream.cu): every SM streams the same share
-# of W by TMA whatever the matrix's shape, mma.sync on the tiles, and the forms of the matrix-vector kernels exist here
-# too (normalising, SwiGLU, adding into the residual stream, q/k/v with rotation and cache write), so a layer is five
-# kernels.  Off by default: measured inside captured graphs on the Llama-3.1-8B shapes at 8 tokens, own / library, us:
-# output product 13.0 / 12.0, q/k/v 15.9 / 11.9, down 27.0 / 23.3, gate/up 42.3 / 40.3 -- the library's kernels run at
-# the rate at which TMA copies alone stream these matrices (8.6, 11.2, 21.3, 38.9 us), this kernel 3 to 5 us above it
-# (1.5 us until its first copy is issued, the meeting of the blocks that share a row tile, uneven finishing times of
-# the SMs), which is more than the folded kernels save: the whole decode step at batch 8 runs at 1,432 tokens/s with
-# these products against 1,616 with the library's.  STREAM["tokens"]: the most tokens the engine gives them (0: never).
-STREAM = {"tokens": 0}
+# The weight-streaming products for steps of 2 to 16 tokens (gemm_stream.cu): W is cut into row tiles low enough that
+# most SMs get one (no tile shared for the layer's own matrices), streamed by TMA, mma.sync on the tiles.  The product
+# that ends a sublayer adds into the residual stream and leaves what the norm after it needs (sums of squares, rows
+# times the norm's weight); the product after that norm runs on those rows and scales its sums by 1 / rms; gate/up has
+# SwiGLU in its epilogue.  A layer is then six kernels instead of ten.  Measured inside captured graphs on the
+# Llama-3.1-8B shapes at 8 tokens, own / library, us: output product with the residual add 11.4 / 12.0 (+ the add in the
+# norm kernel), q/k/v of the normalised stream 12.0 / 11.9 + norm 3.8, gate/up with SwiGLU 40.6 / 40.2 + norm 3.8 + gate
+# 2.3, down with the residual add 26.5 / 23.3; the whole decode step at batch 8 (the output head too): 1,720 tokens/s
+# against 1,608 with the library's products.  STREAM["tokens"]: the most tokens the engine gives them (0: never).
+STREAM = {"tokens": 16}
 if os.environ.get("MASHBOX_STREAM_TOKENS"):        # a tuning knob
     STREAM = {"tokens": int(os.environ["MASHBOX_STREAM_TOKENS"])}
 _stream_scratch = {}
@@ -297,7 +297,7 @@ def _stream_buffers(device, M):
     lib.mb_gemm_stream_workspace.restype = ctypes.c_longlong
     key = str(device)
     sc = _stream_scratch.get(key)
-    tiles = (M + 127) // 128
+    tiles = (M + 31) // 32
     if sc is None or sc[1].numel() < tiles:
         sc = (torch.empty(lib.mb_gemm_stream_workspace(), dtype=torch.float32, device=device),
               torch.zeros(max(tiles, 8192), dtype=torch.int32, device=device))
@@ -305,101 +305,78 @@ def _stream_buffers(device, M):
     return sc
 
 
-def linear_stream(a, w, out, mode="plain"):
-    """a (N <= 16, K) bf16, w (M, K) bf16 ("swiglu": (2M, K)) -> out (N, M): bf16, or float32 for mode "float"."""
-    _cuda(a, w, out)
+def linear_stream(a, w, out, mode="plain", sums=None, eps=0.0):
+    """a (N <= 16, K) bf16, w (M, K) bf16 ("swiglu": (2M, K)) -> out (N, M): bf16, or float32 for mode "float".
+    sums (ceil(K / 32), 16) float32, if given: a holds rows of a residual stream times a norm's weight and sums the sums
+    of squares of those rows by 32 columns, as linear_stream_residual leaves them; out is then the product of
+    rmsnorm(x; weight, eps): 1 / rms scales the float sums of the product."""
+    _cuda(a, w, out, sums)
     N, K = a.shape
     M = out.shape[1]
     ws, cnt = _stream_buffers(a.device, M)
-    f = _fn("gemm_stream", "mb_gemm_stream", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
-                                              c_void_p, c_void_p])
-    _check(f(_p(a), _p(w), _p(out), N, M, K, {"plain": 0, "swiglu": 1, "float": 2}[mode], _p(ws), _p(cnt),
-             _p(error_word(a.device)), _stream()), "gemm_stream")
+    f = _fn("gemm_stream", "mb_gemm_stream", [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                              c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(f(_p(a), _p(sums), float(eps), _p(w), _p(out), N, M, K, {"plain": 0, "swiglu": 1, "float": 2}[mode], _p(ws),
+             _p(cnt), _p(error_word(a.device)), _stream()), "gemm_stream")
     return out
 
 
-def linear_stream_residual(a, w, x, bias=None, sums=None):
-    """x (N <= 16, M) float32 += a (N, K) bf16 @ w (M, K)^T (+ bias (M) float32), in place.  sums (ceil(M / 128), 16)
-    float32, if given, receives the sums of squares of the new rows of x by tile of 128 columns: the normalising product
-    that follows takes them instead of reading the rows again."""
-    _cuda(a, w, x, bias, sums)
+def linear_stream_residual(a, w, x, bias=None, sums=None, next_w=None, scaled=None):
+    """x (N <= 16, M) float32 += a (N, K) bf16 @ w (M, K)^T (+ bias (M) float32), in place.  What the norm that reads x
+    next needs, on request: sums (ceil(M / 32), 16) float32 receives the sums of squares of the new rows by 32 columns,
+    scaled (N, M) bf16 the new rows times that norm's weight next_w (M) float32."""
+    _cuda(a, w, x, bias, sums, next_w, scaled)
     N, K = a.shape
     M = x.shape[1]
     ws, cnt = _stream_buffers(a.device, M)
     f = _fn("gemm_stream", "mb_gemm_stream_residual", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
-                                                       c_void_p, c_void_p, c_void_p, c_void_p])
-    _check(f(_p(a), _p(w), _p(x), _p(bias), N, M, K, _p(sums), _p(ws), _p(cnt), _p(error_word(a.device)), _stream()),
-           "gemm_stream_residual")
+                                                       c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(f(_p(a), _p(w), _p(x), _p(bias), N, M, K, _p(sums), _p(next_w), _p(scaled), _p(ws), _p(cnt),
+             _p(error_word(a.device)), _stream()), "gemm_stream_residual")
     return x
 
 
-def linear_stream_normed(x, norm_w, eps, w, out, mode="plain", sums=None):
-    """x (N <= 16, K) float32 residual stream, norm_w (K) float32 -> out (N, M) bf16 = rmsnorm(x) W^T ("swiglu": W is
-    (2M, K) and out = silu(gate) * up).  The product runs on bf16(x * norm_w); 1 / rms scales the float sums.  sums:
-    what linear_stream_residual left for this x (else the kernel adds up the rows' squares itself)."""
-    _cuda(x, norm_w, w, out, sums)
-    N, K = x.shape
-    M = out.shape[1]
-    ws, cnt = _stream_buffers(x.device, M)
-    f = _fn("gemm_stream", "mb_gemm_stream_normed", [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                                                     c_int, c_void_p, c_void_p, c_void_p, c_void_p])
-    _check(f(_p(x), _p(norm_w), float(eps), _p(sums), _p(w), _p(out), N, M, K, {"plain": 0, "swiglu": 1}[mode], _p(ws), _p(cnt),
-             _p(error_word(x.device)), _stream()), "gemm_stream_normed")
-    return out
-
-
-def linear_stream_normed_qkv(x, norm_w, eps, w, out, bias, positions, tok_seq, table, kpool, vpool, freqs, H, KV, HD, RD,
-                             pairing, page, num_pages, err, sums=None):
-    """As linear_gemv_normed_qkv for up to 16 tokens; the head size must divide 128."""
-    _cuda(x, norm_w, w, out, bias, positions, tok_seq, table, kpool, vpool, freqs, sums)
-    N, K = x.shape
-    M = out.shape[1]
-    ws, cnt = _stream_buffers(x.device, M)
-    f = _fn("gemm_stream", "mb_gemm_stream_normed_qkv",
-            [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
-             c_void_p, c_int, c_void_p, c_void_p, c_void_p] + [c_int] * 7 + [c_void_p, c_void_p, c_void_p, c_void_p])
-    _check(f(_p(x), _p(norm_w), float(eps), _p(sums), _p(w), _p(out), N, M, K, _p(bias), _p(positions), _p(tok_seq),
-             _p(table), table.shape[1], _p(kpool), _p(vpool), _p(freqs), H, KV, HD, RD, pairing, page, num_pages, _p(ws),
-             _p(cnt), _p(err), _stream()), "gemm_stream_normed_qkv")
-    return out
-
-
-# ---- what the parts call at few tokens: the matrix-vector kernels where they are enabled, else the streaming products
+# ---- what the parts call at few tokens: the matrix-vector kernels where they are enabled, else the streaming products.
+# "held" is what the product that last added into the residual stream left for the norm after it (sums of squares by 32
+# columns, rows times the norm's weight in bf16): the streaming products need it, the matrix-vector kernels read x.
 def _use_gemv_fused(N, K):
     return 1 <= N <= min(4, GEMV["fused"]) and K % 8 == 0 and 8 <= K < 8192 and N * K * 2 <= 48 * 1024
 
 
 def small_fused_supports(N, K, dtype):
     """True when a step of N tokens of width K can run its layers on the folded kernels: the product that follows a
-    norm normalises the float32 residual stream itself (linear_small_normed), the product that ends a sublayer adds
-    into it (linear_small_residual)."""
+    norm is the product of the normalised stream without a norm kernel (linear_small_normed), the product that ends a
+    sublayer adds into the stream (linear_small_residual)."""
     return dtype == torch.bfloat16 and (_use_gemv_fused(N, K) or stream_supports(N, K))
 
 
-def small_qkv_supports(N, K, HD):
+def small_normed_needs_held(N, K):
+    return not _use_gemv_fused(N, K)
+
+
+def small_qkv_supports(N, K):
     """True when linear_small_normed_qkv takes this step (else: linear_small_normed, then rope_kv_write)"""
-    return _use_gemv_fused(N, K) or (stream_supports(N, K) and 128 % HD == 0)
+    return _use_gemv_fused(N, K)
 
 
-def linear_small_normed(x, norm_w, eps, w, out, mode="plain", sums=None):
+def linear_small_normed(x, norm_w, eps, w, out, mode="plain", held=None):
     if _use_gemv_fused(*x.shape):
         return linear_gemv_normed(x, norm_w, eps, w, out, mode)
-    return linear_stream_normed(x, norm_w, eps, w, out, mode, sums)
+    sums, scaled = held
+    return linear_stream(scaled, w, out, mode, sums, eps)
 
 
-def linear_small_normed_qkv(x, *args, sums=None):
-    if _use_gemv_fused(*x.shape):
-        return linear_gemv_normed_qkv(x, *args)
-    return linear_stream_normed_qkv(x, *args, sums=sums)
+def linear_small_normed_qkv(x, norm_w, eps, w, out, *args):
+    return linear_gemv_normed_qkv(x, norm_w, eps, w, out, *args)
 
 
-def linear_small_residual(a, w, x, bias=None, sums=None):
-    """-> True when `sums` was filled (see linear_stream_residual)"""
+def linear_small_residual(a, w, x, bias=None, sums=None, next_w=None, scaled=None):
+    """-> True when sums and scaled were filled (see linear_stream_residual)"""
     if _use_gemv_fused(a.shape[0], x.shape[1]) and a.shape[1] % 8 == 0:
         linear_gemv_residual(a, w, x, bias)
         return False
-    linear_stream_residual(a, w, x, bias, sums)
-    return sums is not None
+    linear_stream_residual(a, w, x, bias, sums, next_w, scaled)
+    return sums is not None and scaled is not None
 
 
 def fused_swiglu_supports(N, F, K):

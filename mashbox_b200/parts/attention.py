@@ -138,19 +138,19 @@ class Attention:
         table = group.device_table
         page, pages = ctx.cache.page_size, ctx.cache.num_pages
         rot = self.position.rotation() if self.position is not None else (None, HD, 0)
-        if normed is not None and rot is not None and ops.small_qkv_supports(N, self.D, HD):
+        if normed is not None and rot is not None and ops.small_qkv_supports(N, self.D):
             # a step of very few tokens: norm, product, rotation and the cache write in one kernel
             x, norm = normed
             w, eps = norm.fusable()
             freqs, rd, pairing = rot
             ops.linear_small_normed_qkv(x, w, eps, self.wqkv, qkv, self.bqkv, ctx.dev("positions"), ctx.dev("tok_row"),
                                         table, kpool if run.write else None, vpool if run.write else None, freqs, H, KV,
-                                        HD, rd, pairing, page, pages, ctx.err, sums=ctx.take_row_sums(x))
+                                        HD, rd, pairing, page, pages, ctx.err)
         else:
             if normed is not None:
                 x, norm = normed
                 w, eps = norm.fusable()
-                ops.linear_small_normed(x, w, eps, self.wqkv, qkv, sums=ctx.take_row_sums(x))
+                ops.linear_small_normed(x, w, eps, self.wqkv, qkv, held=ctx.take_held(x, norm))
             else:
                 ops.linear(h, self.wqkv, out=qkv)
             freqs, rd, pairing = (None, HD, 0)
@@ -195,9 +195,7 @@ class Attention:
             ops.attention_simple(qkv, width, out, ctx.dev("positions"), ctx.dev("tok_row"), table, kpool, vpool, H, KV,
                                  HD, page, pages, self.window, self.scale, ctx.err)
         if residual is not None:
-            sums = ctx.row_sums_buffer(residual)
-            if ops.linear_small_residual(out, self.wo, residual, self.bo, sums=sums):
-                ctx.hold_row_sums(residual, sums)
+            ctx.add_into_stream(out, self.wo, residual, self.bo)
             return None
         y = ctx.ws.get("delta", N, (self.D,), ctx.dtype)
         ops.linear(out, self.wo, out=y)

@@ -213,17 +213,33 @@ class StepContext:
     def dev(self, name):
         return self.inputs.get(name)
 
-    # A product that adds into the residual stream x can leave the sums of squares of the new rows (by tile of 128
-    # columns); the normalising product of the next sublayer takes them instead of reading every row again.
-    def row_sums_buffer(self, x):
+    # Steps of few tokens: the product that ends a sublayer adds into the residual stream itself and can leave what the
+    # norm after it needs (sums of squares of the new rows by 32 columns, the new rows times that norm's weight), so the
+    # next sublayer's first product needs no norm kernel.  A block names the norm that follows in `after_norm` before
+    # it runs a part; the model names the first norm of the block that runs next in `next_first_norm`.
+    after_norm = None
+    next_first_norm = None
+
+    def add_into_stream(self, a, w, x, bias=None):
+        """x (N, D) float32 += a W^T (+ bias), in place"""
         import torch
-        tiles = (x.shape[1] + 127) // 128
-        return self.ws.get("row_sums", tiles, (16,), torch.float32, reserve=tiles)
+        nxt = self.after_norm if hasattr(self.after_norm, "fusable") else None
+        sums = scaled = gw = None
+        if nxt is not None:
+            tiles = (x.shape[1] + 31) // 32
+            sums = self.ws.get("row_sums", tiles, (16,), torch.float32, reserve=tiles)
+            scaled = self.ws.get("row_scaled", x.shape[0], (x.shape[1],), torch.bfloat16)
+            gw = nxt.fusable()[0]
+        self.memo.pop("held", None)
+        if self.ops.linear_small_residual(a, w, x, bias, sums=sums, next_w=gw, scaled=scaled):
+            self.memo["held"] = (x.data_ptr(), nxt, sums, scaled)
 
-    def hold_row_sums(self, x, sums):
-        self.memo["row_sums"] = (x.data_ptr(), sums)
+    def held_for(self, x, norm):
+        """-> (sums, scaled) left for this norm by the product that last added into x, or None"""
+        h = self.memo.get("held")
+        return (h[2], h[3]) if h is not None and h[0] == x.data_ptr() and h[1] is norm else None
 
-    def take_row_sums(self, x):
-        """-> the sums held for x as it is now, or None; they are used up"""
-        held = self.memo.pop("row_sums", None)
-        return held[1] if held is not None and held[0] == x.data_ptr() else None
+    def take_held(self, x, norm):
+        h = self.held_for(x, norm)
+        self.memo.pop("held", None)
+        return h

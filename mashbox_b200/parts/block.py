@@ -21,17 +21,25 @@ class PreNormBlock:
 
     def forward(self, ctx, x, pending, run):
         # A step of very few tokens is a chain of short kernels.  Parts that say `fuses_small` take two of them in:
-        # with normed=(x, norm) their first product normalises the residual stream itself (x must be up to date:
-        # nothing pending), with residual=x their last product adds into the stream and nothing is left pending.
+        # with normed=(x, norm) their first product is the product of the normalised stream without a norm kernel (x
+        # must be up to date: nothing pending; the streaming products also need what the product before left for this
+        # norm, ctx.held_for), with residual=x their last product adds into the stream (ctx.add_into_stream) and
+        # nothing is left pending.
         small = ctx.ops.small_fused_supports(ctx.N, x.shape[1], ctx.dtype) and not ctx.options.get("no_small_fusion", False)
-        pending = self._sublayer(ctx, x, pending, self.norm1, self.mixer, small, run)
-        return self._sublayer(ctx, x, pending, self.norm2, self.ffn, small)
+        pending = self._sublayer(ctx, x, pending, self.norm1, self.mixer, small, self.norm2, run)
+        return self._sublayer(ctx, x, pending, self.norm2, self.ffn, small, ctx.next_first_norm)
+
+    def first_norm(self):
+        """the norm that reads the residual stream first when this block runs"""
+        return self.norm1
 
     @staticmethod
-    def _sublayer(ctx, x, pending, norm, part, small, *run):
+    def _sublayer(ctx, x, pending, norm, part, small, after, *run):
+        ctx.after_norm = after                  # the norm that reads x after this part (None: not known)
         if not (small and getattr(part, "fuses_small", False) and hasattr(norm, "fusable")):
             return part.forward(ctx, norm.forward(ctx, x, pending), *run)
-        if pending is not None:
+        ready = pending is None and (not ctx.ops.small_normed_needs_held(ctx.N, x.shape[1]) or ctx.held_for(x, norm) is not None)
+        if not ready:
             return part.forward(ctx, norm.forward(ctx, x, pending), *run, residual=x)
         return part.forward(ctx, None, *run, normed=(x, norm), residual=x)
 

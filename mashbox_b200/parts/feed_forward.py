@@ -31,7 +31,7 @@ class SwiGLU:
         if normed is not None:
             x, norm = normed
             w, eps = norm.fusable()
-            ctx.ops.linear_small_normed(x, w, eps, self.wgu, a, "swiglu", sums=ctx.take_row_sums(x))
+            ctx.ops.linear_small_normed(x, w, eps, self.wgu, a, "swiglu", held=ctx.take_held(x, norm))
         elif ctx.dtype == torch.bfloat16 and ctx.ops.fused_swiglu_supports(N, self.F, self.D):
             ctx.ops.linear_swiglu(h, self.wgu, a)           # both products and the gate in one kernel
         else:
@@ -39,9 +39,7 @@ class SwiGLU:
             ctx.ops.linear(h, self.wgu, out=gu)
             ctx.ops.swiglu(gu, a)
         if residual is not None:
-            sums = ctx.row_sums_buffer(residual)
-            if ctx.ops.linear_small_residual(a, self.wd, residual, sums=sums):
-                ctx.hold_row_sums(residual, sums)
+            ctx.add_into_stream(a, self.wd, residual)
             return None
         y = ctx.ws.get("delta", N, (self.D,), ctx.dtype)
         ctx.ops.linear(a, self.wd, out=y)

@@ -30,7 +30,7 @@ class RMSNorm:
                          reserve=None if rows is None else ctx.options.get("logit_rows", 8))
         delta, bias = pending if pending is not None else (None, None)
         if delta is not None:
-            ctx.take_row_sums(x)                # x changes here: sums held for it no longer describe it
+            ctx.memo.pop("held", None)         # x changes here: what is held for it no longer describes it
         ctx.ops.add_rmsnorm(x, delta, bias, self.weight, self.eps, out, rows)
         return out
 

@@ -566,108 +566,63 @@ def test_qkv_product_with_rotation_and_cache_write_in_its_epilogue(pairing, HD, 
     assert torch.equal(three[:, :H * HD], one[:, :H * HD])
 
 
-@pytest.mark.parametrize("N,M,K", [(8, 6144, 4096), (16, 57, 72), (3, 1000, 2504), (1, 4096, 4096), (5, 264, 14336)])
-def test_streaming_product_that_normalises_and_one_that_adds_to_the_stream(N, M, K):
-    """the folded forms of a step of at most 16 tokens on the streaming kernel: rmsnorm inside the product that
-    follows it (the product runs on bf16(x * g), 1 / rms scales the float accumulator), the residual add inside the
-    product that ends a sublayer; called twice, so the counters of shared row tiles have reset themselves"""
+@pytest.mark.parametrize("N,M,K", [(8, 6144, 4096), (16, 56, 72), (3, 1000, 2504), (1, 4096, 4096), (5, 264, 14336), (8, 4096, 4096)])
+def test_streaming_products_that_add_to_the_stream_and_take_the_norm_in(N, M, K):
+    """the folded forms of a step of at most 16 tokens: the product that ends a sublayer adds into the float32 stream and
+    leaves what the norm after it needs (sums of squares by 32 columns, rows times the norm's weight in bf16); the
+    product after that norm runs on those rows and scales its float sums by 1 / rms.  Tiles of 128, 64 and 32 rows,
+    matrices with one block per tile and with shared tiles; called twice, so the counters have reset themselves"""
     K_ = ops()
     g = torch.Generator().manual_seed(31)
-    x = (3.0 * torch.randn(N, K, generator=g)).to(G.DEV)
-    x[N - 1] *= 40.0                                       # rows of very different size: each has its own 1 / rms
-    nw = (1.0 + 0.2 * torch.randn(K, generator=g)).to(G.DEV)
-    w = (torch.randn(M, K, generator=g) / K ** 0.5).bfloat16().to(G.DEV)
     eps = 1e-5
-    inv = torch.rsqrt((x.double() ** 2).mean(-1, keepdim=True) + eps)
-    want = ((x.double() * nw.double()).float().bfloat16().double() @ w.double().T) * inv
-    for _ in range(2):
-        out = torch.full((N, M), float("nan"), device=G.DEV, dtype=torch.bfloat16)
-        K_.linear_stream_normed(x, nw, eps, w, out, "plain")
-        close(out, want, torch.bfloat16, "normalising streaming product")
-    # against the norm kernel followed by the library product: the same up to the rounding of the normalised row
-    hh = torch.empty(N, K, device=G.DEV, dtype=torch.bfloat16)
-    K_.add_rmsnorm(x.clone(), None, None, nw, eps, hh, None)
-    two = hh.double() @ w.double().T
-    assert nmse(out.double().cpu().numpy(), two.cpu().numpy()) <= 4.0 * 2.0 ** -18
-    one = torch.empty(1, M, device=G.DEV, dtype=torch.bfloat16)
-    K_.linear_stream_normed(x[N - 1:].contiguous(), nw, eps, w, one, "plain")
-    assert torch.equal(one[0], out[N - 1])                 # a row does not depend on the batch it is in
-    F = (M // 2) // 8 * 8
-    act = torch.full((N, F), float("nan"), device=G.DEV, dtype=torch.bfloat16)
-    wgu = torch.cat([w[:F], w[M - F:]]).contiguous()
-    K_.linear_stream_normed(x, nw, eps, wgu, act, "swiglu")
-    h = (x.double() * nw.double()).float().bfloat16().double()
-    gt = ((h @ wgu[:F].double().T) * inv).float().bfloat16().double()
-    up = ((h @ wgu[F:].double().T) * inv).float().bfloat16().double()
-    close(act, gt * torch.sigmoid(gt) * up, torch.bfloat16, "normalising streaming gate/up product")
     a = torch.randn(N, K, generator=g).bfloat16().to(G.DEV)
-    x2 = torch.randn(N, M, generator=g).to(G.DEV)
+    w = (torch.randn(M, K, generator=g) / K ** 0.5).bfloat16().to(G.DEV)
+    x2 = (3.0 * torch.randn(N, M, generator=g)).to(G.DEV)
+    x2[N - 1] *= 40.0                                      # rows of very different size: each has its own 1 / rms
     bias = torch.randn(M, generator=g).to(G.DEV)
+    nw = (1.0 + 0.2 * torch.randn(M, generator=g)).to(G.DEV)
     want = x2.double() + a.double() @ w.double().T
     for b in (None, bias):
-        got = x2.clone()
-        K_.linear_stream_residual(a, w, got, b)
-        close(got, want if b is None else want + bias.double(), torch.float32, "residual add in the streaming product")
-    # the sums of squares of the new rows, by tile of 128 columns, for the norm that follows
-    tiles = (M + 127) // 128
+        for _ in range(2):
+            got = x2.clone()
+            K_.linear_stream_residual(a, w, got, b)
+            close(got, want if b is None else want + bias.double(), torch.float32, "residual add in the streaming product")
+    tiles = (M + 31) // 32
     sums = torch.full((tiles, 16), float("nan"), device=G.DEV)
-    got = x2.clone()
-    K_.linear_stream_residual(a, w, got, bias, sums)
-    sq = torch.nn.functional.pad(got.double() ** 2, (0, tiles * 128 - M)).reshape(N, tiles, 128).sum(-1).T
+    scaled = torch.full((N, M), float("nan"), device=G.DEV, dtype=torch.bfloat16)
+    x = x2.clone()
+    K_.linear_stream_residual(a, w, x, bias, sums, nw, scaled)
+    close(x, want + bias.double(), torch.float32, "residual add that also prepares the norm")
+    sq = torch.nn.functional.pad(x.double() ** 2, (0, tiles * 32 - M)).reshape(N, tiles, 32).sum(-1).T
     assert float((sums[:, :N].double() - sq).abs().max()) <= 1e-5 * float(sq.max())
     assert float(sums[:, N:].abs().max() if N < 16 else 0.0) == 0.0
-    # ... which the normalising product takes instead of reading the rows: got (N, M) is now the stream, W2 (M2, M)
-    M2 = 136
-    w2 = (torch.randn(M2, M, generator=g) / M ** 0.5).bfloat16().to(G.DEV)
-    nw2 = (1.0 + 0.2 * torch.randn(M, generator=g)).to(G.DEV)
-    if M % 8 == 0:
-        with_sums = torch.empty(N, M2, device=G.DEV, dtype=torch.bfloat16)
-        without = torch.empty(N, M2, device=G.DEV, dtype=torch.bfloat16)
-        K_.linear_stream_normed(got, nw2, eps, w2, with_sums, "plain", sums)
-        K_.linear_stream_normed(got, nw2, eps, w2, without, "plain")
-        assert float((with_sums.double() - without.double()).abs().max()) <= 2.0 ** -7 * float(without.double().abs().max())
+    assert torch.equal(scaled, (x * nw).bfloat16())
+    # the product after the norm: x (N, M) is now the stream, W2 (M2, M)
+    if M % 8:
+        return
+    for M2 in (136, 4096 if M <= 4096 else 264):
+        w2 = (torch.randn(M2, M, generator=g) / M ** 0.5).bfloat16().to(G.DEV)
+        inv = torch.rsqrt((x.double() ** 2).mean(-1, keepdim=True) + eps)
+        want2 = (scaled.double() @ w2.double().T) * inv
+        out = torch.full((N, M2), float("nan"), device=G.DEV, dtype=torch.bfloat16)
+        K_.linear_stream(scaled, w2, out, "plain", sums, eps)
+        close(out, want2, torch.bfloat16, "streaming product of the normalised stream")
+        # against the norm kernel followed by the product: the same up to the rounding of the normalised row
+        hh = torch.empty(N, M, device=G.DEV, dtype=torch.bfloat16)
+        K_.add_rmsnorm(x.clone(), None, None, nw, eps, hh, None)
+        assert nmse(out.double().cpu().numpy(), (hh.double() @ w2.double().T).cpu().numpy()) <= 4.0 * 2.0 ** -18
+        one = torch.empty(1, M2, device=G.DEV, dtype=torch.bfloat16)
+        K_.linear_stream(scaled[N - 1:].contiguous(), w2, one, "plain",
+                         torch.nn.functional.pad(sums[:, N - 1:N], (0, 15)).contiguous(), eps)
+        assert torch.equal(one[0], out[N - 1])             # a row does not depend on the batch it is in
+        F = (M2 // 2) // 8 * 8
+        act = torch.full((N, F), float("nan"), device=G.DEV, dtype=torch.bfloat16)
+        wgu = torch.cat([w2[:F], w2[M2 - F:]]).contiguous()
+        K_.linear_stream(scaled, wgu, act, "swiglu", sums, eps)
+        gt = ((scaled.double() @ wgu[:F].double().T) * inv).float().bfloat16().double()
+        up = ((scaled.double() @ wgu[F:].double().T) * inv).float().bfloat16().double()
+        close(act, gt * torch.sigmoid(gt) * up, torch.bfloat16, "streaming gate/up product of the normalised stream")
     K_.check_error_word(K_.error_word(G.DEV))
-
-
-@pytest.mark.parametrize("pairing,HD,RD,H,KV,bias,new", [("adjacent", 64, 64, 4, 2, True, [1, 1, 1]), ("halves", 32, 16, 3, 1, False, [2, 1, 5]),
-                                                         ("halves", 128, 128, 2, 2, True, [1, 1, 1, 1, 1, 1, 1, 1]),
-                                                         ("halves", 128, 64, 5, 1, False, [16]), ("adjacent", 16, 16, 3, 3, True, [1, 2])])
-def test_streaming_qkv_product_with_rotation_and_cache_write_in_its_epilogue(pairing, HD, RD, H, KV, bias, new):
-    """norm + q/k/v product + rotation + cache write as one streaming kernel leaves what the normalising
-    streaming product followed by the rotate-and-store kernel leaves: q in the buffer, k and v in their pages"""
-    K_ = ops()
-    g = torch.Generator().manual_seed(33)
-    D, page = 256, 8
-    lens = [37, 5, 90, 12, 64, 7, 300, 21][:len(new)]
-    seqs = G.PagedSequences(lens, new, H, KV, HD, page, torch.bfloat16, seed=6).build()
-    N, M = seqs.N, (H + 2 * KV) * HD
-    x = (2.0 * torch.randn(N, D, generator=g)).to(G.DEV)
-    nw = (1.0 + 0.2 * torch.randn(D, generator=g)).to(G.DEV)
-    w = (torch.randn(M, D, generator=g) / D ** 0.5).bfloat16().to(G.DEV)
-    b = (0.5 * torch.randn(M, generator=g)).to(G.DEV) if bias else None
-    freqs = torch.from_numpy(plain.rope_frequencies(10000.0, RD, None)).to(G.DEV)
-    pr = 0 if pairing == "adjacent" else 1
-    err = K_.new_error_word(G.DEV)
-    k2, v2 = torch.zeros_like(seqs.kpool), torch.zeros_like(seqs.vpool)
-    two = torch.empty(N, M, device=G.DEV, dtype=torch.bfloat16)
-    K_.linear_stream_normed(x, nw, 1e-5, w, two, "plain")
-    K_.rope_kv_write(two, b, seqs.positions, seqs.tok_row, seqs.table, k2, v2, freqs, H, KV, HD, RD, pr, page,
-                     seqs.num_pages, err)
-    for _ in range(2):
-        k1, v1 = torch.zeros_like(seqs.kpool), torch.zeros_like(seqs.vpool)
-        one = torch.zeros(N, M, device=G.DEV, dtype=torch.bfloat16)
-        K_.linear_stream_normed_qkv(x, nw, 1e-5, w, one, b, seqs.positions, seqs.tok_row, seqs.table, k1, v1, freqs, H, KV,
-                                    HD, RD, pr, page, seqs.num_pages, err)
-        K_.check_error_word(err)
-        assert torch.equal(one[:, :H * HD], two[:, :H * HD])
-        assert torch.equal(k1, k2) and torch.equal(v1, v2) and float(k1.float().abs().sum()) > 0
-    three = torch.zeros(N, M, device=G.DEV, dtype=torch.bfloat16)
-    K_.linear_stream_normed_qkv(x, nw, 1e-5, w, three, b, seqs.positions, seqs.tok_row, seqs.table, None, None, freqs, H, KV,
-                                HD, RD, pr, page, seqs.num_pages, err)
-    assert torch.equal(three[:, :H * HD], one[:, :H * HD])
-    with pytest.raises(Exception, match="does not take these sizes"):       # a head size that does not divide 128
-        K_.linear_stream_normed_qkv(x, nw, 1e-5, w[:4 * 48].contiguous(), three[:, :4 * 48].contiguous(), None, seqs.positions,
-                                    seqs.tok_row, seqs.table, None, None, freqs, 2, 1, 48, 16, pr, page, seqs.num_pages, err)
 
 
 @pytest.mark.parametrize("N,M,K", [(1, 4096, 4096), (4, 6144, 4096), (2, 509, 320), (3, 4096, 14336), (1, 57, 72), (2, 37, 8200)])
