@@ -199,6 +199,17 @@ __global__ void __launch_bounds__(S_THREADS, 1) gemm_stream_kernel(const __grid_
                     old[a] = (m < M && n < N) ? __ldcg(reinterpret_cast<const float*>(out) + (size_t)n * M + m) : 0.0f;
                 }
             }
+            float row_b[4] = {0.0f, 0.0f, 0.0f, 0.0f}, row_w[4] = {0.0f, 0.0f, 0.0f, 0.0f};      // bias and next norm's weight of this thread's rows
+            if (EPI == 3 && active) {
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    const int m = tile * TH + mg * 32 + (q >> 1) * 16 + g + (q & 1) * 8;
+                    if (m < M) {
+                        if (bias) row_b[q] = __ldg(bias + m);
+                        if (after.scaled) row_w[q] = __ldg(after.w + m);
+                    }
+                }
+            }
             for (int kb = k_lo; kb < k_hi; kb++, it++) {
                 const int s = it % STAGES, round = it / STAGES;
                 if (!mbar_wait(full0 + 8 * s, round & 1, err)) { ok = false; break; }
@@ -298,9 +309,9 @@ __global__ void __launch_bounds__(S_THREADS, 1) gemm_stream_kernel(const __grid_
                         if (EPI == 2) {
                             reinterpret_cast<float*>(out)[(size_t)n * M + m] = v;
                         } else if (EPI == 3) {
-                            v += old[a] + (bias ? bias[m] : 0.0f);
+                            v += old[a] + row_b[((a >> 3) & 1) * 2 + ((a >> 1) & 1)];
                             reinterpret_cast<float*>(out)[(size_t)n * M + m] = v;
-                            if (after.scaled) after.scaled[(size_t)n * M + m] = __float2bfloat16_rn(v * after.w[m]);
+                            if (after.scaled) after.scaled[(size_t)n * M + m] = __float2bfloat16_rn(v * row_w[((a >> 3) & 1) * 2 + ((a >> 1) & 1)]);
                             accf[a] = v;
                         } else if (EPI == 1) {
                             // gate and up pass through bf16 as they do when the products are separate kernels
