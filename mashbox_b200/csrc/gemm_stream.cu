@@ -181,7 +181,7 @@ __global__ void __launch_bounds__(S_THREADS, 1) gemm_stream_kernel(const __grid_
         const bool active = kg == 0;
         const int tact = mg * 32 + lane;                              // this thread's column of the slots and of meet
         int it = 0;
-        bool ok = true;
+        bool ok = true, have_rms = false;
         if (t128 == 0) s_mark(2);
         for (int j = 0; j < range.n_seg && ok; j++) {
             const StreamSeg sg = range.seg(j);
@@ -236,7 +236,6 @@ __global__ void __launch_bounds__(S_THREADS, 1) gemm_stream_kernel(const __grid_
                 if (lane == 0) mbar_arrive(empty0 + 8 * s);           // this warp has read the stage
             }
             if (!ok) break;
-            if (SCALED && j == 0) asm volatile("bar.sync 2, 160;\n" ::: "memory");      // warp 5 has left 1 / rms
             if (t128 == 0 && j == range.n_seg - 1) s_mark(5);
             if (KG > 1) {
                 // the warps that shared the k of these rows add their sums, in the order of the warps
@@ -295,6 +294,9 @@ __global__ void __launch_bounds__(S_THREADS, 1) gemm_stream_kernel(const __grid_
             }
             if (t128 == 0 && j == range.n_seg - 1) s_mark(6);
             if (!finish) continue;
+            // the first tile this block finishes waits for warp 5's 1 / rms (its loads queue behind the TMA copies, so
+            // not earlier than needed: a wait here while tiles are still to come would stall the ring)
+            if (SCALED && !have_rms) { asm volatile("bar.sync 2, 160;\n" ::: "memory"); have_rms = true; }
             // row r of the tile and token n of sum a of this thread
 #define S_ROW(a) (mg * 32 + (((a) >> 3) & 1) * 16 + g + (((a) >> 1) & 1) * 8)
 #define S_TOK(a) (8 * (((a) >> 2) & 1) + 2 * t + ((a) & 1))
@@ -361,7 +363,7 @@ __global__ void __launch_bounds__(S_THREADS, 1) gemm_stream_kernel(const __grid_
         const int quad = lane & 3, part = lane >> 2;
         float4 ss = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         const float4* rows = reinterpret_cast<const float4*>(nrm.ssq);
-#pragma unroll 8
+#pragma unroll 16
         for (int tl = part; tl < nrm.ssq_tiles; tl += 8) {
             const float4 v = __ldcg(rows + tl * 4 + quad);
             ss.x += v.x; ss.y += v.y; ss.z += v.z; ss.w += v.w;
