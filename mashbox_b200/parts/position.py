@@ -55,17 +55,21 @@ class RotaryEncoding:
         return [Want(self.factors_name, (self.rotary_dim // 2,), "vector", optional=True)]
 
     def frequencies(self, stored_factors=None):
+        """float32 angle per position step of every rotated pair.  Stored divisors stand in for the computed llama3
+        ones; the linear factor multiplies whatever the divisors are (the reference divides by the stored tensor and
+        multiplies by 1/factor in the same expression, dense.py:316-317)."""
         f = base_frequencies(self.theta, self.rotary_dim)
+        kind = self.scaling[0] if self.scaling else None
+        if kind not in (None, "linear", "llama3"):
+            raise ValueError(self.scaling)
         if stored_factors is not None:
-            return (f / np.asarray(stored_factors, np.float32)).astype(np.float32)
-        if self.scaling is None:
-            return f
-        if self.scaling[0] == "linear":
-            return (f * np.float32(1.0 / self.scaling[1])).astype(np.float32)
-        if self.scaling[0] == "llama3":
+            f = (f / np.asarray(stored_factors, np.float32)).astype(np.float32)
+        elif kind == "llama3":
             _, factor, low, high, original = self.scaling
-            return (f / llama3_factors(self.theta, self.rotary_dim, factor, low, high, original)).astype(np.float32)
-        raise ValueError(self.scaling)
+            f = (f / llama3_factors(self.theta, self.rotary_dim, factor, low, high, original)).astype(np.float32)
+        if kind == "linear":
+            f = (f * np.float32(1.0 / self.scaling[1])).astype(np.float32)
+        return f
 
     def bind(self, tensors, env):
         import torch

@@ -100,20 +100,23 @@ def llama3_factors(theta, dim, sc):
     return np.asarray(out, np.float32)
 
 
-def rope_frequencies(theta, rd, scaling):
+def rope_frequencies(theta, rd, scaling, stored=None):
     """float32 angle per position step for each rotated pair: inv_i = theta^(-2i/RD) (src/mashbox/gguf/archs/
-    dense.py:302), divided by the llama3 factors when there are any (dense.py:316), times 1/factor for linear
-    scaling (dense.py:93-94, 317)."""
+    dense.py:302), divided by the file's rope_freqs.weight when it has one, else by the llama3 factors when the
+    configuration asks for them (dense.py:316; the Hugging Face path makes that tensor from the configuration,
+    src/mashbox/hf/adapter.py:263-265), times 1/factor for linear scaling (dense.py:93-94, 317)."""
     inv = (1.0 / (np.float32(theta) ** (np.arange(0, rd, 2, dtype=np.int64).astype(np.float32) / np.float32(rd)))
            ).astype(np.float32)
     kind = (scaling or {}).get("rope_type", (scaling or {}).get("type"))
-    if kind in (None, "default"):
-        return inv
+    if kind not in (None, "default", "linear", "llama3"):
+        raise ValueError(kind)
+    if stored is not None:
+        inv = (inv / np.asarray(stored, np.float32)).astype(np.float32)
+    elif kind == "llama3":
+        inv = (inv / llama3_factors(theta, rd, scaling)).astype(np.float32)
     if kind == "linear":
-        return (inv * np.float32(1.0 / float(scaling["factor"]))).astype(np.float32)
-    if kind == "llama3":
-        return (inv / llama3_factors(theta, rd, scaling)).astype(np.float32)
-    raise ValueError(kind)
+        inv = (inv * np.float32(1.0 / float(scaling["factor"]))).astype(np.float32)
+    return inv
 
 
 def rope_adjacent(x, positions, freqs):
@@ -122,7 +125,7 @@ def rope_adjacent(x, positions, freqs):
     x (T, heads, HD), positions (T,) ints."""
     rd = 2 * len(freqs)
     ang = (np.asarray(positions, np.float32)[:, None] * np.asarray(freqs, np.float32)[None, :]).astype(np.float32)
-    ang = torch.from_numpy(ang.astype(np.float64))
+    ang = torch.from_numpy(ang.astype(np.float64)).to(x.device)
     cos, sin = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
     a, b = x[..., 0:rd:2], x[..., 1:rd:2]
     rot = torch.stack([a * cos - b * sin, a * sin + b * cos], -1).reshape(x.shape[:-1] + (rd,))
@@ -134,7 +137,7 @@ def rope_halves(x, positions, freqs):
     adjacent form on permuted rows (that equality is what the permutation is for)."""
     rd = 2 * len(freqs)
     ang = (np.asarray(positions, np.float32)[:, None] * np.asarray(freqs, np.float32)[None, :]).astype(np.float32)
-    ang = torch.from_numpy(ang.astype(np.float64))
+    ang = torch.from_numpy(ang.astype(np.float64)).to(x.device)
     cos, sin = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
     a, b = x[..., :rd // 2], x[..., rd // 2:rd]
     return torch.cat([a * cos - b * sin, b * cos + a * sin, x[..., rd:]], -1)
@@ -153,7 +156,7 @@ def attention(q, k, v, scale, window=None, positions=None):
     T, H, HD = q.shape
     KV = k.shape[1]
     G = H // KV
-    pos = torch.arange(T) if positions is None else torch.as_tensor(positions)
+    pos = (torch.arange(T) if positions is None else torch.as_tensor(positions)).to(q.device)
     s = torch.einsum("tkgd,skd->kgts", q.reshape(T, KV, G, HD), k) * scale
     mask = pos[:, None] >= pos[None, :]
     if window is not None:
@@ -184,54 +187,74 @@ def round_bf16(t):
     return t.to(torch.float32).to(torch.bfloat16).to(F64)
 
 
-def block(x, W, l, c, freqs, positions, held=_same):
+# Tensor names of a layer and of the model in the two conventions a file may use: Hugging Face
+# (src/mashbox/hf/adapter.py:183-192) and GGUF (src/mashbox/gguf/archs/dense.py:135-139, 241-248).
+HF_NAMES = dict(layer="model.layers.{}.", ln1="input_layernorm", q="self_attn.q_proj", k="self_attn.k_proj",
+                v="self_attn.v_proj", o="self_attn.o_proj", ln2="post_attention_layernorm", gate="mlp.gate_proj",
+                up="mlp.up_proj", down="mlp.down_proj", embed="model.embed_tokens.weight", norm="model.norm.weight",
+                head="lm_head.weight", permute=True)
+GGUF_NAMES = dict(layer="blk.{}.", ln1="attn_norm", q="attn_q", k="attn_k", v="attn_v", o="attn_output",
+                  ln2="ffn_norm", gate="ffn_gate", up="ffn_up", down="ffn_down", embed="token_embd.weight",
+                  norm="output_norm.weight", head="output.weight", permute=False)
+
+
+def block(x, W, l, c, freqs, positions, held=_same, names=HF_NAMES):
     """One pre-norm residual block: x += attn(ln1(x)); x += ffn(ln2(x)).  src/mashbox/gguf/archs/dense.py:339-357.
-    W holds Hugging Face names; q/k rows are permuted here as the loader of the reference does.  `held` is applied to
-    every tensor the reference holds in its activation dtype (dense.py:335-357: the results of rms, of every matmul,
-    of the rotation and of silu*up are cast to `act`; biases are added in float32 before the cast of q, k, v and
-    after it for the output); the identity gives the exact model, round_bf16 a model of bfloat16 storage."""
-    p = f"model.layers.{l}."
+    With Hugging Face names q/k rows are permuted here as the loader of the reference does; GGUF-named q/k rows are
+    in adjacent-pair order already (src/mashbox/hf/adapter.py:223-225 is what a converter did to them).  `held` is
+    applied to every tensor the reference holds in its activation dtype (dense.py:335-357: the results of rms, of
+    every matmul, of the rotation and of silu*up are cast to `act`; biases are added in float32 before the cast of q,
+    k, v and after it for the output); the identity gives the exact model, round_bf16 a model of bfloat16 storage."""
+    p = names["layer"].format(l)
     T = x.shape[0]
     H, KV, HD = c["H"], c["KV"], c["HD"]
-    bias = lambda n: W.get(p + n)
+    weight = lambda n: W[p + names[n] + ".weight"]
+    bias = lambda n: W.get(p + names[n] + ".bias")
     plus = lambda y, b: y if b is None else y + b
-    h = held(rms_norm(x, W[p + "input_layernorm.weight"], c["eps"]))
-    wq, wk = permute_rows(W[p + "self_attn.q_proj.weight"], H), permute_rows(W[p + "self_attn.k_proj.weight"], KV)
-    bq, bk = bias("self_attn.q_proj.bias"), bias("self_attn.k_proj.bias")
-    bq = None if bq is None else permute_rows(bq, H)
-    bk = None if bk is None else permute_rows(bk, KV)
+    h = held(rms_norm(x, weight("ln1"), c["eps"]))
+    wq, wk, bq, bk = weight("q"), weight("k"), bias("q"), bias("k")
+    if names["permute"]:
+        wq, wk = permute_rows(wq, H), permute_rows(wk, KV)
+        bq = None if bq is None else permute_rows(bq, H)
+        bk = None if bk is None else permute_rows(bk, KV)
     q = plus(held(linear(h, wq)), bq).reshape(T, H, HD)
     k = plus(held(linear(h, wk)), bk).reshape(T, KV, HD)
-    v = held(plus(held(linear(h, W[p + "self_attn.v_proj.weight"])), bias("self_attn.v_proj.bias"))).reshape(T, KV, HD)
+    v = held(plus(held(linear(h, weight("v"))), bias("v"))).reshape(T, KV, HD)
     q, k = held(rope_adjacent(q, positions, freqs)), held(rope_adjacent(k, positions, freqs))
     o = held(attention(q, k, v, HD ** -0.5, window=c.get("window"), positions=positions))
-    x = x + plus(held(linear(o, W[p + "self_attn.o_proj.weight"])), bias("self_attn.o_proj.bias"))
-    h = held(rms_norm(x, W[p + "post_attention_layernorm.weight"], c["eps"]))
-    g = held(linear(h, W[p + "mlp.gate_proj.weight"]))
-    u = held(linear(h, W[p + "mlp.up_proj.weight"]))
+    x = x + plus(held(linear(o, weight("o"))), bias("o"))
+    h = held(rms_norm(x, weight("ln2"), c["eps"]))
+    g = held(linear(h, weight("gate")))
+    u = held(linear(h, weight("up")))
     a = held(g * torch.sigmoid(g) * u)                                  # dense.py:356
-    return x + held(linear(a, W[p + "mlp.down_proj.weight"]))
+    return x + held(linear(a, weight("down")))
 
 
-def head(x, W, c, held=_same):
+def head(x, W, c, held=_same, names=HF_NAMES):
     """logits = rms(x, norm) W_head^T; the head is the embedding when tied.  src/mashbox/gguf/archs/dense.py:386-390,
     tie dense.py:129.  The logits themselves stay unrounded (this engine keeps them in float32)."""
-    w = W["model.embed_tokens.weight"] if c["tie"] or "lm_head.weight" not in W else W["lm_head.weight"]
-    return held(rms_norm(x, W["model.norm.weight"], c["eps"])) @ w.T
+    w = W[names["embed"]] if c["tie"] or names["head"] not in W else W[names["head"]]
+    return held(rms_norm(x, W[names["norm"]], c["eps"])) @ w.T
 
 
-def forward(cfg, W, tokens, held=_same):
-    """Logits (T, V) float64 at every position of one whole sequence.  src/mashbox/gguf/archs/dense.py:309-392.
-    held: see block()."""
+def forward(cfg, W, tokens, held=_same, device=None, rows=None):
+    """Logits (T, V) float64 at every position of one whole sequence (rows: only at these positions).
+    src/mashbox/gguf/archs/dense.py:309-392.  held: see block().  The tensors may carry Hugging Face names or GGUF
+    names (told apart by the embedding's name); a GGUF-named set may bring rope_freqs.weight.  device: where the
+    float64 arithmetic runs (a large model is slow on the CPU)."""
     c = sizes(cfg)
-    W = {k: v.to(F64) for k, v in W.items()}
+    names = GGUF_NAMES if GGUF_NAMES["embed"] in W else HF_NAMES
+    W = {k: torch.as_tensor(v).to(device=device, dtype=F64) for k, v in W.items()}
     tokens = [int(t) for t in tokens]
     positions = np.arange(len(tokens))
-    freqs = rope_frequencies(c["theta"], c["HD"], c["scaling"])
-    x = W["model.embed_tokens.weight"][torch.tensor(tokens)]           # dense.py:328
+    stored = W["rope_freqs.weight"].cpu().numpy() if "rope_freqs.weight" in W else None
+    freqs = rope_frequencies(c["theta"], c["HD"], c["scaling"], stored)
+    x = W[names["embed"]][torch.tensor(tokens, device=device)]          # dense.py:328
     for l in range(c["L"]):
-        x = block(x, W, l, c, freqs, positions, held)
-    return head(x, W, c, held)
+        x = block(x, W, l, c, freqs, positions, held, names)
+    if rows is not None:
+        x = x[torch.as_tensor(list(rows), device=device)]
+    return head(x, W, c, held, names)
 
 
 def greedy(cfg, W, prompt, n):

@@ -74,3 +74,49 @@ def test_rounded_model_is_close_to_the_exact_one():
     b = plain.forward(m["config"], W, m["tokens"], held=plain.round_bf16).numpy()
     e = ((a - b) ** 2).sum() / (a ** 2).sum()
     assert 0 < e < 1e-3
+
+
+# ---------------------------------------------------------------------------------------- llama.cpp's logits (GGUF names)
+from tests.golden import gguf_llama
+
+LLAMA_CPP_NMSE = 1e-10      # the reference's bar between two float32 programs is 1e-4 (tests/contracts/test_arch.py:11-38)
+
+
+def gguf_case(name):
+    return gguf_llama.config(name), {k: torch.from_numpy(v) for k, v in gguf_llama.tensors(name).items()}, \
+        gguf_llama.reference(name)
+
+
+@pytest.mark.parametrize("name", list(gguf_llama.CASES))
+def test_rebuilt_gguf_tensors_are_the_reference_files_tensors(name):
+    want = gguf_llama.tensor_digests()[name]
+    got = {k: gguf_llama.digest(v) for k, v in gguf_llama.tensors(name).items()}
+    assert got == want
+
+
+@pytest.mark.parametrize("name", list(gguf_llama.CASES))
+def test_plain_matches_llama_cpp_logits(name):
+    """GGUF-named tensors: q/k rows already in adjacent-pair order, rope_freqs.weight as stored, biases, a tied head,
+    an eps near the activations' mean square, linear scaling on top of the stored divisors."""
+    cfg, W, ref = gguf_case(name)
+    got = plain.forward(cfg, W, ref["tokens"]).numpy()
+    from tests.tolerances import nmse
+    assert nmse(got, ref["logits"]) <= LLAMA_CPP_NMSE
+    assert (got.argmax(-1) == ref["logits"].argmax(-1)).all()
+
+
+def test_the_gguf_fixtures_show_what_they_are_for():
+    """Each option the fixtures pin moves the logits far beyond the bar when it is ignored: the stored divisors, the
+    linear factor, the eps of the file, the pre-permuted row order."""
+    from tests.tolerances import nmse
+    cfg, W, ref = gguf_case("llama-linear-f32")
+    no_factor = dict(cfg, rope_scaling=None)
+    assert nmse(plain.forward(no_factor, W, ref["tokens"]).numpy(), ref["logits"]) > 1e-3
+    no_divisors = {k: v for k, v in W.items() if k != "rope_freqs.weight"}
+    assert nmse(plain.forward(cfg, no_divisors, ref["tokens"]).numpy(), ref["logits"]) > 1e-3
+    cfg, W, ref = gguf_case("llama-eps-f32")
+    assert nmse(plain.forward(dict(cfg, rms_norm_eps=1e-5), W, ref["tokens"]).numpy(), ref["logits"]) > 1e-3
+    cfg, W, ref = gguf_case("llama-f32")
+    again = dict(W)
+    again["blk.0.attn_q.weight"] = plain.permute_rows(W["blk.0.attn_q.weight"], cfg["num_attention_heads"])
+    assert nmse(plain.forward(cfg, again, ref["tokens"]).numpy(), ref["logits"]) > 1e-3

@@ -187,8 +187,38 @@ def test_bad_files(tmp_path):
 
 
 def test_reads_the_reference_fixture_files():
+    """the loader binds the reference's two Hugging Face fixtures as the plain implementation reads them: q/k rows and
+    biases permuted for adjacent pairs, q|k|v stacked, the llama3 divisors from rope_parameters, the tied head"""
     for name in ("llama", "mistral"):
         m = ANCHORS["models"][name]
+        c = plain.sizes(m["config"])
         W = plain.read_safetensors(os.path.join(GOLD, f"hf_{name}.safetensors"))
         model = build_model(m["config"], DictSource({k: v.float() for k, v in W.items()}), "float32", "cpu")
-        assert len(model.layers) == m["config"]["num_hidden_layers"]
+        assert len(model.layers) == c["L"]
+        for l, block in enumerate(model.layers):
+            p = f"model.layers.{l}.self_attn."
+            want = torch.cat([plain.permute_rows(W[p + "q_proj.weight"], c["H"]),
+                              plain.permute_rows(W[p + "k_proj.weight"], c["KV"]), W[p + "v_proj.weight"]]).float()
+            assert torch.equal(block.mixer.wqkv, want)
+            if p + "q_proj.bias" in W:
+                wb = torch.cat([plain.permute_rows(W[p + "q_proj.bias"], c["H"]),
+                                plain.permute_rows(W[p + "k_proj.bias"], c["KV"]), W[p + "v_proj.bias"]]).float()
+                assert torch.equal(block.mixer.bqkv, wb)
+            assert np.array_equal(block.mixer.position.freqs.numpy(),
+                                  plain.rope_frequencies(c["theta"], c["HD"], c["scaling"]))
+        tied = c["tie"]
+        assert (model.head.weight.data_ptr() == model.embedding.table.data_ptr()) == tied
+
+
+def test_stored_divisors_and_the_linear_factor_apply_together():
+    """a GGUF-named file may bring rope_freqs.weight AND ask for linear scaling: angle = pos * inv / divisor / factor
+    (src/mashbox/gguf/archs/dense.py:93-94, 316-317)"""
+    from mashbox_b200.parts.position import RotaryEncoding, base_frequencies
+    div = np.linspace(1.0, 8.0, 16).astype(np.float32)
+    got = RotaryEncoding(32, 32, 5e5, ("linear", 4.0)).frequencies(div)
+    want = ((base_frequencies(5e5, 32) / div).astype(np.float32) * np.float32(0.25)).astype(np.float32)
+    assert np.array_equal(got, want)
+    assert np.array_equal(got, plain.rope_frequencies(5e5, 32, dict(rope_type="linear", factor=4.0), div))
+    # stored divisors stand in for the llama3 ones the configuration would give
+    sc = ("llama3", 8.0, 1.0, 4.0, 64)
+    assert np.array_equal(RotaryEncoding(32, 32, 5e5, sc).frequencies(div), (base_frequencies(5e5, 32) / div).astype(np.float32))
