@@ -2,10 +2,13 @@
 
 Layers whose mixers keep the same thing form a *group* (all keys of every position; the keys of a window; nothing).
 Each group has its own pool of pages and its own block tables, so a group with a window gives pages back as soon as
-the window has passed them while a full group keeps them until the request ends.  A page of a group holds `page_size`
-positions of every layer of the group: pools are tensors (layers, 2 [k, v], pages, kv heads, page_size, head size), so
-one kv head of one page is contiguous.  Position p of a request lives in page table[row, p // page_size], slot
-p % page_size; an entry is -1 before it is given and again after a window has passed it.
+the window has passed them while a full group keeps them until the request ends.  What a mixer keeps per position is
+its own business: a need lists the tensors (heads, width) one position holds -- keys and values of equal shape for
+attention, one latent vector for a mixer that keeps such, keys and values of different widths -- and the group gets one
+pool per listed tensor, (layers, pages, heads, page_size, width), so one head of one page is contiguous.  A page of a
+group holds `page_size` positions of every layer of the group.  Position p of a request lives in page
+table[row, p // page_size], slot p % page_size; an entry is -1 before it is given and again after a window has passed
+it.
 
 Per-request state of fixed size (a recurrent mixer's state) lives in `state` tensors indexed by the request's state
 slot; a slot is zeroed when a request takes it.  The Llama architecture has no such state: its slot count is still
@@ -26,11 +29,17 @@ from .pages import Pool
 
 @dataclass(frozen=True)
 class CacheNeed:
-    """What one mixer keeps per position: kind "full" (every position) or "window" (the last `window` positions)."""
+    """What one mixer keeps per position: kind "full" (every position) or "window" (the last `window` positions), and
+    `tensors`, one (heads, width) per tensor a position holds, each stored in a pool of its own."""
     kind: str
-    kv_heads: int
-    head_dim: int
+    tensors: tuple
     window: Optional[int] = None
+
+    @classmethod
+    def keys_and_values(cls, kv_heads, head_dim, window=None):
+        """what attention keeps: a key and a value of (kv_heads, head_dim) per position"""
+        shape = (int(kv_heads), int(head_dim))
+        return cls("window" if window else "full", (shape, shape), int(window) if window else None)
 
 
 @dataclass(frozen=True)
@@ -46,7 +55,7 @@ class Group:
         self.index_of = {c: i for i, c in enumerate(self.cache_ids)}
         self.pool = Pool(num_pages, "page")
         self.table = np.full((max_requests, max_blocks), -1, np.int32)
-        self.kv = None                      # device tensor (layers, 2, pages, kv heads, page_size, head size)
+        self.pools = None                   # device tensors, one per tensor of the need: (layers, pages, heads, page_size, width)
         self.device_table = None            # device copy of `table`
         self.pending = []                   # (flat index, value) table changes not yet on the device
 
@@ -71,7 +80,8 @@ class CacheManager:
         for cid, need in needs.items():
             if need is None:
                 continue
-            if need.kind not in ("full", "window") or (need.kind == "window" and not need.window):
+            if need.kind not in ("full", "window") or (need.kind == "window" and not need.window) or not need.tensors \
+                    or any(len(t) != 2 or min(t) < 1 for t in need.tensors):
                 raise CacheError(f"cache need {need} is not understood")
             by_need.setdefault(need, []).append(cid)
         self.groups = [Group(need, cids, self.num_pages, self.max_requests, self.max_blocks)
@@ -85,9 +95,8 @@ class CacheManager:
         if device is not None:
             import torch
             for g in self.groups:
-                n = g.need
-                g.kv = torch.zeros((len(g.cache_ids), 2, self.num_pages, n.kv_heads, self.page_size, n.head_dim),
-                                   dtype=dtype, device=device)
+                g.pools = [torch.zeros((len(g.cache_ids), self.num_pages, heads, self.page_size, width), dtype=dtype,
+                                       device=device) for heads, width in g.need.tensors]
                 g.device_table = torch.full((self.max_requests, self.max_blocks), -1, dtype=torch.int32, device=device)
             for cid, s in self.state_needs.items():
                 self.state[cid] = torch.zeros((self.max_requests,) + tuple(s.shape), dtype=getattr(torch, s.dtype),
@@ -204,10 +213,29 @@ class CacheManager:
             g.pending.clear()
 
     def layer_cache(self, cache_id):
-        """-> (group, k pool, v pool) of one cache id: pools are (pages, kv heads, page_size, head size)"""
+        """-> (group, pool of each tensor of the need ...) of one cache id: a pool is (pages, heads, page_size, width);
+        attention gets (group, k pool, v pool)"""
         g = self.groups[self.group_of[cache_id]]
-        kv = g.kv[g.index_of[cache_id]]
-        return g, kv[0], kv[1]
+        i = g.index_of[cache_id]
+        return (g,) + tuple(pool[i] for pool in g.pools)
+
+    def pages_to_hold(self, tokens, portion):
+        """-> per group, the most pages a request of `tokens` tokens holds at any time when it is fed in portions of at
+        most `portion` tokens: every page of a full group; of a window group only those the window and one portion
+        reach (what lies behind the window is given back at every commit)"""
+        whole = -(-int(tokens) // self.page_size)
+        out = []
+        for g in self.groups:
+            if g.need.kind == "window":
+                out.append(min(whole, -(-(g.need.window - 1 + int(portion)) // self.page_size) + 1))
+            else:
+                out.append(whole)
+        return out
+
+    def pages_held(self, rid):
+        """-> per group, the pages the request holds now"""
+        r = self.get(rid)
+        return [int((g.table[r.row] >= 0).sum()) for g in self.groups]
 
     # -------------------------------------------------------------------------------------------- checks
     def free_pages(self):

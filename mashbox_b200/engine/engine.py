@@ -34,7 +34,8 @@ class Engine:
         self.model = model
         self.runner = ModelRunner(model, self.cfg, options)
         self.cache = self.runner.cache
-        self.scheduler = Scheduler(self.cache, model.vocab, self.cfg.max_tokens_per_step, self.cfg.chunk)
+        align = model.portion_alignment() if hasattr(model, "portion_alignment") else 1
+        self.scheduler = Scheduler(self.cache, model.vocab, self.cfg.max_tokens_per_step, self.cfg.chunk, align)
         self.sampler = Sampler(model.vocab, self.cfg.max_requests, self.runner.device)
         self.log = log
         self.counter = 0
@@ -155,21 +156,22 @@ class Engine:
         wait for the ids of the first, book them and return.  So the GPU never waits for the host between steps.  What
         a placeholder cannot foresee is a stop token: the request then ends as it should, one step late for the GPU:
         the step already queued carries a token of it whose result is dropped."""
+        cur = nxt = None
         try:
             if self._flight is None:
                 prep = self._prepare()
                 if prep is None:
                     return []
                 self._flight = self._launch(prep)
-            cur, nxt = self._flight, None
+            cur = self._flight
             if self.scheduler.busy():
                 prep = self._prepare(cur)
                 if prep is not None and prep is not self.DEFER:
                     nxt = self._launch(prep, cur)
             tokens = self.sampler.wait(cur.pending)
-        except BaseException:
+        except BaseException as e:
             self._flight = None
-            self._drop_live()
+            self._drop_live([f for f in (cur, nxt) if f is not None], f"a step failed: {type(e).__name__}: {e}")
             raise
         self._flight = nxt
         now = time.perf_counter()
@@ -196,12 +198,23 @@ class Engine:
         self.stats["generated_tokens"] += len(tokens)
         return ended
 
-    def _drop_live(self):
+    def _drop_live(self, flights=(), why="a step failed"):
         """After a failed step nothing that was live can be trusted: every live request ends with "error" and the
-        cache is given back whole (the reference drops its live rows the same way, engine.py:752-762)."""
+        cache is given back whole (the reference drops its live rows the same way, engine.py:752-762).  flights: the
+        steps that were queued and never booked; the tokens they stood placeholders for never arrive, so the
+        placeholders go, and a request that had reached max_new on such a placeholder ends with "error" too."""
+        for f in flights:
+            for p in f.picks:
+                r = p.request
+                had = False
+                while r.generated and r.generated[-1] == self.PLACEHOLDER:
+                    r.generated.pop()
+                    had = True
+                if had and r.finish == "length":
+                    r.finish, r.error = "error", why
         for r in list(self.scheduler.running) + list(self.scheduler.waiting):
             try:
-                self.scheduler.finish(r, "error", "a step failed")
+                self.scheduler.finish(r, "error", why)
             except Exception:
                 pass
 

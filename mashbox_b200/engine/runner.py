@@ -150,7 +150,8 @@ class ModelRunner:
         self.stats["steps"] += 1
 
     def _run_graph(self, ctx):
-        sig = (self.inputs.signature(), getattr(self.ws, "generation", 0), getattr(self.inputs, "generation", 0))
+        sig = (self.inputs.signature(), getattr(self.ws, "generation", 0), getattr(self.inputs, "generation", 0),
+               kernels.scratch_generation())
         g = self.graphs.get(sig)
         if g is not None:
             g[0].replay()

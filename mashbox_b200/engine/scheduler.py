@@ -11,9 +11,16 @@ budget, src/mashbox/runtime/engine.py:953-1074, on whole-context slots instead o
 When pages run out: a decoding request that needs a page none is free for makes the scheduler PREEMPT the most recently
 admitted running request (possibly itself): its pages, row and state slot are given back, it returns to the FRONT of
 the waiting queue with prompt + generated as the tokens to recompute, and its sampling continues at the same token
-index, so its answer does not change.  A prompt portion never preempts anyone: it shrinks to the pages that are free or
-waits.  A waiting request is admitted only when the pages for all its known tokens plus one are free.  A request whose
+index, so its answer does not change.  A prompt portion never preempts a decoding request: it shrinks to the pages that
+are free or waits.  A waiting request is admitted only when the pages for all its known tokens plus one are free AFTER
+the pages that running prompts still have to take are set aside (window groups count only what a window and one
+portion reach), so prompts that are read side by side can all be read to their end.  Should nothing be able to run
+all the same while requests are live, the newest running request is preempted until something can.  A request whose
 prompt + max_new can never fit the pool or the context is refused at check() and touches nothing.
+
+Portions may have to end on a grid: `align` > 1 (a mixer that works on blocks of that many positions; the reference
+cuts on multiples of 64 for such a mixer, src/mashbox/runtime/engine.py:76, 966-967) makes every portion that does not
+reach the request's last known token end at a position that is a multiple of `align`.
 
 Finish reasons as the reference (engine.py:820-827, 1040-1050): "stop" (a stop token, not emitted), "length" (max_new
 reached; the first token counts), "cancel", "error".
@@ -61,9 +68,12 @@ class Planned:
 
 
 class Scheduler:
-    def __init__(self, cache, vocab, max_tokens_per_step=2048, chunk=2048):
+    def __init__(self, cache, vocab, max_tokens_per_step=2048, chunk=2048, align=1):
         self.cache, self.vocab = cache, int(vocab)
-        self.budget, self.chunk = int(max_tokens_per_step), int(chunk)
+        self.budget, self.chunk, self.align = int(max_tokens_per_step), int(chunk), max(1, int(align))
+        if self.align > min(self.budget, self.chunk):
+            raise RequestError(f"portions end on multiples of {self.align}: the step's token budget ({self.budget}) and "
+                               f"the chunk ({self.chunk}) must be at least that")
         self.waiting, self.running = deque(), []
         self.counter = 0
         self.stats = dict(preemptions=0, steps=0)
@@ -114,6 +124,21 @@ class Scheduler:
     def plan(self):
         """-> list of Planned for the next step (empty when nothing can run).  Pages are not taken here: the step
         function takes them; this only makes sure they are there."""
+        while True:
+            plan = self._plan()
+            if plan or not self.running:
+                return plan
+            # live requests, and not one token can run: the newest running request gives way until something can
+            self._preempt(max(self.running, key=lambda q: q.order))
+
+    def _cut(self, r, n):
+        """the portion of at most n tokens that request r may be fed: its end lies on the grid unless it reaches the
+        request's last known token (0: no cut fits, the request waits for a step with more room)"""
+        if self.align == 1 or n >= r.remaining:
+            return n
+        return max(0, (r.computed + n) // self.align * self.align - r.computed)
+
+    def _plan(self):
         cache = self.cache
         free = list(cache.free_pages())
         plan, used = [], 0
@@ -124,6 +149,12 @@ class Scheduler:
         def take(r, n):
             for gi, a in enumerate(cache.pages_needed(r.rid, n)):
                 free[gi] -= a
+
+        def owed(r, n):
+            """pages request r still has to take after a portion of n tokens to hold all its known tokens + 1"""
+            hold = cache.pages_to_hold(len(r.prompt) + len(r.generated) + 1, self.chunk)
+            return [max(0, h - have - new) for h, have, new in
+                    zip(hold, cache.pages_held(r.rid), cache.pages_needed(r.rid, n))]
 
         # 1. every decoding request gets its token; newest running requests give way when pages are short
         decoding = [r for r in self.running if r.remaining == 1]
@@ -144,30 +175,34 @@ class Scheduler:
                 take(r, 1)
         used = len(plan)
         # 2. portions of prompts already running, first come first served
+        aside = [0] * len(free)             # pages the running prompts have still to take after this step
         for r in self.running:
-            if r.remaining <= 1 or used >= self.budget:
+            if r.remaining <= 1:
                 continue
-            n = min(r.remaining, self.chunk, self.budget - used)
+            n = self._cut(r, min(r.remaining, self.chunk, max(0, self.budget - used)))
             while n > 0 and not fits(r, n):
-                n = self._shrink(r, n, free)
+                n = self._cut(r, self._shrink(r, n, free))
             if n > 0:
                 plan.append(Planned(r, r.computed, n, n == r.remaining))
                 take(r, n)
                 used += n
-        # 3. new admissions, in order, while the whole of their known tokens (+1) fits
+            aside = [a + o for a, o in zip(aside, owed(r, n))]
+        # 3. new admissions, in order, while the whole of their known tokens (+1) fits beside what is set aside
         while self.waiting and used < self.budget and cache.can_admit():
             r = self.waiting[0]
             whole = len(r.prompt) + len(r.generated) + 1
-            pages = -(-whole // cache.page_size)
-            if any(pages > f for f in free):
+            if any(p > f - a for p, f, a in zip(cache.pages_to_hold(whole, self.chunk), free, aside)):
+                break
+            n = self._cut(r, min(r.remaining, self.chunk, self.budget - used))
+            if n == 0:
                 break
             self.waiting.popleft()
             cache.admit(r.rid)
             self.running.append(r)
-            n = min(r.remaining, self.chunk, self.budget - used)
             plan.append(Planned(r, r.computed, n, n == r.remaining))
             take(r, n)
             used += n
+            aside = [a + o for a, o in zip(aside, owed(r, n))]
         return plan
 
     def _shrink(self, r, n, free):

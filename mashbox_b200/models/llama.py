@@ -34,7 +34,7 @@ def model_spec(c: LlamaConfig) -> ModelSpec:
     mixer = PartSpec("attention", hidden=c.hidden, heads=c.num_heads, kv_heads=c.num_kv_heads, head_dim=c.head_dim,
                      bias=c.attention_bias, position=rope)
     ffn = PartSpec("swiglu", hidden=c.hidden, intermediate=c.intermediate)
-    layers = [LayerSpec(prefix=f"blk.{i}.", block="prenorm", norm=norm, mixer=mixer, ffn=ffn)
+    layers = [LayerSpec(prefix=f"blk.{i}.", block=PartSpec("prenorm", norm=norm, mixer=mixer, ffn=ffn))
               for i in range(c.num_layers)]
     return ModelSpec(hidden=c.hidden, vocab=c.vocab,
                      embedding=PartSpec("table", vocab=c.vocab, hidden=c.hidden),

@@ -1,14 +1,14 @@
 """A model put together from a ModelSpec: embedding, a list of layers (blocks of parts), the schedule that says in
 which order they run and which cache each run touches, final norm and head.  Nothing here knows an architecture."""
 from ..errors import ConfigError
-from ..parts.base import PartSpec, make
+from ..parts.base import make
 
 
 class Model:
     def __init__(self, spec, config=None):
         self.spec, self.config = spec, config
         self.embedding = make("embedding", spec.embedding)
-        self.layers = [make("block", PartSpec(ls.block), layer=ls) for ls in spec.layers]
+        self.layers = [make("block", ls.block, prefix=ls.prefix) for ls in spec.layers]
         self.schedule = list(spec.schedule)
         self.final_norm = make("norm", spec.final_norm)
         self.head = make("head", spec.head)
@@ -18,12 +18,8 @@ class Model:
         self.hidden, self.vocab = spec.hidden, spec.vocab
         # A step can be replayed from a captured graph only if no part's forward() looks at host values of the batch
         # (sequence lengths, positions): parts say so themselves, and one that does not say it keeps graphs off.
+        # (A part that holds parts of its own, as attention holds its position encoding, answers for them.)
         self.graph_safe = all(getattr(p, "graph_safe", False) for p in self.parts() + self.layers)
-        for b in self.layers:
-            for p in b.parts():
-                pos = getattr(p, "position", None)
-                if pos is not None and not getattr(pos, "graph_safe", False):
-                    self.graph_safe = False
 
     def parts(self):
         out = [self.embedding]
@@ -46,6 +42,12 @@ class Model:
     def bind(self, tensors, env):
         for p in self.parts():
             p.bind(tensors, env)
+
+    def portion_alignment(self):
+        """Portions of a prompt that do not reach its end must end at a multiple of this many positions: the least
+        common multiple of what the parts ask for (`portion_alignment`, 1 when a part does not say)."""
+        import math
+        return math.lcm(*[max(1, int(getattr(p, "portion_alignment", 1))) for p in self.parts()])
 
     def cache_needs(self):
         """-> ({cache id: CacheNeed or None}, {cache id: StateNeed}) from the schedule: the run that writes a cache
@@ -86,8 +88,6 @@ class Model:
             ctx.next_first_norm = after.first_norm() if hasattr(after, "first_norm") else None
             pending = self.layers[run.layer].forward(ctx, x, pending, run)
         if ctx.n_out == 0:
-            if pending is not None:         # keep the stream whole even when nobody asks for logits
-                return None
             return None
         h = self.final_norm.forward(ctx, x, pending, rows=ctx.dev("want"))
         return self.head.forward(ctx, h)

@@ -59,6 +59,16 @@ def _check(code, what):
     raise KernelError(f"{what}: CUDA error {code} at launch")
 
 
+# Scratch that the faces below keep per device (partial sums, counters, reduction buffers) is made once and grows
+# when a larger problem comes.  A captured graph holds the addresses it was captured with, so whoever replays graphs
+# must capture again after a growth: scratch_generation() changes whenever any such buffer was replaced.
+_scratch = {"generation": 0}
+
+
+def scratch_generation():
+    return _scratch["generation"]
+
+
 _fn_cache = {}
 
 
@@ -302,6 +312,7 @@ def _stream_buffers(device, M):
         sc = (torch.empty(lib.mb_gemm_stream_workspace(), dtype=torch.float32, device=device),
               torch.zeros(max(tiles, 8192), dtype=torch.int32, device=device))
         _stream_scratch[key] = sc
+        _scratch["generation"] += 1
     return sc
 
 
@@ -457,6 +468,7 @@ def attention_tma(q, q_stride, out, kpool, vpool, items, n_items, decode, q_star
         key = str(q.device)
         if key not in _merge_counters:
             _merge_counters[key] = torch.zeros(MERGE_COUNTERS, dtype=torch.int32, device=q.device)
+            _scratch["generation"] += 1
         counters = _merge_counters[key]
     f = _fn("attention_tma", "mb_attn_tma_bf16",
             [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
@@ -524,6 +536,7 @@ def sample(logits, work, params, cnt, seen, n_rows, out, any_cut=True, keep_work
               torch.empty(cap * 32, dtype=torch.int32, device=logits.device),
               torch.empty(cap * 2, dtype=torch.int32, device=logits.device))
         _sample_scratch[key] = sc
+        _scratch["generation"] += 1
     f = _fn("sampling", "mb_sample_fast", [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p,
                                            c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p])
     _check(f(_p(logits), _p(work), _p(params), _p(cnt), _p(seen), n_rows, logits.shape[1], _p(sc[2]), _p(sc[0]), _p(sc[1]),
@@ -551,6 +564,7 @@ def argmax(logits, out):
         sc = (torch.empty(max(n, 64) * 32, dtype=torch.float32, device=logits.device),
               torch.empty(max(n, 64) * 32, dtype=torch.int32, device=logits.device))
         _argmax_scratch[key] = sc
+        _scratch["generation"] += 1
     f = _fn("sampling", "mb_argmax", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
     _check(f(_p(logits), n, logits.shape[1], _p(sc[0]), _p(sc[1]), _p(out), _stream()), "argmax")
 

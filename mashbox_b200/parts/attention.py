@@ -23,7 +23,11 @@ DECODE_ROWS, PREFILL_ROWS, KEY_TILE = 16, 64, 64
 
 
 class Attention:
-    graph_safe = True       # forward() depends on the batch only through the lengths of the step's arrays
+    @property
+    def graph_safe(self):
+        """forward() depends on the batch only through the lengths of the step's arrays; so must the position encoding"""
+        return self.position is None or bool(getattr(self.position, "graph_safe", False))
+
     def __init__(self, hidden, heads, kv_heads, head_dim, bias=False, position=None, window=None, scale=None,
                  prefix="", names=None):
         self.D, self.H, self.KV, self.HD = int(hidden), int(heads), int(kv_heads), int(head_dim)
@@ -59,7 +63,7 @@ class Attention:
             self.position.bind(tensors, env)
 
     def cache_need(self):
-        return CacheNeed("window" if self.window else "full", self.KV, self.HD, self.window)
+        return CacheNeed.keys_and_values(self.KV, self.HD, self.window)
 
     def state_need(self):
         return None
@@ -77,7 +81,8 @@ class Attention:
                 and ctx.ops.attention_tc5_supports(self.HD, ctx.cache.page_size))
 
     def plan_key(self):
-        return ("attention", self.H // self.KV, self.KV, self.window)
+        # everything the work list depends on: the head size decides the kernel and its rows per tile
+        return ("attention", self.H // self.KV, self.KV, self.HD, self.window)
 
     def prepare(self, ctx):
         """Work list of the flash kernel for this step: (sequence, row tile, split, splits) per block, decode-form

@@ -16,7 +16,8 @@ Interfaces (all tensors on the device; N = tokens of the step, D = the part's wi
                 forward(ctx, h, run) -> (delta (N, D), bias or None).  run says which cache id it reads and whether
                 it writes it.
   FeedForward   wants(prefix);  bind;  forward(ctx, h) -> (delta, bias or None)
-  Block         built from its parts;  forward(ctx, x, pending, run) -> pending
+  Block         built from the part specs in its own PartSpec and the layer's prefix;  parts() -> every part it
+                holds;  mixer: the part that owns the cache of a run;  forward(ctx, x, pending, run) -> pending
 
 A part may set the class attribute graph_safe = True: its forward() then reads the batch from the device arrays of
 ctx.inputs only, and everything it decides on the host (which kernels, how many blocks, buffer sizes) follows from the
@@ -53,11 +54,12 @@ class PartSpec:
 
 @dataclass
 class LayerSpec:
-    prefix: str                 # canonical tensor-name prefix of the layer, e.g. "blk.3."
-    block: str                  # block arrangement kind
-    norm: PartSpec
-    mixer: PartSpec
-    ffn: PartSpec
+    """One layer: the canonical tensor-name prefix of its tensors (e.g. "blk.3.") and its block arrangement, a
+    PartSpec whose parameters are the specs of the parts that arrangement puts together -- "prenorm" takes mixer, ffn
+    and norm (or norm1 and norm2 when the two differ); another arrangement (post-norms, mixer and feed-forward side by
+    side) is another block kind with the parts it needs."""
+    prefix: str
+    block: PartSpec
 
 
 @dataclass(frozen=True)

@@ -9,12 +9,13 @@ from .base import make, register
 
 class PreNormBlock:
     graph_safe = True       # forward() depends on the batch only through the lengths of the step's arrays
-    def __init__(self, layer):
-        p = layer.prefix
-        self.norm1 = make("norm", layer.norm, name=p + "attn_norm.weight")
-        self.mixer = make("mixer", layer.mixer, prefix=p)
-        self.norm2 = make("norm", layer.norm, name=p + "ffn_norm.weight")
-        self.ffn = make("feed_forward", layer.ffn, prefix=p)
+    def __init__(self, prefix, mixer, ffn, norm=None, norm1=None, norm2=None):
+        """mixer, ffn: part specs; norm: the spec of both norms, or norm1 / norm2 when they differ"""
+        p = prefix
+        self.norm1 = make("norm", norm1 or norm, name=p + "attn_norm.weight")
+        self.mixer = make("mixer", mixer, prefix=p)
+        self.norm2 = make("norm", norm2 or norm, name=p + "ffn_norm.weight")
+        self.ffn = make("feed_forward", ffn, prefix=p)
 
     def parts(self):
         return [self.norm1, self.mixer, self.norm2, self.ffn]

@@ -11,7 +11,7 @@ from mashbox_b200.errors import CacheError
 
 
 def manager(pages=12, page=4, requests=4, window=10, context=0):
-    needs = {0: CacheNeed("full", 2, 16), 1: CacheNeed("window", 2, 16, window), 2: CacheNeed("full", 2, 16), 3: None}
+    needs = {0: CacheNeed.keys_and_values(2, 16), 1: CacheNeed.keys_and_values(2, 16, window), 2: CacheNeed.keys_and_values(2, 16), 3: None}
     return CacheManager(needs, {3: StateNeed((5,), "float32")}, page, pages, requests, context)
 
 

@@ -68,6 +68,8 @@ def test_model_spec_is_data():
     spec = model_spec(H.TINY_B)
     assert len(spec.layers) == 3 and [r.layer for r in spec.schedule] == [0, 1, 2]
     assert all(r.cache == r.layer and r.write for r in spec.schedule)
-    m = spec.layers[1].mixer
+    b = spec.layers[1].block
+    assert b.kind == "prenorm" and b.params["norm"].params["eps"] == 1e-6
+    m = b.params["mixer"]
     assert m.kind == "attention" and m.params["heads"] == 6 and m.params["kv_heads"] == 1 and m.params["head_dim"] == 32
-    assert m.params["position"].kind == "rope" and spec.layers[1].ffn.params["intermediate"] == 320
+    assert m.params["position"].kind == "rope" and b.params["ffn"].params["intermediate"] == 320

@@ -310,3 +310,48 @@ def test_command_line_with_a_tokenizer(tmp_path):
     os.remove(os.path.join(folder, "tokenizer.json"))
     r = subprocess.run(cmd, capture_output=True, text=True, env=env, timeout=600)
     assert r.returncode == 2 and "tokenizer.json" in r.stderr
+
+
+@pytest.mark.parametrize("where", ["launch", "wait", "prepare"])
+def test_a_step_that_fails_on_the_host_ends_every_live_request_and_leaves_the_engine_usable(tmp_path_factory, where,
+                                                                                             monkeypatch):
+    """The failure is made on the host (a patched method raises on its n-th call); nothing on the GPU faults.  Three
+    requests are live and a step is in flight when it happens.  Every live request ends "error" with the reason,
+    no request keeps a placeholder among its ids, the step in flight is forgotten, every page, row and state slot is
+    back, and the next generate() gives the answers of an engine that never failed
+    (the reference drops its live rows after a failed device call, src/mashbox/runtime/engine.py:752-762)."""
+    from mashbox_b200.engine.runner import ModelRunner
+    from mashbox_b200.sampling.sampler import Sampler
+    folder, eng = engine(tmp_path_factory.mktemp("m"), "A", "f32", chunk=16, max_tokens_per_step=24)
+    prompts = H.prompts_for("A", (30, 9, 21), seed=9)
+    want = eng.generate(prompts, max_new=3 if where != "wait" else 12)
+    target = {"launch": (ModelRunner, "launch"), "wait": (Sampler, "wait"), "prepare": (ModelRunner, "prepare")}[where]
+    original = getattr(*target)
+    calls = {"n": 0}
+
+    def failing(self, *a, **kw):
+        calls["n"] += 1
+        if calls["n"] == 5:
+            raise RuntimeError("injected on the host")
+        return original(self, *a, **kw)
+
+    monkeypatch.setattr(target[0], target[1], failing)
+    rows = eng.admit([dict(ids=p, max_new=3 if i == 1 and where != "wait" else 12) for i, p in enumerate(prompts)])
+    with pytest.raises(RuntimeError, match="injected on the host"):
+        while eng.busy():
+            eng.step()
+    monkeypatch.setattr(target[0], target[1], original)
+    assert calls["n"] == 5
+    assert not eng.busy() and eng._flight is None
+    assert all(r.finish in ("error", "length") for r in rows) and sum(r.finish == "error" for r in rows) >= 2
+    for r in rows:
+        assert eng.PLACEHOLDER not in r.generated
+        if r.finish == "error":
+            assert "injected on the host" in r.error
+        else:
+            assert len(r.generated) == r.max_new
+    eng.cache.check()
+    assert eng.cache.free_pages() == [eng.cache.num_pages] and eng.cache.rows.n_free == eng.cache.max_requests
+    assert not eng.scheduler.running and not eng.scheduler.waiting
+    again = eng.generate(prompts, max_new=3 if where != "wait" else 12)
+    assert again["ids"] == want["ids"] and again["finish"] == want["finish"]

@@ -245,7 +245,7 @@ def toy_architecture():
                                    position=pos)
         mixers = [att(rope), PartSpec("running_mean", hidden=c.hidden), att(None)]
         return ModelSpec(hidden=c.hidden, vocab=c.vocab, embedding=PartSpec("table", vocab=c.vocab, hidden=c.hidden),
-                         layers=[LayerSpec(prefix=f"blk.{i}.", block="prenorm", norm=norm, mixer=m, ffn=ffn)
+                         layers=[LayerSpec(prefix=f"blk.{i}.", block=PartSpec("prenorm", norm=norm, mixer=m, ffn=ffn))
                                  for i, m in enumerate(mixers)],
                          schedule=[LayerRun(layer=l, cache=ca, write=bool(w)) for l, ca, w in c.order],
                          final_norm=PartSpec("rms", width=c.hidden, eps=c.eps, name="output_norm.weight"),

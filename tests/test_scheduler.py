@@ -9,7 +9,7 @@ from mashbox_b200.errors import RequestError
 
 
 def make(pages=16, page=4, requests=4, budget=16, chunk=8, vocab=100, context=0):
-    cache = CacheManager({0: CacheNeed("full", 1, 16)}, {}, page, pages, requests, context)
+    cache = CacheManager({0: CacheNeed.keys_and_values(1, 16)}, {}, page, pages, requests, context)
     return cache, Scheduler(cache, vocab, max_tokens_per_step=budget, chunk=chunk)
 
 
@@ -148,3 +148,96 @@ def test_random_traffic_always_finishes_and_frees_everything(seed):
         assert 3 not in r.generated
     cache.check()
     assert cache.free_pages() == [cache.num_pages] and cache.rows.n_free == cache.max_requests
+
+
+def test_two_long_prompts_side_by_side_cannot_starve_each_other():
+    """budget > chunk: two prompts that each fit the pool alone were once admitted together, shrank each other to
+    nothing and left an empty plan.  Pages a running prompt still has to take are now set aside before anyone is let in."""
+    cache, s = make(pages=25, page=4, requests=4, budget=64, chunk=32)
+    a = s.add("a", list(range(80)), 4)
+    b = s.add("b", list(range(60)), 4)
+    steps = 0
+    while s.busy():
+        plan, _ = run_step(cache, s)
+        assert plan, (steps, [(r.rid, r.computed) for r in s.running], cache.free_pages())
+        if steps == 0:
+            assert [p.request.rid for p in plan] == ["a"] and b in s.waiting      # 21 + 16 pages do not fit 25
+        steps += 1
+        assert steps < 100
+    assert a.finish == b.finish == "length" and s.stats["preemptions"] == 0
+    assert cache.free_pages() == [25]
+
+
+def test_nothing_can_run_while_requests_are_live_the_newest_gives_way():
+    """a state the admission rule keeps from arising is still resolved: pages taken behind the scheduler's back leave
+    two running prompts with no room; the newest is preempted and the other goes on"""
+    cache, s = make(pages=10, page=4, requests=4, budget=64, chunk=8)
+    a = s.add("a", list(range(20)), 2)
+    run_step(cache, s)
+    b = s.add("b", list(range(8)), 2)
+    run_step(cache, s)
+    assert a in s.running and b in s.running
+    cache.admit("thief")
+    cache.extend("thief", cache.free_pages()[0] * 4)
+    plan = s.plan()
+    assert b in s.waiting and b.preemptions == 1 and [p.request.rid for p in plan] == ["a"]
+
+
+def test_portions_end_on_the_grid():
+    cache = CacheManager({0: CacheNeed.keys_and_values(1, 16)}, {}, 4, 64, 4, 0)
+    s = Scheduler(cache, 100, max_tokens_per_step=24, chunk=20, align=8)
+    a = s.add("a", list(range(43)), 2)
+    b = s.add("b", list(range(11)), 2)
+    seen = {"a": [], "b": []}
+    while s.busy():
+        plan = s.plan()
+        assert plan
+        for p in plan:
+            seen[p.request.rid].append((p.start, p.count))
+            end = p.start + p.count
+            assert end % 8 == 0 or end == len(p.request.tokens), (p.request.rid, p.start, p.count)
+            cache.extend(p.request.rid, p.count)
+            cache.commit(p.request.rid, p.count)
+        s.advance(plan, [7 for p in plan if p.sample])
+    assert seen["a"][:3] == [(0, 16), (16, 16), (32, 11)]           # 20 -> 16: the cut falls back to the grid
+    assert seen["b"][0] == (0, 8)                                    # 24 - 16 = 8 tokens of budget left: one block
+    with pytest.raises(RequestError, match="multiples of 8"):
+        Scheduler(cache, 100, max_tokens_per_step=24, chunk=4, align=8)
+
+
+def test_a_window_group_is_not_charged_for_pages_it_gives_back():
+    """a long prompt in a pool whose window group could never hold all of it: admitted, because behind the window the
+    pages come back at every commit"""
+    needs = {0: CacheNeed.keys_and_values(1, 16), 1: CacheNeed.keys_and_values(1, 16, 6)}
+    cache = CacheManager(needs, {}, 4, 40, 4, 0)
+    assert cache.pages_to_hold(100, 8) == [25, 5]
+    s = Scheduler(cache, 100, max_tokens_per_step=8, chunk=8)
+    a = s.add("a", list(range(100)), 3)
+    peak = 0
+    while s.busy():
+        plan, _ = run_step(cache, s)
+        assert plan
+        peak = max(peak, 40 - cache.free_pages()[1])
+    assert a.finish == "length" and peak <= 5
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_traffic_with_long_prompts_and_a_budget_over_the_chunk(seed):
+    rng = random.Random(100 + seed)
+    page = rng.choice([2, 4])
+    cache, s = make(pages=rng.choice([12, 20, 30]), page=page, requests=rng.choice([2, 3, 5]),
+                    budget=rng.choice([24, 40, 64]), chunk=rng.choice([4, 8, 16]))
+    cap = s.capacity()
+    reqs, steps = [], 0
+    while steps < 4000 and (s.busy() or len(reqs) < 25):
+        if len(reqs) < 25 and rng.random() < 0.4:
+            n = rng.randrange(1, cap - 1)
+            mx = rng.randrange(1, max(2, cap - n))
+            reqs.append((s.add(len(reqs), [rng.randrange(100) for _ in range(n)], mx), n, mx))
+        if s.busy():
+            plan, _ = run_step(cache, s, token=lambda r: rng.randrange(100))
+            assert plan, "the scheduler has requests but plans nothing"
+        steps += 1
+    assert not s.busy()
+    assert all(r.finish == "length" and len(r.generated) == mx for r, n, mx in reqs)
+    assert cache.free_pages() == [cache.num_pages]

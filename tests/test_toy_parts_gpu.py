@@ -109,13 +109,14 @@ def routed_architecture():
         norm = PartSpec("rms", width=c.hidden, eps=c.eps)
         att = lambda pos: PartSpec("attention", hidden=c.hidden, heads=c.heads, kv_heads=c.kv_heads,
                                    head_dim=c.head_dim, position=pos)
-        layers = [LayerSpec(prefix="blk.0.", block="prenorm", norm=norm,
-                            mixer=att(PartSpec("learned_shift", head_dim=c.head_dim, prefix="blk.0.")),
-                            ffn=PartSpec("top_one_experts", hidden=c.hidden, intermediate=c.inner, experts=c.experts)),
-                  LayerSpec(prefix="blk.1.", block="prenorm", norm=norm,
-                            mixer=att(PartSpec("rope", head_dim=c.head_dim, rotary_dim=c.head_dim // 2, theta=500.0,
-                                               pairing="halves")),
-                            ffn=PartSpec("swiglu", hidden=c.hidden, intermediate=c.inner))]
+        layers = [LayerSpec(prefix="blk.0.", block=PartSpec(
+                      "prenorm", norm=norm, mixer=att(PartSpec("learned_shift", head_dim=c.head_dim, prefix="blk.0.")),
+                      ffn=PartSpec("top_one_experts", hidden=c.hidden, intermediate=c.inner, experts=c.experts))),
+                  LayerSpec(prefix="blk.1.", block=PartSpec(
+                      "prenorm", norm=norm,
+                      mixer=att(PartSpec("rope", head_dim=c.head_dim, rotary_dim=c.head_dim // 2, theta=500.0,
+                                         pairing="halves")),
+                      ffn=PartSpec("swiglu", hidden=c.hidden, intermediate=c.inner)))]
         return ModelSpec(hidden=c.hidden, vocab=c.vocab, embedding=PartSpec("table", vocab=c.vocab, hidden=c.hidden),
                          layers=layers, schedule=[LayerRun(layer=i, cache=i, write=True) for i in range(2)],
                          final_norm=PartSpec("rms", width=c.hidden, eps=c.eps, name="output_norm.weight"),

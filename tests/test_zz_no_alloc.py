@@ -6,7 +6,8 @@ manager.  For them the sampling kernel's scratch lives in a fixed 2 MiB array in
 the exported C symbol directly (ctypes, raw pointers), twice in a row so that the second call finds the first one's
 scratch, and checks each result against the ordinary entry point, which takes its scratch from the caller: the tokens
 must be equal, as everywhere in the sampling tests.  It also checks that sizes beyond the fixed array are refused with
-words, and that the call leaves torch's allocator untouched.
+words, and that the device's free memory (as the driver reports it, whoever allocates) does not change over a call
+once the library's image, with its fixed array, has been loaded by the first call.
 """
 import ctypes
 
@@ -47,7 +48,7 @@ def test_no_alloc_sampling_equals_the_ordinary_entry_point_twice_in_a_row():
         (1009, [dict(temperature=0.9, top_k=50, seed=1), dict(), dict(temperature=1.2, top_p=0.7, seed=2, step=3),
                 dict(temperature=0.8, min_p=0.1, rep=1.3, slot=1, seed=4)]),
         (257, [dict(temperature=0.5, top_k=3, top_p=0.9, seed=9, step=1), dict(temperature=1.0, seed=5)])]
-    for vocab, rows in calls:
+    for call, (vocab, rows) in enumerate(calls):
         n = len(rows)
         logits = (3 * torch.randn(n, vocab, generator=g)).to(DEV)
         params = pack(rows)
@@ -61,12 +62,15 @@ def test_no_alloc_sampling_equals_the_ordinary_entry_point_twice_in_a_row():
         K.sample(logits, torch.empty(n, vocab, device=DEV), params, cnt_a, seen_a, n, want)
         got = torch.full((n,), -1, dtype=torch.int32, device=DEV)
         torch.cuda.synchronize()
-        before = torch.cuda.memory_allocated()
+        before = torch.cuda.mem_get_info()[0]       # the driver's count: a cudaMalloc by anyone would show here
         rc = lib.mb_sample_noalloc(logits.data_ptr(), params.data_ptr(), cnt_b.data_ptr(), seen_b.data_ptr(), n, vocab,
                                    got.data_ptr(), stream)
         assert rc == 0, lib.mb_noalloc_strerror(rc)
         torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated() == before
+        # The first call on a device is when the driver loads the library's image, the fixed 2 MiB array included;
+        # from then on a call changes nothing.
+        spent = before - torch.cuda.mem_get_info()[0]
+        assert spent == 0 if call else 0 <= spent <= 8 << 20, spent
         assert got.tolist() == want.tolist()
         assert torch.equal(cnt_a, cnt_b) and torch.equal(seen_a, seen_b)
 
@@ -82,3 +86,5 @@ def test_no_alloc_sampling_refuses_what_does_not_fit():
     assert too_many == too_wide == -3 and b"beyond the fixed scratch" in lib.mb_noalloc_strerror(too_many)
     assert lib.mb_sample_noalloc(None, params.data_ptr(), None, None, 1, 16, out.data_ptr(), None) == -4
     assert b"null pointer" in lib.mb_noalloc_strerror(-4)
+    cnt = torch.zeros(2, 16, dtype=torch.int32, device=DEV)
+    assert lib.mb_sample_noalloc(x.data_ptr(), params.data_ptr(), cnt.data_ptr(), None, 1, 16, out.data_ptr(), None) == -4
