@@ -29,7 +29,12 @@ class _Flight:
 
 
 class Engine:
-    def __init__(self, model, engine_config=None, options=None, log=None):
+    def __init__(self, model, engine_config=None, options=None, log=None, trace=None):
+        """trace: record per generated token the order-independent hash of its logits and the gap between the two
+        largest (generate() then returns them under "lh"); None reads MASHBOX_TRACE=1 from the environment, as the
+        reference does (src/mashbox/cli.py:1062, src/mashbox/runtime/engine.py:80-89, 253-262)."""
+        import os
+        self.trace = bool(trace) if trace is not None else os.environ.get("MASHBOX_TRACE") == "1"
         self.cfg = engine_config or EngineConfig()
         self.model = model
         self.runner = ModelRunner(model, self.cfg, options)
@@ -43,20 +48,22 @@ class Engine:
         self.stats = dict(steps=0, prompt_tokens=0, generated_tokens=0, deferred=0)
 
     @classmethod
-    def from_folder(cls, folder, dtype="bfloat16", device="cuda:0", options=None, log=None, **engine_options):
+    def from_folder(cls, folder, dtype="bfloat16", device="cuda:0", options=None, log=None, trace=None,
+                    **engine_options):
         cfg = EngineConfig(dtype=dtype, device=device, **engine_options)
         model = load_model(folder, dtype=cfg.dtype, device=device, log=log)
-        return cls(model, cfg, options, log)
+        return cls(model, cfg, options, log, trace)
 
     @classmethod
-    def from_config(cls, config, source, dtype="bfloat16", device="cuda:0", options=None, log=None, **engine_options):
+    def from_config(cls, config, source, dtype="bfloat16", device="cuda:0", options=None, log=None, trace=None,
+                    **engine_options):
         """config: an architecture's typed configuration; source: a TensorSource with its tensors (for instance
         weights.random_init.RandomSource)."""
         from .. import ops
         from .loading import build_model
         cfg = EngineConfig(dtype=dtype, device=device, **engine_options)
         model = build_model(config.to_hf(), source, cfg.dtype, device, ops=ops, log=log)
-        return cls(model, cfg, options, log)
+        return cls(model, cfg, options, log, trace)
 
     # -------------------------------------------------------------------------------------------- low level
     def check(self, q):
@@ -143,7 +150,7 @@ class Engine:
                 self.sampler.start_row(slot, r.prompt, r.generated)
             r.needs_penalty_start = False
         params = self.runner.inputs.get("sample_rows") if self.runner.inputs.has("sample_rows") else None
-        pending = self.sampler.sample_async(logits, rows, self.runner.err, params)
+        pending = self.sampler.sample_async(logits, rows, self.runner.err, params, trace=self.trace)
         ended = self.scheduler.advance(plan, [self.PLACEHOLDER] * len(picks))
         return _Flight(plan, picks, [len(p.request.generated) - 1 for p in picks], pending, ended)
 
@@ -176,7 +183,8 @@ class Engine:
         self._flight = nxt
         now = time.perf_counter()
         ended = list(cur.ended)
-        for p, i, t in zip(cur.picks, cur.index, tokens):
+        traced = self.sampler.trace_of(cur.pending) if self.trace and cur.pending is not None else None
+        for j, (p, i, t) in enumerate(zip(cur.picks, cur.index, tokens)):
             r = p.request
             if r.finish not in (None, "length") or i >= len(r.generated):
                 continue                        # cancelled or stopped since the step was queued: the token is dropped
@@ -191,6 +199,8 @@ class Engine:
                     r.finish = "stop"           # it had also reached max_new: the stop token wins, as in the reference
                 continue
             r.generated[i] = t
+            if traced is not None:
+                r.lh.append(traced[j])
         for r in ended:
             r.t_end = now
         self.stats["steps"] += 1
@@ -221,7 +231,7 @@ class Engine:
     # -------------------------------------------------------------------------------------------- generate
     def generate(self, prompts, max_new=128, stop_ids=(), samp=None, on_step=None):
         """prompts: lists of token ids.  -> dict(ids, finish, timing{prefill_s, decode_s, decode_calls, new_tokens,
-        sampled}).  on_step(ids, finish) is called after every step and may return indexes of prompts to cancel."""
+        sampled}[, lh]).  on_step(ids, finish) is called after every step and may return indexes of prompts to cancel."""
         n = len(prompts)
         if n < 1:
             raise ValueError("1 or more prompts per call")
@@ -244,8 +254,11 @@ class Engine:
                 self.cancel([rows[i] for i in on_step(seen, [r.finish for r in rows]) or ()])
         t2 = time.perf_counter()
         t1 = max([r.t_first for r in rows if r.t_first is not None] or [t2])
-        return dict(ids=[list(r.generated) for r in rows], finish=[r.finish for r in rows],
-                    preemptions=[r.preemptions for r in rows],
-                    timing=dict(prefill_s=t1 - t0, decode_s=t2 - t1, decode_calls=calls,
-                                new_tokens=sum(len(r.generated) for r in rows),
-                                sampled=any(not r.sampling.greedy for r in rows)))
+        out = dict(ids=[list(r.generated) for r in rows], finish=[r.finish for r in rows],
+                   preemptions=[r.preemptions for r in rows],
+                   timing=dict(prefill_s=t1 - t0, decode_s=t2 - t1, decode_calls=calls,
+                               new_tokens=sum(len(r.generated) for r in rows),
+                               sampled=any(not r.sampling.greedy for r in rows)))
+        if self.trace:
+            out["lh"] = [list(r.lh) for r in rows]         # (hash, top-2 gap) per generated token
+        return out

@@ -8,7 +8,10 @@ forward pass, cache or loader of its own.  Steps come as JSON lines:
 `entries`: each request's next tokens and the places among them whose logits are wanted; all entries of a step are one
 batch.  `end`: requests finished after the step; their pages are given back.  For a step that wants something the
 logits are written to <out>/<step>.f32 as little-endian float32 [wanted, vocab], in the order of the entries and of
-`want`; after every step a line `done <step>` is printed and flushed.
+`want`; after every step a line `done <step>` is printed and flushed.  With --trace a step that wants something
+also writes <out>/<step>.lh.json: per wanted row [hash, gap], the order-independent hash of the row's logits
+(sum of bits(lg[v]) * (2 v + 1) mod 2^32) and the gap between its two largest, computed on the device as
+mashbox-labs/mashbox traces them (src/mashbox/runtime/engine.py:80-89).
 """
 import json
 import os
@@ -31,7 +34,7 @@ def make_runner(model_dir, dtype, max_tokens, page_size=16, device="cuda:0", opt
     return ModelRunner(model, cfg, options)
 
 
-def run_step(runner, step, out_dir=None):
+def run_step(runner, step, out_dir=None, trace=False):
     """One step dict through the runner.  -> float32 CPU tensor [wanted, vocab] or None."""
     cache = runner.cache
     entries = []
@@ -41,8 +44,15 @@ def run_step(runner, step, out_dir=None):
             cache.admit(rid)
         entries.append((rid, [int(t) for t in e["tokens"]], [int(w) for w in e.get("want", [])]))
     logits = runner.step(entries) if entries else None
-    result = None
+    result = traced = None
     if logits is not None:
+        if trace:
+            import torch
+
+            from .. import ops
+            pairs = torch.empty((logits.shape[0], 2), dtype=torch.int32, device=logits.device)
+            ops.logit_trace(logits, pairs)
+            traced = ops.read_logit_trace(pairs)
         result = logits.detach().float().cpu()
     runner.check()
     for rid in step.get("end", []):
@@ -50,6 +60,9 @@ def run_step(runner, step, out_dir=None):
             cache.release(rid)
     if result is not None and out_dir is not None:
         result.numpy().astype("<f4").tofile(os.path.join(out_dir, f"{step['step']}.f32"))
+        if traced is not None:
+            with open(os.path.join(out_dir, f"{step['step']}.lh.json"), "w") as fh:
+                json.dump([[h, g] for h, g in traced], fh)
     return result
 
 
@@ -63,6 +76,8 @@ def main(argv=None):
     ap.add_argument("--max-tokens", required=True, type=int,
                     help="most tokens live requests hold at any time (each rounded up to a multiple of 64)")
     ap.add_argument("--page-size", type=int, default=16)
+    ap.add_argument("--trace", action="store_true",
+                    help="also write <step>.lh.json: [hash of the logits, gap between the two largest] per wanted row")
     a = ap.parse_args(argv)
     os.makedirs(a.out, exist_ok=True)
     print(f"trace_run: loading {a.model} ({a.dtype})", file=sys.stderr, flush=True)
@@ -73,6 +88,6 @@ def main(argv=None):
         if not line:
             continue
         step = json.loads(line)
-        run_step(runner, step, a.out)
+        run_step(runner, step, a.out, trace=a.trace)
         print(f"done {step['step']}", flush=True)
     return 0

@@ -40,6 +40,7 @@ class Request:
     sampling: SamplingParams = field(default_factory=SamplingParams)
     stop_ids: frozenset = frozenset()
     generated: list = field(default_factory=list)
+    lh: list = field(default_factory=list)      # with tracing on: (hash of the logits, top-2 gap) per generated token
     computed: int = 0
     finish: str = None
     error: str = None

@@ -573,3 +573,22 @@ def penalty_fill(cnt_row, seen_row, tokens, n_prompt, n_total, V):
     _cuda(cnt_row, seen_row, tokens)
     f = _fn("sampling", "mb_penalty_fill", [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
     _check(f(_p(cnt_row), _p(seen_row), _p(tokens), n_prompt, n_total, V, _stream()), "penalty_fill")
+
+
+# ------------------------------------------------------------------------------------------------ tracing
+def logit_trace(logits, out):
+    """logits (R, V) float32 contiguous -> out (R, 2) int32: per row the order-independent hash
+    sum(bits(lg[v]) * (2 v + 1)) mod 2^32 and the bits of the float32 gap between the two largest logits
+    (src/mashbox/runtime/engine.py:80-89)."""
+    _cuda(logits, out)
+    if logits.dtype != torch.float32 or not logits.is_contiguous():
+        raise KernelError("logit_trace: float32 contiguous logits only")
+    f = _fn("trace", "mb_logit_trace", [c_void_p, c_int, c_int, c_void_p, c_void_p])
+    _check(f(_p(logits), logits.shape[0], logits.shape[1], _p(out), _stream()), "logit_trace")
+
+
+def read_logit_trace(pairs):
+    """int32 (R, 2) as logit_trace writes it (any device or a numpy array) -> [(hash, gap)] with hash in 0..2^32-1"""
+    import numpy as np
+    a = np.ascontiguousarray(pairs.cpu().numpy() if hasattr(pairs, "cpu") else pairs, dtype=np.int32).reshape(-1, 2)
+    return [(int(h), float(g)) for h, g in zip(a[:, 0].view(np.uint32), a[:, 1].copy().view(np.float32))]

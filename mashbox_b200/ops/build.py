@@ -36,6 +36,7 @@ LIBRARIES = {            # library name -> (source file, extra compiler flags)
     "attention_tc5": ("attention_tc5.cu", []),
     "sampling": ("sampling.cu", []),
     "sampling_noalloc": ("sampling_noalloc.cu", []),
+    "trace": ("trace.cu", []),
 }
 EXTRA_SOURCES = {"sampling_noalloc": ["sampling.cu", "sampling_noalloc.h"]}      # files a library includes
 _loaded = {}
@@ -135,6 +136,18 @@ def load_library(name):
                 raise KernelError(f"cannot load {path}: {e}") from None
             _loaded[name] = lib
         return lib
+
+
+def prune():
+    """Removes libraries in the build folder that no current source hashes to (left by earlier versions of a file)."""
+    d = build_dir()
+    current = {os.path.basename(library_path(n)) for n in LIBRARIES}
+    for f in os.listdir(d):
+        if f.startswith("libmashbox_b200_") and f.endswith(".so") and f not in current:
+            try:
+                os.remove(os.path.join(d, f))
+            except OSError:
+                pass
 
 
 def build_all(verbose=True):

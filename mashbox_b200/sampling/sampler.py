@@ -55,15 +55,16 @@ class Sampler:
                          (p.seed >> 32) & 0xFFFFFFFF, step, i)
         return packed.view(np.int32)
 
-    def sample_async(self, logits, rows, err=None, params=None):
+    def sample_async(self, logits, rows, err=None, params=None, trace=False):
         """Launches the sampling kernels and starts the copy of the ids (and of the kernels' error word, when given)
         to pinned host memory.  -> a handle for wait().  params: pack(rows) already on the device (the engine sends it
-        with the step's arrays; a copy from pageable memory here would make the host wait for the GPU)."""
+        with the step's arrays; a copy from pageable memory here would make the host wait for the GPU).  trace: the
+        hash of every row's logits and the gap between its two largest travel with the ids (trace_of())."""
         n = len(rows)
         if n == 0:
             return None
-        if self.ret is None or self.ret.shape[0] < n + 1:
-            cap = max(n, self.max_slots) + 1
+        if self.ret is None or self.ret.shape[0] < 3 * n + 1:
+            cap = 3 * max(n, self.max_slots) + 1            # ids | error word | (hash, gap) per row
             self.ret = torch.empty(cap, dtype=torch.int32, device=self.device)
             self.host = [torch.empty(cap, dtype=torch.int32).pin_memory() for _ in range(2)]
             self.turn = 0
@@ -81,18 +82,28 @@ class Sampler:
             kernels.sample(logits, self.work, params, self.cnt, self.seen, n, out, any_cut=cuts, keep_work=False)
         if err is not None:
             self.ret[n:n + 1].copy_(err)
+        size = n + 1
+        if trace:
+            kernels.logit_trace(logits[:n], self.ret[n + 1:3 * n + 1].view(n, 2))
+            size = 3 * n + 1
         self.turn ^= 1
         host = self.host[self.turn]
-        host[:n + 1].copy_(self.ret[:n + 1], non_blocking=True)
+        host[:size].copy_(self.ret[:size], non_blocking=True)
         ev = torch.cuda.Event()
         ev.record()
-        return host, n, ev, err
+        return host, n, ev, err, trace
+
+    @staticmethod
+    def trace_of(pending):
+        """-> [(hash, gap)] per row of a step sampled with trace=True, after wait()"""
+        host, n, _, _, trace = pending
+        return kernels.read_logit_trace(host[n + 1:3 * n + 1].numpy()) if trace else None
 
     def wait(self, pending):
         """-> the token ids of sample_async (raises when a kernel of the step left an error code)"""
         if pending is None:
             return []
-        host, n, ev, err = pending
+        host, n, ev, err, _ = pending
         ev.synchronize()
         vals = host[:n + 1].tolist()
         if err is not None and vals[n]:

@@ -355,3 +355,30 @@ def test_a_step_that_fails_on_the_host_ends_every_live_request_and_leaves_the_en
     assert not eng.scheduler.running and not eng.scheduler.waiting
     again = eng.generate(prompts, max_new=3 if where != "wait" else 12)
     assert again["ids"] == want["ids"] and again["finish"] == want["finish"]
+
+
+def test_traced_generation_gives_the_same_hashes_alone_and_batched(tmp_path_factory):
+    """trace=True: generate() returns per generated token the hash of its logits and the top-2 gap.  On the 32-bit path
+    a request's hashes are the same alone, in a batch of four with prompt portions beside decoded tokens, and after a
+    preemption: the logits are bit-identical, not merely close."""
+    from mashbox_b200.engine.engine import Engine
+    tmp = tmp_path_factory.mktemp("m")
+    folder = H.make_folder(tmp, "B", "float32")
+    prompts = H.prompts_for("B", (5, 40, 130, 61), seed=12)
+    make = lambda tokens, **kw: Engine.from_folder(folder, dtype="float32", page_size=8, max_tokens=tokens, max_requests=4,
+                                                   chunk=32, max_tokens_per_step=40, trace=True, **kw)
+    eng = make(1024)
+    batched = eng.generate(prompts, max_new=20)
+    assert [len(x) for x in batched["lh"]] == [20] * 4
+    assert all(isinstance(h, int) and 0 <= h < 1 << 32 and g >= 0.0 for row in batched["lh"] for h, g in row)
+    for i, p in enumerate(prompts):
+        alone = eng.generate([p], max_new=20)
+        assert alone["ids"][0] == batched["ids"][i]
+        assert alone["lh"][0] == batched["lh"][i], f"request {i}: logits differ in some bit between alone and batched"
+    tight = make(264)                                                  # 4 requests of up to 150 tokens do not fit
+    squeezed = tight.generate(prompts, max_new=20)
+    assert sum(squeezed["preemptions"]) > 0
+    assert squeezed["lh"] == batched["lh"] and squeezed["ids"] == batched["ids"]
+    # without tracing the result has no "lh" key
+    folder2, plain_eng = engine(tmp, "A", "f32")
+    assert "lh" not in plain_eng.generate(H.prompts_for("A", (7,)), max_new=2)

@@ -652,3 +652,29 @@ def test_matrix_vector_product(N, M, K):
     close(act, gt * torch.sigmoid(gt) * up, torch.bfloat16, "matrix-vector fused SwiGLU")
     with pytest.raises(Exception, match="does not take these sizes"):
         K_.linear_gemv(torch.zeros(5, K, device=G.DEV, dtype=torch.bfloat16), w, torch.empty(5, M, device=G.DEV, dtype=torch.bfloat16))
+
+
+@pytest.mark.parametrize("V", [1, 2, 509, 4096, 128256])
+def test_logit_trace_hash_and_gap(V):
+    """the order-independent hash sum(bits(lg[v]) * (2 v + 1)) mod 2^32 and the float32 gap between the two largest
+    logits of every row (src/mashbox/runtime/engine.py:80-89), against numpy: equal, not close"""
+    from tests.test_replay_gpu import np_logit_hash
+    K, DEV = ops(), G.DEV
+    g = torch.Generator().manual_seed(V)
+    lg = (4 * torch.randn(5, V, generator=g)).float()
+    if V >= 2:
+        lg[1, V // 2] = lg[1].max() + 0.75                   # a clear winner
+        lg[2, 0] = lg[2, V - 1] = lg[2].max() + 1.0           # two equal maxima, at both ends: gap 0
+        lg[3, V - 1] = -0.0                                  # the sign bit of a zero counts in the hash
+        lg[4] = -lg[4].abs() - 1.0                           # all negative
+    out = torch.empty((5, 2), dtype=torch.int32, device=DEV)
+    K.logit_trace(lg.to(DEV), out)
+    got = K.read_logit_trace(out)
+    want = np_logit_hash(lg.numpy()) if V >= 2 else [(int(np.float32(x).view(np.uint32)), 0.0) for x in lg[:, 0].numpy()]
+    assert got == want
+    if V >= 2:
+        assert got[2][1] == 0.0 and abs(got[1][1] - 0.75) < 1e-5
+        flipped = lg.clone()
+        flipped[0, V // 3] = torch.nextafter(flipped[0, V // 3], torch.tensor(float("inf")))
+        K.logit_trace(flipped.to(DEV), out)
+        assert K.read_logit_trace(out)[0][0] != got[0][0]    # one changed bit changes the hash

@@ -142,3 +142,77 @@ def test_streaming_products_for_steps_of_few_tokens(tmp_path_factory, name):
         runner.cache.check()
     finally:
         ops.STREAM.update(before)
+
+
+def np_logit_hash(lg):
+    """sum over v of bits(lg[v]) * (2 v + 1) mod 2^32 (src/mashbox/runtime/engine.py:80-84) and the top-2 gap, per row"""
+    lg = np.ascontiguousarray(lg, np.float32)
+    u = lg.view(np.uint32).astype(np.uint64)
+    k = (2 * np.arange(lg.shape[1], dtype=np.uint64) + 1)
+    h = (u * k % (1 << 32)).sum(-1) % (1 << 32)
+    top = np.sort(lg, -1)[:, -2:]
+    return [(int(a), float(np.float32(t[1]) - np.float32(t[0]))) for a, t in zip(h, top)]
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_float32_logits_are_bit_identical_under_every_cut(tmp_path_factory, name):
+    """What the 32-bit path promises: the logits of a position are the same BITS whether the request ran whole, with its
+    last 32 tokens one by one, in portions of changing size down to two tokens, or mixed with other requests on pages
+    that were used before.  Every float32 kernel gives each output element one accumulator and a fixed order that does
+    not depend on the step (gemm_f32.cu, attention_simple.cu, the norm's fixed tree), so this is equality, not a bar.
+    The device-side logit hash must say the same."""
+    from mashbox_b200.engine.replay import run_step
+    tmp = tmp_path_factory.mktemp("m")
+    lengths = (50, 33, 64, 20, 61, 47, 9, 58)
+    prompts = H.prompts_for(name, lengths, seed=3)
+    folder, runner = runner_for(tmp, name, "f32", 4 * 64)
+    whole = [replay(runner, [dict(entries=[dict(id="w", tokens=p, want=list(range(len(p))))], end=["w"])])[0]
+             for p in prompts]
+    for p, w in zip(prompts, whole):                                     # beside the bar against the plain model
+        H.check(w, folder, p, "f32", "whole")
+    # last 32 one by one
+    for p, w in zip(prompts[:3], whole[:3]):
+        cut = max(1, len(p) - 32)
+        steps = [dict(entries=[dict(id="a", tokens=p[:cut], want=list(range(cut)))], end=[])]
+        steps += [dict(entries=[dict(id="a", tokens=[t], want=[0])], end=[]) for t in p[cut:]]
+        steps[-1]["end"] = ["a"]
+        out = replay(runner, steps)
+        assert np.array_equal(np.concatenate([out[i] for i in range(len(steps))]), w), "last 32 one by one"
+    # portions of changing size
+    p, w = prompts[2], whole[2]
+    at, steps = 0, []
+    for s in [2, 17, 3, 2, 31, 9]:
+        s = min(s, len(p) - at)
+        steps.append(dict(entries=[dict(id="a", tokens=p[at:at + s], want=list(range(s)))], end=[]))
+        at += s
+    assert at == len(p)
+    steps[-1]["end"] = ["a"]
+    out = replay(runner, steps)
+    assert np.array_equal(np.concatenate([out[i] for i in range(len(steps))]), w), "portions"
+    # mixed, up to four live, pages used again; the hash kernel on the same rows
+    steps, where = mixed_trace(prompts, np.random.default_rng(5))
+    out, hashes = {}, {}
+    for i, s in enumerate(steps):
+        r = run_step(runner, dict(s, step=i))
+        out[i] = r.numpy()
+    for i, (p, w) in enumerate(zip(prompts, whole)):
+        got = np.concatenate([out[s][o:o + n] for s, o, n in where[i]])
+        assert np.array_equal(got, w), f"mixed, request {i}"
+    runner.cache.check()
+    assert all(f == runner.cache.num_pages for f in runner.cache.free_pages())
+
+
+def test_trace_run_writes_the_logit_hash(tmp_path):
+    """replay with --trace: the device's hash and gap of every wanted row equal numpy's on the logits it wrote"""
+    import json
+
+    from mashbox_b200.engine.replay import run_step
+    folder, runner = runner_for(tmp_path, "B", "f32", 128)
+    p = H.prompts_for("B", (40,), seed=8)[0]
+    out = tmp_path / "out"
+    out.mkdir()
+    lg = run_step(runner, dict(step=3, entries=[dict(id="a", tokens=p, want=[0, 5, 39])], end=["a"]), str(out), trace=True)
+    lh = json.load(open(out / "3.lh.json"))
+    want = np_logit_hash(lg.numpy())
+    assert [(int(h), float(g)) for h, g in lh] == want
+    assert np.array_equal(np.fromfile(out / "3.f32", "<f4").reshape(3, -1), lg.numpy())
