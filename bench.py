@@ -3,6 +3,9 @@ weights at batch 8 and 8,192 tokens of context per request, with the 2,048-token
 decode at batch 1 and 64 on the same JSON line.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--batch B] [--context C] [--no-points]
+    python bench.py --workload 3b-serving   # 64 requests of mixed lengths through Engine.admit/step, Llama-3.2-3B shape
+    python bench.py --workload 1b-long      # 4 prompts of 32,768 tokens in 2,048-token portions, then 256 sampled steps
+    python bench.py --kernels               # single kernels against the library on the layer's shapes
     python bench.py --impl reference        # the reference arm (unavailable here: it needs JAX and a TPU)
 
 A "step" is one decode step of the whole batch.  `value` is timed on the device with CUDA events around K calls of the
@@ -22,7 +25,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
 def peaks():
@@ -30,7 +33,8 @@ def peaks():
     if os.path.isfile(p):
         try:
             d = json.load(open(p))
-            return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
+            return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                    "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained") or d["bf16_tflops"]), "source": "measured"}
         except Exception:
             pass
     return dict(FALLBACK_PEAKS)
@@ -149,8 +153,9 @@ def run_ours(a):
             pre_ms.append(e0.elapsed_time(e1))
     pre = statistics.median(pre_ms)
     pk = peaks()
-    prefill = {"value": P / (pre / 1e3), "tokens": P, "ms": pre,
-               "frac": flops_prefill(cfg, layers, P) / (pre / 1e3) / (pk["bf16_tflops"] * 1e12)}
+    tflops = flops_prefill(cfg, layers, P) / (pre / 1e3) / 1e12
+    prefill = {"value": P / (pre / 1e3), "tokens": P, "ms": pre, "frac": tflops / pk["bf16_tflops"],
+               "tflops": tflops, "frac_of_sustained": tflops / pk["bf16_tflops_sustained"]}
 
     # ---- decode
     def decode(batch, with_e2e):
@@ -203,11 +208,17 @@ def run_ours(a):
         eng.cancel(rows)
         return res
 
+    def roof(r):
+        gbs = bytes_decode(cfg, layers, r["batch"], r["kv_len"]) / (r["ms_per_step"] / 1e3) / 1e9
+        return {"ms_per_step": r["ms_per_step"], "mean_kv_len_timed": round(r["kv_len"], 1), "achieved_gbs": gbs,
+                "frac": gbs / pk["hbm_gbs"]}
+
     main = decode(a.batch, True)
-    points = {}
+    points, detail = {}, {}
     for b in batches[1:]:
-        points[f"decode_b{b}"] = decode(b, False)["value"]
-    points[f"decode_b{a.batch}"] = main["value"]
+        r = decode(b, False)
+        points[f"decode_b{b}"], detail[f"decode_b{b}"] = r["value"], roof(r)
+    points[f"decode_b{a.batch}"], detail[f"decode_b{a.batch}"] = main["value"], roof(main)
     clk = clocks.stop()
     nbytes = bytes_decode(cfg, layers, main["batch"], main["kv_len"])
     achieved = nbytes / (main["ms_per_step"] / 1e3) / 1e9
@@ -230,7 +241,128 @@ def run_ours(a):
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved / pk["hbm_gbs"]},
         "points": points,
+        "points_roofline": detail,
         "impl": "ours",
+    }
+    print(json.dumps(line))
+    return 0
+
+
+WORKLOADS = {
+    # BASELINE.json configs[3]: continuous batching of 64 requests, prompts U[128, 4096], outputs U[64, 512], greedy
+    "3b-serving": dict(model="llama-3.2-3b-shape", layers=28, hidden=3072, heads=24, kv_heads=8, head_dim=128,
+                       intermediate=8192, factor=32.0, requests=64, prompt=(128, 4096), new=(64, 512), temperature=0.0),
+    # BASELINE.json configs[4]: 4 prompts of 32,768 tokens in 2,048-token portions, then 256 steps at temperature 1.0
+    "1b-long": dict(model="llama-3.2-1b-shape", layers=16, hidden=2048, heads=32, kv_heads=8, head_dim=64,
+                    intermediate=8192, factor=32.0, requests=4, prompt=(32768, 32768), new=(256, 256), temperature=1.0),
+}
+
+
+def run_workload(a):
+    """A whole workload through the public entry point (Engine.admit / Engine.step, host token ids in, sampled ids read
+    back every step): one JSON line with total, prompt and generated tokens per second, what the scheduler and the
+    graph cache did, and how much of the wall time the GPU spent inside steps."""
+    import random
+
+    import torch
+    from mashbox_b200 import ops
+    from mashbox_b200.config.llama import LlamaConfig, RopeScaling
+    from mashbox_b200.config.registry import architecture
+    from mashbox_b200.engine.engine import Engine
+    from mashbox_b200.weights.random_init import RandomSource
+
+    w = WORKLOADS[a.workload]
+    torch.cuda.set_device(0)
+    dev = "cuda:0"
+    layers = a.layers or w["layers"]
+    cfg = LlamaConfig(architecture="LlamaForCausalLM", num_layers=layers, hidden=w["hidden"], num_heads=w["heads"],
+                      num_kv_heads=w["kv_heads"], head_dim=w["head_dim"], intermediate=w["intermediate"], vocab=128256,
+                      rms_eps=1e-5, rope_theta=500000.0, rope_scaling=RopeScaling("llama3", w["factor"], 1.0, 4.0, 8192),
+                      tie_embeddings=True, attention_bias=False, max_position=131072)
+    rng = random.Random(a.seed)
+    n_req = a.requests or w["requests"]
+    plens = [rng.randint(*w["prompt"]) for _ in range(n_req)]
+    news = [rng.randint(*w["new"]) for _ in range(n_req)]
+    per_request = max(p + n for p, n in zip(plens, news))
+    pool = a.pool_tokens or sum(-(-(p + n) // 64) * 64 for p, n in zip(plens, news)) + 4096
+    eng = Engine.from_config(cfg, RandomSource(architecture(cfg.architecture).stored_tensors(cfg), 0, torch.bfloat16, dev),
+                             dtype="bfloat16", device=dev, page_size=16, max_tokens=pool, max_requests=n_req,
+                             max_tokens_per_step=2048 + n_req, chunk=2048, max_context=-(-per_request // 64) * 64,
+                             cuda_graphs=not a.no_graphs, options=json.loads(a.options) if a.options else None)
+    gen = torch.Generator().manual_seed(a.seed)
+    prompts = [torch.randint(0, cfg.vocab, (n,), generator=gen).tolist() for n in plens]
+    samp = None if w["temperature"] == 0 else dict(temperature=w["temperature"], seed=a.seed)
+
+    # GPU time inside steps: an event before a step's first launch and one after its sampling kernels
+    spans = []
+    inner = eng._launch
+
+    def timed_launch(prep, before=None):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        f = inner(prep, before)
+        e1.record()
+        spans.append((e0, e1, sum(p.count for p in prep[0])))
+        return f
+
+    def once(timed):
+        spans.clear()
+        rows = eng.admit([dict(ids=p, max_new=n, samp=samp) for p, n in zip(prompts, news)])
+        l0 = ops.COUNTERS["launches"]
+        before = dict(eng.runner.stats), dict(eng.scheduler.stats)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        steps, t_first, new_at_first = 0, None, 0
+        while eng.busy():
+            eng.step()
+            steps += 1
+            if t_first is None and all(r.t_first is not None or r.finish is not None for r in rows):
+                t_first = time.perf_counter()
+                new_at_first = sum(len(r.generated) for r in rows)
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        gpu_ms = sum(e0.elapsed_time(e1) for e0, e1, _ in spans)
+        new = sum(len(r.generated) for r in rows)
+        assert all(r.finish == "length" for r in rows), [r.finish for r in rows]
+        rs, ss = eng.runner.stats, eng.scheduler.stats
+        return dict(wall_s=wall, steps=steps, new_tokens=new, prompt_tokens=sum(plens), gpu_ms_in_steps=gpu_ms,
+                    until_all_first_tokens_s=(t_first or t0 + wall) - t0, new_at_first=new_at_first,
+                    preemptions=ss["preemptions"] - before[1]["preemptions"],
+                    graph_captures=rs["graph_captures"] - before[0]["graph_captures"],
+                    graph_replays=rs["graph_replays"] - before[0]["graph_replays"],
+                    launches=ops.COUNTERS["launches"] - l0, deferred=eng.stats["deferred"])
+
+    eng._launch = timed_launch
+    clocks = Clocks()
+    if a.workload_warm:
+        once(False)                      # a first pass loads every kernel and captures the graphs of recurring shapes
+    clocks.start()
+    r = once(True)
+    clk = clocks.stop()
+    wall = r["wall_s"]
+    decode_s = wall - r["until_all_first_tokens_s"]
+    line = {
+        "metric": f"generated tokens/s, {a.workload} workload, {w['model']}, random bf16 weights",
+        "value": r["new_tokens"] / wall, "unit": "tokens/s", "n_gpus": 1, "steps": r["steps"], "warmup": int(a.workload_warm),
+        "ms_per_step": wall * 1e3 / r["steps"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: seeded random weights made on the GPU, seeded uniform random token ids and lengths",
+        "config": {"model": w["model"], "layers": layers, "layers_of_config": w["layers"], "hidden": cfg.hidden,
+                   "heads": cfg.num_heads, "kv_heads": cfg.num_kv_heads, "head_dim": cfg.head_dim,
+                   "intermediate": cfg.intermediate, "vocab": cfg.vocab, "requests": n_req,
+                   "prompt_tokens": r["prompt_tokens"], "new_tokens": r["new_tokens"], "temperature": w["temperature"],
+                   "pool_tokens": pool, "page_size": 16, "chunk": 2048, "seed": a.seed,
+                   "cuda_graphs": bool(eng.runner.use_graphs), "parallelism": "single-gpu"},
+        "clocks": clk,
+        "workload": {"wall_s": wall, "total_tokens_per_s": (r["prompt_tokens"] + r["new_tokens"]) / wall,
+                     "prompt_tokens_per_s_until_all_first_tokens": r["prompt_tokens"] / r["until_all_first_tokens_s"],
+                     "generated_tokens_per_s_after_that": (None if decode_s <= 0 else
+                                                           (r["new_tokens"] - r["new_at_first"]) / decode_s),
+                     "until_all_first_tokens_s": r["until_all_first_tokens_s"],
+                     "preemptions": r["preemptions"], "graph_captures": r["graph_captures"],
+                     "graph_replays": r["graph_replays"], "steps_deferred": r["deferred"],
+                     "gpu_s_inside_steps": r["gpu_ms_in_steps"] / 1e3,
+                     "share_of_wall_outside_steps": 1.0 - r["gpu_ms_in_steps"] / 1e3 / wall},
+        "gpu_launches": r["launches"], "impl": "ours",
     }
     print(json.dumps(line))
     return 0
@@ -357,6 +489,12 @@ def main():
     ap.add_argument("--no-graphs", action="store_true", help="launch every kernel directly (for profilers)")
     ap.add_argument("--options", default="", help="JSON of engine options (kernel choices), for experiments")
     ap.add_argument("--kernels", action="store_true", help="time single kernels against the library instead of the model")
+    ap.add_argument("--workload", default="", choices=("", "3b-serving", "1b-long"),
+                    help="run one of the other workloads of the baseline through Engine.admit/step instead")
+    ap.add_argument("--requests", type=int, default=0, help="workloads: fewer requests than the workload names")
+    ap.add_argument("--pool-tokens", type=int, default=0, help="workloads: size of the cache pool (0: every request fits)")
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--workload-warm", type=int, default=1, help="workloads: run the workload once untimed first")
     a = ap.parse_args()
     if a.impl == "reference":
         return run_reference(a)
@@ -365,6 +503,8 @@ def main():
             print(f"bench.py: this engine runs on ONE GPU; --gpus {a.gpus} is not measured")
         return 2
     a.warmup = max(a.warmup, 3)
+    if a.workload:
+        return run_workload(a)
     return run_kernels(a) if a.kernels else run_ours(a)
 
 

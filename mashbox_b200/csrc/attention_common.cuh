@@ -3,8 +3,6 @@
 #pragma once
 #include "common.cuh"
 
-typedef __nv_bfloat16 bf16;
-
 struct AttnParams {
     const bf16* q; int q_stride;            // q[n * q_stride + h * HD + d]
     bf16* out;                              // out[n * H * HD + h * HD + d]
@@ -20,8 +18,6 @@ struct AttnParams {
     float scale_log2;
     int* err;
 };
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, int bytes) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(dst)), "l"(src), "r"(bytes));
@@ -41,10 +37,6 @@ __device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], 
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<uint32_t*>(&v);
 }
 
 // Rows of a tile in shared memory hold HD bf16 values in 16-byte chunks, swizzled against bank conflicts by XOR with

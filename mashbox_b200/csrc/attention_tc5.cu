@@ -1,115 +1,37 @@
-// Paged flash attention for prompt portions on the 5th-generation tensor cores (head size 128).
+// Paged flash attention for prompt portions on the 5th-generation tensor cores, head sizes 64 and 128.
 //
-// One block works on 128 packed query rows -- (token, head-in-group) of one sequence and one kv head -- against the keys
-// up to the last row's position, 128 keys at a time:
-//   warp 0     producer: walks the block table and brings each K and V tile in with one cp.async.bulk.tensor.2d per
-//              page and 64-column half (128-byte swizzle), two stages;
-//   warp 1     one thread issues the products: S = Q K^T (tcgen05.mma, M = 128 rows, N = 128 keys, 8 k-steps over the
-//              head) into one of two score buffers in tensor memory, and O += P V (M = 128 rows, N = 128 head columns,
-//              8 k-steps over the keys; V is the MN-major operand, read as the TMA laid it out).  The score product of
-//              the next tile is issued before the softmax of the current one is done.
-//   warps 2-5  softmax: thread = row.  tcgen05.ld brings the row's 128 scores; maximum and sum need no shuffle; the
-//              probabilities are written as bf16 into shared memory in the swizzled K-major layout the next product
-//              reads.  The output accumulator stays in tensor memory over all tiles; a row rescales its own lane of
-//              it (tcgen05.ld / tcgen05.st) only when its running maximum moved.  At the end the row is normalised
-//              and written.
-// Softmax, scale and running sums are float32.  Waits on mbarriers are bounded; every role reaches the common exit,
-// where the tensor memory is given back.  Page sizes 8..128 (powers of two); other sizes go to the mma.sync kernels.
-#include <cuda.h>
+// A work unit is 256 packed query rows -- (token, head-in-group) of one sequence and one kv head -- as TWO query tiles
+// of 128 rows that share the K and V tiles, against the keys up to the last row's position, 128 keys at a time.  A
+// block of 384 threads walks a static list of units (sorted heaviest first, dealt back and forth over the blocks):
+//   warps 0-3, 4-7  softmax, one warpgroup per query tile, thread = row.  tcgen05.ld brings the row's 128 scores with one
+//              wait; maximum and sum need no shuffle; the probabilities go back as bf16 pairs into the first 64 columns
+//              of their own scores in tensor memory, where the output product reads them as its A operand.  The output
+//              accumulator stays in tensor memory over all tiles; a row rescales its lane of it (tcgen05.ld / st) only
+//              when its running maximum has grown by more than 8.  At the end the row is normalised and written.  The
+//              warpgroup also fetches its query tile of the NEXT unit before this unit's output is written.
+//   warp 8     producer: walks the block table and brings each K and V tile in with one cp.async.bulk.tensor.2d per
+//              page and 64-column half (128-byte swizzle), one lane per box, page ids read one tile ahead; two stages.
+//   warp 9     one thread issues the products, for the two query tiles in turn: O_g += P_g V (M = 128 rows, N = head
+//              size, 8 k-steps over the keys; V is the MN-major operand, read as the TMA laid it out), then
+//              S_g = Q_g K^T of the next key tile (M = 128, N = 128 keys, head size / 16 k-steps), so the products of
+//              one query tile run under the softmax of the other.
+// Tensor memory (512 columns): scores of tile g in columns g * 128, outputs of tile g from column 256 + g * head size.
+// The roles keep their barriers and phase counts from unit to unit; nothing is handed out at run time and there is
+// no block-wide barrier between units.  Softmax, scale and running sums are float32.  Every mbarrier wait is bounded;
+// every role reaches the common exit, where the tensor memory is given back.  Page sizes 8..128 (powers of two); other
+// sizes and head sizes go to the mma.sync kernels.
+#include "tcgen05.cuh"
 #include "attention_common.cuh"
 
-#define T5_WAIT_LIMIT (1 << 22)
 #define T5_BM 128                              // rows of one query tile: one softmax warpgroup, thread = row
 #define T5_QT 2                                // query tiles of a block, sharing the K and V tiles
 #define T5_ROWS (T5_BM * T5_QT)
 #define T5_THREADS (T5_QT * T5_BM + 128)       // two softmax warpgroups; a third holds the producer warp and the product warp
 #define T5_BN 128
-#define T5_HD 128
-#define T5_TILE (T5_BN * T5_HD * 2)            // bytes of one K or V tile (two 64-column halves of 16 KB)
-#define T5_HALF (128 * 128)                    // bytes of one half: 128 rows x 128 bytes
+#define T5_HALF (128 * 128)                    // bytes of 128 rows of 64 bf16: what one 128-byte-swizzled column half of a tile takes
 #ifndef T5_POLY
 #define T5_POLY 0                              // pairs in eight whose 2^x is a polynomial on the FMA units
 #endif
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, int count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* err) {
-    for (int it = 0; it < T5_WAIT_LIMIT; it++) {
-        uint32_t ok;
-        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
-                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-        if (ok) return true;
-    }
-    mb_set_error(err, MB_ERR_WAIT_TIMEOUT);
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
-                 ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-                 ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-// the same product with the A operand in tensor memory (row = lane, two bf16 per 32-bit column, k ascending)
-__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
-                 ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31};\n"
-        ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
-          "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]),
-          "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
-          "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]), "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
-__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
-
-// Build with -DT5_TRACE=1 (every mark) or -DT5_TRACE=<event> (that mark alone, which disturbs little) to record, for block 0, the SM clock at the hand-over points of the three roles
-// (a debugging aid: the array is read back with mb_attn_tc5_trace).
-#ifdef T5_TRACE
-__device__ long long t5_trace[3 * 4096];
-__device__ int t5_trace_n;
-__device__ long long t5_blocks[4 * 256];       // global timer (ns) at the start and the end of every block
-__device__ __forceinline__ long long t5_now() { long long v; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(v)); return v; }
-// every warp's first lane writes into a region of its own (no atomics: a mark costs a few stores)
-#ifndef T5_TRACE_BLOCK
-#define T5_TRACE_BLOCK 0
-#endif
-#define T5_MARK(ev, t) do { if ((T5_TRACE == 1 || (ev) == T5_TRACE) && blockIdx.x == T5_TRACE_BLOCK && (threadIdx.x & 31) == 0 && trace_i < 400) { \
-    const int i__ = (threadIdx.x >> 5) * 400 + trace_i++; \
-    t5_trace[3 * i__] = (ev) + 1000 * (threadIdx.x >> 5); t5_trace[3 * i__ + 1] = (t); t5_trace[3 * i__ + 2] = clock64(); } } while (0)
-#else
-#define T5_MARK(ev, t) do { } while (0)
-#endif
-
 // 2^x with the special-function unit (ex2.approx.ftz: 2 ulp; -inf gives 0)
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
@@ -166,18 +88,7 @@ __device__ __forceinline__ void poly_exp2_pair(uint64_t x2, float& ra, float& rb
     rb = __uint_as_float(__float_as_uint(pb) + (__float_as_uint(ib) << 23));
 }
 
-// shared-memory matrix descriptor, 128-byte swizzle, version 1: start address, leading and stride byte offsets
-__device__ __forceinline__ uint64_t umma_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
-    uint64_t d = 0;
-    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
-    d |= (uint64_t)((lbo >> 4) & 0x3FFF) << 16;
-    d |= (uint64_t)((sbo >> 4) & 0x3FFF) << 32;
-    d |= (uint64_t)1 << 46;
-    d |= (uint64_t)2 << 61;
-    return d;
-}
-
-// The same descriptor in two halves.  Only the low word changes from product to product (start address in bits 0-13,
+// The shared-memory matrix descriptor (128-byte swizzle, version 1) in two halves.  Only the low word changes from product to product (start address in bits 0-13,
 // leading byte offset in bits 16-29), so the issuing thread keeps one low word per operand and adds a constant: built
 // whole for every product, the descriptors cost that one thread more time than the products take to run.
 constexpr uint32_t T5_DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);       // stride byte offset 1024, version 1, 128-byte swizzle
@@ -235,22 +146,23 @@ __device__ __forceinline__ int t5_unit_at(int k, int n_units) {
     return u < n_units ? u : -1;
 }
 
+template <int HD>
 __global__ void __launch_bounds__(T5_THREADS, 1) attn_tc5_kernel(const AttnParams P, const __grid_constant__ CUtensorMap kmap,
                                                                   const __grid_constant__ CUtensorMap vmap, int n_units) {
+    constexpr int HALVES = HD / 64;                 // 64-column halves of a row of a tile (one TMA box wide each)
+    constexpr int TILE = T5_BN * HD * 2;            // bytes of one K or V tile, and of one query tile
+    constexpr int OC = HD / 32;                     // 32-column groups of a row of the output
     extern __shared__ unsigned char smem_unaligned[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(
         (reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~static_cast<uintptr_t>(1023));
-    // 2 x Q tile (32 KB each) | 2 stages x K tile (32 KB) | 2 stages x V tile (32 KB) | barriers
-    const uint32_t q_s0 = smem_u32(smem), k_s0 = q_s0 + T5_QT * 2 * T5_HALF, v_s0 = k_s0 + 2 * T5_TILE;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + T5_QT * 2 * T5_HALF + 4 * T5_TILE);
+    // 2 x Q tile | 2 stages x K tile | 2 stages x V tile (32 KB each at head size 128, 16 KB at 64) | barriers
+    const uint32_t q_s0 = smem_u32(smem), k_s0 = q_s0 + T5_QT * TILE, v_s0 = k_s0 + 2 * TILE;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + T5_QT * TILE + 4 * TILE);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
     const uint32_t k_full0 = smem_u32(bars), k_empty0 = k_full0 + 16, v_full0 = k_full0 + 32, v_empty0 = k_full0 + 48,
                    s_full0 = k_full0 + 64, p_full0 = k_full0 + 80, o_done0 = k_full0 + 96, q_ready0 = k_full0 + 112;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-#ifdef T5_TRACE
-    if (tid == 0 && blockIdx.x < 256) t5_blocks[768 + blockIdx.x] = t5_now();
-#endif
     if (tid == 8 * 32) {
         asm volatile("prefetch.tensormap [%0];\n" ::"l"(&kmap) : "memory");
         asm volatile("prefetch.tensormap [%0];\n" ::"l"(&vmap) : "memory");
@@ -276,12 +188,8 @@ __global__ void __launch_bounds__(T5_THREADS, 1) attn_tc5_kernel(const AttnParam
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     // tensor memory: scores of tile g in columns g*128 .. +127 (its probabilities go back into the first 64 of them as
-    // bf16 pairs), output accumulator of tile g in columns 256 + g*128 .. +127
+    // bf16 pairs), output accumulator of tile g in columns 256 + g*HD .. +HD-1
     const uint32_t tm_s0 = tmem_base, tm_o0 = tmem_base + 256;
-#ifdef T5_TRACE
-    int trace_i = 0;
-    if (tid == 0 && blockIdx.x < 256) { t5_blocks[2 * blockIdx.x] = t5_now(); t5_blocks[512 + 2 * blockIdx.x] = clock64(); }
-#endif
 
     // The block is compiled for 168 registers a thread; a softmax thread keeps a row of 128 scores in registers and wants
     // more, the third warpgroup needs few: it hands its share over.
@@ -293,8 +201,8 @@ __global__ void __launch_bounds__(T5_THREADS, 1) attn_tc5_kernel(const AttnParam
         // issuing them one after the other took 3,000 to 4,000 cycles per 32 KB tile and was what the whole block
         // waited for.  The lane's page id is read from the block table one tile ahead.
         const int shift = P.page_shift, page = P.page;
-        const int boxes = (T5_BN >> shift) * 2;                      // 2 .. 32
-        const int p = lane >> 1, h = lane & 1;
+        const int boxes = (T5_BN >> shift) * HALVES;                 // 1 .. 32
+        const int p = lane / HALVES, h = lane % HALVES;
         T5Unit U;
         int k = 0, unit = t5_unit_at(0, n_units);
         bool live = unit >= 0 && t5_unit(P, unit, U);
@@ -314,8 +222,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1) attn_tc5_kernel(const AttnParam
                 const uint32_t empty = (keys ? k_empty0 : v_empty0) + 8 * s, fb = (keys ? k_full0 : v_full0) + 8 * s;
                 bool got = round == 0 || mbar_wait(empty, (round - 1) & 1, P.err);
                 if (!__all_sync(0xffffffffu, got)) return false;
-                T5_MARK(keys ? 10 : 12, t);
-                if (lane == 0) mbar_expect_tx(fb, T5_TILE);
+                if (lane == 0) mbar_expect_tx(fb, TILE);
                 __syncwarp();
                 if (lane < boxes) {
                     const int key0 = U.lo_al + t * T5_BN + p * page;
@@ -323,10 +230,9 @@ __global__ void __launch_bounds__(T5_THREADS, 1) attn_tc5_kernel(const AttnParam
                         if (key0 < U.hi && key0 + page > U.lo) mb_set_error(P.err, pg < 0 ? MB_ERR_PAGE_MISSING : MB_ERR_PAGE_RANGE);
                         pg = 0;                                      // any page: every key of it is masked
                     }
-                    const uint32_t dst = (keys ? k_s0 : v_s0) + s * T5_TILE + h * T5_HALF + p * page * 128;
+                    const uint32_t dst = (keys ? k_s0 : v_s0) + s * TILE + h * T5_HALF + p * page * 128;
                     tma_load_2d(dst, keys ? &kmap : &vmap, h * 64, (pg * P.KV + U.kvh) * page, fb);
                 }
-                T5_MARK(keys ? 11 : 13, t);
                 return true;
             };
             int pg_cur = page_of(0);
@@ -346,9 +252,9 @@ __global__ void __launch_bounds__(T5_THREADS, 1) attn_tc5_kernel(const AttnParam
         // overwrites the buffer its probabilities lay in; it is issued after the output product that read them, and the
         // products run in the order they were issued.
         if (lane == 0) {
-            // D float, A and B bf16, M = 128, N = 128; the second descriptor has B MN-major (bit 16) for P V
-            constexpr uint32_t idesc_qk = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
-            constexpr uint32_t idesc_pv = idesc_qk | (1u << 16);
+            // D float, A and B bf16, M = 128; scores N = 128 keys, outputs N = HD with B MN-major (bit 16)
+            constexpr uint32_t idesc_qk = umma_idesc(T5_BM, T5_BN);
+            constexpr uint32_t idesc_pv = umma_idesc(T5_BM, HD) | (1u << 16);
             T5Unit U;
             int k = 0, unit = t5_unit_at(0, n_units);
             bool live = unit >= 0 && t5_unit(P, unit, U);
@@ -361,37 +267,31 @@ __global__ void __launch_bounds__(T5_THREADS, 1) attn_tc5_kernel(const AttnParam
                 };
                 auto scores = [&](int g, int t) -> bool {           // S_g = Q_g K_t^T
                     const int n = kt + t, s = n & 1;
-                    T5_MARK(20 + g, t);
                     if (!mbar_wait(k_full0 + 8 * s, (n >> 1) & 1, P.err)) return false;
                     tc_fence_after();
-                    const uint32_t k_lo = umma_desc_lo(k_s0 + s * T5_TILE, 0), q_lo = umma_desc_lo(q_s0 + g * 2 * T5_HALF, 0);
+                    const uint32_t k_lo = umma_desc_lo(k_s0 + s * TILE, 0), q_lo = umma_desc_lo(q_s0 + g * TILE, 0);
 #pragma unroll
-                    for (int ks = 0; ks < 8; ks++) {
+                    for (int ks = 0; ks < HD / 16; ks++) {
                         constexpr uint32_t half = T5_HALF >> 4;
                         const uint32_t off = (ks >> 2) * half + (ks & 3) * 2;             // in 16-byte units
                         umma_f16(tm_s0 + g * 128, umma_desc_join(q_lo + off), umma_desc_join(k_lo + off), idesc_qk, ks > 0);
                     }
                     if (last_reader(g, t)) umma_commit(k_empty0 + 8 * s);
                     umma_commit(s_full0 + 8 * g);
-                    T5_MARK(22 + g, t);
                     return true;
                 };
                 auto outputs = [&](int g, int t) -> bool {          // O_g += P_g V_t
                     const int n = kt + t, s = n & 1;
-                    T5_MARK(24 + g, t);
                     if (!mbar_wait(p_full0 + 8 * g, ((g == 0 ? nt0 : nt1) + t) & 1, P.err)) return false;
-                    T5_MARK(40 + g, t);
                     if (!mbar_wait(v_full0 + 8 * s, (n >> 1) & 1, P.err)) return false;
-                    T5_MARK(26 + g, t);
                     tc_fence_after();
-                    const uint32_t v_lo = umma_desc_lo(v_s0 + s * T5_TILE, T5_HALF);
+                    const uint32_t v_lo = umma_desc_lo(v_s0 + s * TILE, T5_HALF);
 #pragma unroll
                     for (int kk = 0; kk < 8; kk++)                  // 16 keys per step: 2,048 bytes further in the tile
-                        umma_f16_ts(tm_o0 + g * 128, tm_s0 + g * 128 + kk * 8, umma_desc_join(v_lo + kk * 128), idesc_pv,
+                        umma_f16_ts(tm_o0 + g * HD, tm_s0 + g * 128 + kk * 8, umma_desc_join(v_lo + kk * 128), idesc_pv,
                                     (t > 0 || kk > 0) ? 1u : 0u);
                     if (last_reader(g, t)) umma_commit(v_empty0 + 8 * s);
                     if (t == U.tiles(g) - 1) umma_commit(o_done0 + 8 * g);
-                    T5_MARK(28 + g, t);
                     return true;
                 };
 #pragma unroll
@@ -415,9 +315,9 @@ __global__ void __launch_bounds__(T5_THREADS, 1) attn_tc5_kernel(const AttnParam
         // ---------------------------------------------------------------- softmax: warpgroup = query tile, thread = row
         const int g = warp >> 2, q = warp & 3, r_loc = q * 32 + lane;
         const int st = tid - g * T5_BM;                             // 0..127 within the warpgroup
-        const uint32_t q_s = q_s0 + g * 2 * T5_HALF;
+        const uint32_t q_s = q_s0 + g * TILE;
         const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
-        const uint32_t s_addr = tm_s0 + g * 128 + lane_addr, o_addr = tm_o0 + g * 128 + lane_addr;
+        const uint32_t s_addr = tm_s0 + g * 128 + lane_addr, o_addr = tm_o0 + g * HD + lane_addr;
         T5Unit U;
         int k = 0, unit = t5_unit_at(0, n_units);
         bool live = unit >= 0 && t5_unit(P, unit, U);
@@ -435,12 +335,12 @@ __global__ void __launch_bounds__(T5_THREADS, 1) attn_tc5_kernel(const AttnParam
         // the unit's query tile goes into shared memory (asynchronous copies, waited for in publish_q)
         auto fetch_q = [&]() {
             const int row_g = U.row0 + g * T5_BM;
-            for (int cid = st; cid < T5_BM * 16; cid += T5_BM) {
-                const int row = cid >> 4, c = cid & 15, rr = row_g + row;
+            for (int cid = st; cid < T5_BM * (HD / 8); cid += T5_BM) {
+                const int row = cid / (HD / 8), c = cid % (HD / 8), rr = row_g + row;
                 const bf16* src = P.q;
                 int bytes = 0;
                 if (rr < U.R) {
-                    src = P.q + (size_t)(U.tok0 + rr / U.G) * P.q_stride + (size_t)(U.kvh * U.G + rr % U.G) * T5_HD + c * 8;
+                    src = P.q + (size_t)(U.tok0 + rr / U.G) * P.q_stride + (size_t)(U.kvh * U.G + rr % U.G) * HD + c * 8;
                     bytes = 16;
                 }
                 const uint32_t dst = q_s + (c >> 3) * T5_HALF + (row >> 3) * 1024 + (row & 7) * 128 + (((c & 7) ^ (row & 7)) << 4);
@@ -466,11 +366,9 @@ __global__ void __launch_bounds__(T5_THREADS, 1) attn_tc5_kernel(const AttnParam
             }
             float m_run = -INFINITY, l_run = 0.0f;
             for (int t = 0; t < Tq && ok; t++) {
-                T5_MARK(30 + g, t);
                 // the scores of this tile are complete -- and so is every product issued before them: the output product
                 // of the tile before, which read the probabilities in this buffer and wrote the accumulator
                 if (!mbar_wait(s_full0 + 8 * g, (nt + t) & 1, P.err)) { ok = false; break; }
-                T5_MARK(32 + g, t);
                 tc_fence_after();
                 const int kb = lo_al + t * T5_BN;
                 const bool full_tile = kb + T5_BN - 1 <= pos_min_g && kb >= ((P.window > 0) ? pos_max_g - P.window + 1 : 0);
@@ -516,7 +414,7 @@ __global__ void __launch_bounds__(T5_THREADS, 1) attn_tc5_kernel(const AttnParam
                 const bool rescale = t > 0 && __any_sync(0xffffffffu, m_new != m_run);
                 if (rescale) {
 #pragma unroll 1
-                    for (int c = 0; c < 4; c++) {
+                    for (int c = 0; c < OC; c++) {
                         uint32_t ov[32];
                         tmem_ld32(o_addr + c * 32, ov);
                         tmem_ld_wait();
@@ -525,7 +423,6 @@ __global__ void __launch_bounds__(T5_THREADS, 1) attn_tc5_kernel(const AttnParam
                         tmem_st32(o_addr + c * 32, ov);
                     }
                 }
-                T5_MARK(34 + g + (rescale ? 100 : 0), t);
                 m_run = m_new;
                 // probabilities = 2^(scale * s - reference); as bf16 pairs they go back into the first 64 columns of the
                 // score buffer, where the output product reads them as its A operand.  T5_POLY pairs in eight take the
@@ -567,27 +464,22 @@ __global__ void __launch_bounds__(T5_THREADS, 1) attn_tc5_kernel(const AttnParam
                 l_run = l_run * corr + sum;
                 tc_fence_before();
                 mbar_arrive(p_full0 + 8 * g);
-                T5_MARK(36 + g, t);
             }
             if (!ok) break;
             // Every score product of this unit is done (the last tile's scores were read above), so the query tile of
             // the next unit can come in now, while the last output product runs; it is handed to the product thread
             // before this unit's output is written, so the first scores of the next unit are computed meanwhile.
-#ifndef T5_LATE_Q
             advance();
             if (unit >= 0) fetch_q();
-#endif
             if (!mbar_wait(o_done0 + 8 * g, nu & 1, P.err)) { ok = false; break; }
             tc_fence_after();
-#ifndef T5_LATE_Q
             if (unit >= 0) publish_q();
-#endif
             {
                 const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
                 const bool live_row = r < R;                        // rows past the end take part in the loads only
-                bf16* dst = P.out + (live_row ? ((size_t)(tok0 + r / G) * P.H + (kvh * G + r % G)) * T5_HD : 0);
+                bf16* dst = P.out + (live_row ? ((size_t)(tok0 + r / G) * P.H + (kvh * G + r % G)) * HD : 0);
 #pragma unroll 1
-                for (int c = 0; c < 4; c++) {
+                for (int c = 0; c < OC; c++) {
                     uint32_t ov[32];
                     tmem_ld32(o_addr + c * 32, ov);
                     tmem_ld_wait();
@@ -604,20 +496,12 @@ __global__ void __launch_bounds__(T5_THREADS, 1) attn_tc5_kernel(const AttnParam
                     }
                 }
             }
-#ifdef T5_LATE_Q
-            advance();
-            if (unit >= 0) { fetch_q(); publish_q(); }
-#endif
             nu++;
             nt += Tq;
-            T5_MARK(38 + g, 0);
         }
     }
     tc_fence_before();
     __syncthreads();
-#ifdef T5_TRACE
-    if (tid == 0 && blockIdx.x < 256) { t5_blocks[2 * blockIdx.x + 1] = t5_now(); t5_blocks[512 + 2 * blockIdx.x + 1] = clock64(); }
-#endif
     if (warp == 9) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(*tmem_slot), "r"(512u) : "memory");
@@ -625,32 +509,17 @@ __global__ void __launch_bounds__(T5_THREADS, 1) attn_tc5_kernel(const AttnParam
 }
 
 // ------------------------------------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiled encode_fn() {
-    static EncodeTiled fn = nullptr;
-    if (!fn) {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiled>(p);
-    }
-    return fn;
-}
-
-struct MapKey { const void* ptr; long long rows; int hd, page; };
-struct MapEntry { MapKey key; CUtensorMap map; };
-#define MAP_CACHE 512
-static MapEntry map_cache[MAP_CACHE];
-static int map_count = 0;
+// tensor maps of the cache pools: a pool is (pages * kv heads * page) rows of HD bf16; a box is one page of one kv head,
+// 64 columns wide, with the 128-byte swizzle
+struct PoolMap { const void* ptr; long long rows; int hd, page; CUtensorMap map; };
+#define POOL_MAPS 512
+static PoolMap pool_maps[POOL_MAPS];
+static int pool_map_count = 0;
 
 static int pool_map(const void* pool, long long rows, int HD, int page, CUtensorMap* out) {
-    for (int i = 0; i < map_count; i++) {
-        const MapKey& k = map_cache[i].key;
-        if (k.ptr == pool && k.rows == rows && k.hd == HD && k.page == page) { *out = map_cache[i].map; return 0; }
+    for (int i = 0; i < pool_map_count; i++) {
+        const PoolMap& k = pool_maps[i];
+        if (k.ptr == pool && k.rows == rows && k.hd == HD && k.page == page) { *out = k.map; return 0; }
     }
     EncodeTiled enc = encode_fn();
     if (!enc) return -6;
@@ -663,11 +532,7 @@ static int pool_map(const void* pool, long long rows, int HD, int page, CUtensor
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return -6;
-    if (map_count < MAP_CACHE) {
-        map_cache[map_count].key = MapKey{pool, rows, HD, page};
-        map_cache[map_count].map = m;
-        map_count++;
-    }
+    if (pool_map_count < POOL_MAPS) pool_maps[pool_map_count++] = PoolMap{pool, rows, HD, page, m};
     *out = m;
     return 0;
 }
@@ -675,7 +540,26 @@ static int pool_map(const void* pool, long long rows, int HD, int page, CUtensor
 MB_API int mb_attn_tc5_rows() { return T5_ROWS; }
 
 MB_API int mb_attn_tc5_supports(int HD, int page) {
-    return HD == 128 && (page == 8 || page == 16 || page == 32 || page == 64 || page == 128);
+    return (HD == 64 || HD == 128) && (page == 8 || page == 16 || page == 32 || page == 64 || page == 128);
+}
+
+template <int HD>
+static int launch_tc5(const AttnParams& P, const CUtensorMap& kmap, const CUtensorMap& vmap, int n_units, cudaStream_t st) {
+    constexpr size_t smem = 1024 + (T5_QT + 4) * (size_t)(T5_BN * HD * 2) + 16 * 8 + 16;
+    static bool configured = false;
+    static int sms = 0;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_tc5_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (sms <= 0) sms = 148;
+        configured = true;
+    }
+    attn_tc5_kernel<HD><<<n_units < sms ? n_units : sms, T5_THREADS, smem, st>>>(P, kmap, vmap, n_units);
+    MB_LAUNCH_CHECK();
+    return 0;
 }
 
 // items: (sequence, tile of T5_ROWS = 256 packed rows, 0, 1), heaviest first -- this kernel does not split the keys over blocks.
@@ -703,36 +587,6 @@ MB_API int mb_attn_tc5_bf16(const void* q, int q_stride, void* out, const void* 
     if (rc) return rc;
     rc = pool_map(vpool, rows, HD, page, &vmap);
     if (rc) return rc;
-    const size_t smem = 1024 + T5_QT * 2 * T5_HALF + 4 * T5_TILE + 16 * 8 + 16;
-    static bool configured = false;
-    static int sms = 0;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_tc5_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-        if (sms <= 0) sms = 148;
-        configured = true;
-    }
     const int n_units = n_items * KV;
-    attn_tc5_kernel<<<n_units < sms ? n_units : sms, T5_THREADS, smem, st>>>(P, kmap, vmap, n_units);
-    MB_LAUNCH_CHECK();
-    return 0;
+    return HD == 64 ? launch_tc5<64>(P, kmap, vmap, n_units, st) : launch_tc5<128>(P, kmap, vmap, n_units, st);
 }
-
-#ifdef T5_TRACE
-MB_API int mb_attn_tc5_blocks(long long* host) {
-    cudaMemcpyFromSymbol(host, t5_blocks, sizeof(long long) * 4 * 256);
-    return 256;
-}
-// -> the number of event slots copied (4 roles x 1024); unused slots hold zeros; the device array is cleared
-MB_API int mb_attn_tc5_trace(long long* host, int max_events) {
-    int n = max_events < 4096 ? max_events : 4096;
-    cudaMemcpyFromSymbol(host, t5_trace, (size_t)n * 3 * sizeof(long long));
-    void* p = nullptr;
-    cudaGetSymbolAddress(&p, t5_trace);
-    cudaMemset(p, 0, sizeof(long long) * 3 * 4096);
-    return n;
-}
-#endif

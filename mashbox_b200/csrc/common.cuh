@@ -6,6 +6,8 @@
 
 #define MB_API extern "C" __attribute__((visibility("default")))
 
+typedef __nv_bfloat16 bf16;
+
 // Codes a kernel leaves in the engine's error word (first one wins); the host reads the word after a step.
 enum MbDeviceError {
     MB_ERR_NONE = 0,
@@ -49,6 +51,14 @@ __device__ __forceinline__ float mb_block_sum(float v, float* scratch /* 32 floa
     __syncthreads();
     float t = (lane < nwarp) ? scratch[lane] : 0.0f;
     return mb_warp_sum(t);
+}
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// two floats rounded to bf16 in one 32-bit word, the first in the low half
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
 }
 
 #define MB_LAUNCH_CHECK() do { cudaError_t e__ = cudaGetLastError(); if (e__ != cudaSuccess) return (int)e__; } while (0)

@@ -146,10 +146,10 @@ __global__ void __launch_bounds__(192, 1) gemm_tc5_kernel(const __grid_constant_
                         for (int i = 0; i < 32; i += 8)
                             if (m0 + c + i + 8 <= M) {
                                 uint4 v;
-                                v.x = pack2(__uint_as_float(r[i]), __uint_as_float(r[i + 1]));
-                                v.y = pack2(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
-                                v.z = pack2(__uint_as_float(r[i + 4]), __uint_as_float(r[i + 5]));
-                                v.w = pack2(__uint_as_float(r[i + 6]), __uint_as_float(r[i + 7]));
+                                v.x = pack_bf16(__uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+                                v.y = pack_bf16(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]));
+                                v.z = pack_bf16(__uint_as_float(r[i + 4]), __uint_as_float(r[i + 5]));
+                                v.w = pack_bf16(__uint_as_float(r[i + 6]), __uint_as_float(r[i + 7]));
                                 *reinterpret_cast<uint4*>(dst + i) = v;
                             }
                     }

@@ -482,7 +482,7 @@ def attention_tma(q, q_stride, out, kpool, vpool, items, n_items, decode, q_star
 
 
 def attention_tc5_supports(HD, page):
-    return HD == 128 and page in (8, 16, 32, 64, 128)
+    return HD in (64, 128) and page in (8, 16, 32, 64, 128)
 
 
 def attention_tc5_rows():
@@ -495,7 +495,7 @@ def attention_tc5_rows():
 def attention_tc5(q, q_stride, out, kpool, vpool, items, n_items, q_start, q_len, pos0, seq_row, table, H, KV, HD, page,
                   num_pages, window, scale, err):
     """Prompt-form attention on tcgen05: items are (sequence, tile of attention_tc5_rows() packed rows, 0, 1); head
-    size 128."""
+    sizes 64 and 128."""
     _cuda(q, out, kpool, vpool, items, q_start, q_len, pos0, seq_row, table)
     f = _fn("attention_tc5", "mb_attn_tc5_bf16",
             [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,

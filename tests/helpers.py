@@ -24,7 +24,13 @@ TINY_C = LlamaConfig(architecture="LlamaForCausalLM", num_layers=2, hidden=256, 
                      intermediate=384, vocab=311, rms_eps=1e-5, rope_theta=1000000.0,
                      rope_scaling=RopeScaling("linear", 2.0), tie_embeddings=False, attention_bias=False,
                      max_position=1024)
-TINY = {"A": (TINY_A, 0, 16), "B": (TINY_B, 1, 8), "C": (TINY_C, 2, 16)}          # config, seed, page size
+# and a fourth with heads of 64 (not hidden / heads), three query heads per kv head, biases and a tied head: the head
+# size of the smallest models, which the TMA-fed and tcgen05 attention kernels take in a form of its own
+TINY_D = LlamaConfig(architecture="LlamaForCausalLM", num_layers=2, hidden=192, num_heads=6, num_kv_heads=2, head_dim=64,
+                     intermediate=272, vocab=401, rms_eps=1e-5, rope_theta=10000.0,
+                     rope_scaling=RopeScaling("llama3", 4.0, 1.0, 4.0, 32), tie_embeddings=True, attention_bias=True,
+                     max_position=1024)
+TINY = {"A": (TINY_A, 0, 16), "B": (TINY_B, 1, 8), "C": (TINY_C, 2, 16), "D": (TINY_D, 3, 32)}   # config, seed, page size
 # Random weights shaped like a trained model's rather than like an initialisation: an embedding of order one, readers
 # (q, k, v, gate, up, head) near 1/sqrt(fan in) so that attention is not uniform, and writers into the residual stream
 # (o_proj, down_proj) small, so that a layer changes the stream a little instead of replacing it.  With every matrix

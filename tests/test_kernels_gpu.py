@@ -214,13 +214,16 @@ def test_attention_plain_kernel_window_edge(dtype):
 MMA_CASES = [  # HD, H, KV, page, window, splits
     (256, 8, 4, 16, None, 2), (96, 6, 2, 8, 70, 1), (80, 4, 1, 16, None, 4), (48, 3, 3, 4, None, 1),
     (128, 6, 2, 16, None, 1), (128, 5, 5, 32, 300, 1), (128, 8, 2, 16, None, 1), (128, 8, 2, 16, None, 4), (64, 6, 2, 8, None, 3), (32, 6, 1, 8, 50, 2),
-    (16, 4, 2, 4, None, 1), (128, 32, 8, 32, 700, 8), (64, 5, 5, 16, None, 2), (128, 16, 1, 16, None, 2)]
+    (16, 4, 2, 4, None, 1), (128, 32, 8, 32, 700, 8), (64, 5, 5, 16, None, 2), (128, 16, 1, 16, None, 2),
+    (64, 32, 8, 16, None, 1), (64, 8, 2, 64, 300, 2), (64, 3, 1, 128, None, 1)]
 
 
 def run_mma(seqs, window, splits, kind="mma"):
     K = ops()
-    flash = K.attention_mma if kind == "mma" else K.attention_tma
     H, KV, HD, page = seqs.H, seqs.KV, seqs.HD, seqs.page
+    flash = K.attention_mma if kind == "mma" else K.attention_tma
+    if kind == "tc5" and not K.attention_tma_supports(HD, page):        # decode-form items beside the tcgen05 kernel:
+        flash = K.attention_mma                                        # the kernel the mixer would pick for them
     Gq = H // KV
     dec, pre, part_base, part_tok = G.mma_items(seqs, Gq, splits, prefill_rows=K.attention_tc5_rows() if kind == "tc5" else 64,
                                                 split_prefill=kind != "tc5")
@@ -258,7 +261,7 @@ def test_attention_tensor_core_kernel(HD, H, KV, page, window, splits, kind):
     dominant_key(seqs, 0, far)
     seqs.round().build()
     if kind == "tc5" and not ops().attention_tc5_supports(HD, page):
-        pytest.skip("the tcgen05 kernel takes head size 128 only")
+        pytest.skip("the tcgen05 kernel takes head sizes 64 and 128 only")
     if kind.startswith("tma") and not ops().attention_tma_supports(HD, page):
         with pytest.raises(Exception, match="does not take these sizes"):
             run_mma(seqs, window, splits, kind)
@@ -269,7 +272,8 @@ def test_attention_tensor_core_kernel(HD, H, KV, page, window, splits, kind):
     assert float((out[0].double().cpu() - want).abs().max()) < 0.05 * float(want.abs().max()) + 1e-2
 
 
-@pytest.mark.parametrize("kind,HD", [("mma", 64), ("tma", 64), ("tma", 128), ("tma-merging", 128), ("tc5", 128)])
+@pytest.mark.parametrize("kind,HD", [("mma", 64), ("tma", 64), ("tma", 128), ("tma-merging", 128), ("tc5", 128),
+                                     ("tc5", 64)])
 @pytest.mark.parametrize("splits", [1, 4])
 def test_attention_tensor_core_kernel_window_edge(splits, kind, HD):
     H, KV, page, window = 8, 2, 16, 130

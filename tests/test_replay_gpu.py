@@ -8,7 +8,7 @@ import torch
 from tests import helpers as H
 
 pytestmark = pytest.mark.gpu
-CASES = [(n, m) for n in ("A", "B", "C") for m in H.MODES]
+CASES = [(n, m) for n in ("A", "B", "C", "D") for m in H.MODES]
 
 
 def runner_for(tmp, name, mode, max_tokens, options=None):
@@ -115,7 +115,7 @@ def test_mixed_batches_with_page_reuse(tmp_path_factory, name, mode):
     assert all(f == runner.cache.num_pages for f in runner.cache.free_pages())
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_streaming_products_for_steps_of_few_tokens(tmp_path_factory, name):
     """the weight-streaming products (off by default) take every step of at most 16 tokens: norm, rotation, cache write,
     gate and residual add inside the four products of a layer, the sums of squares handed from one to the next"""
@@ -154,7 +154,7 @@ def np_logit_hash(lg):
     return [(int(a), float(np.float32(t[1]) - np.float32(t[0]))) for a, t in zip(h, top)]
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_float32_logits_are_bit_identical_under_every_cut(tmp_path_factory, name):
     """What the 32-bit path promises: the logits of a position are the same BITS whether the request ran whole, with its
     last 32 tokens one by one, in portions of changing size down to two tokens, or mixed with other requests on pages
