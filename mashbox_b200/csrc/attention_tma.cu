@@ -68,6 +68,10 @@ __global__ void __launch_bounds__(160, 2) attn_tma_kernel(const AttnParams P, co
     uint64_t* bars = reinterpret_cast<uint64_t*>(qs + BM * HD);          // full[STAGES], empty[STAGES]
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
 
+    // Up to pdl_wait() the kernel reads the step's own arrays only (which no kernel writes); the queries, the pages --
+    // the step's own keys and values among them -- and the splits' partial results come after it, by TMA, cp.async.cg
+    // and ld.global.cg.
+    pdl_launch_dependents();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, tig = lane & 3;
     const int4 item = P.items[blockIdx.x];
     const int seq = item.x, m_tile = item.y, split = item.z, n_splits = item.w;
@@ -95,6 +99,7 @@ __global__ void __launch_bounds__(160, 2) attn_tma_kernel(const AttnParams P, co
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     }
     __syncthreads();
+    pdl_wait();
 
     if (warp == 4) {
         // ---------------------------------------------------------------- producer
@@ -431,6 +436,8 @@ static int pool_map(const void* pool, long long rows, int HD, int page, CUtensor
     return 0;
 }
 
+MB_PDL_SWITCH(mb_attn_tma_set_pdl)
+
 template <int HD, bool DECODE, int STAGES>
 static int launch_tma(const AttnParams& P, const CUtensorMap& kmap, const CUtensorMap& vmap, int n_items, cudaStream_t st) {
     constexpr int BM = DECODE ? 16 : 64;
@@ -445,9 +452,9 @@ static int launch_tma(const AttnParams& P, const CUtensorMap& kmap, const CUtens
                              cudaSharedmemCarveoutMaxShared);
         configured = true;
     }
-    attn_tma_kernel<HD, DECODE, STAGES><<<dim3(n_items, P.KV), 160, smem, st>>>(P, kmap, vmap);
-    MB_LAUNCH_CHECK();
-    return 0;
+    const cudaError_t e = mb_launch(mb_pdl != 0, attn_tma_kernel<HD, DECODE, STAGES>, dim3(n_items, P.KV), dim3(160), smem, st,
+                                    P, kmap, vmap);
+    return e == cudaSuccess ? 0 : (int)e;
 }
 
 MB_API int mb_attn_tma_supports(int HD, int page) {

@@ -61,4 +61,34 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// ---- programmatic dependent launch.  A kernel launched with the programmatic-serialization attribute may start while
+// the kernel before it in the stream still runs.  It must call pdl_wait() -- every thread that goes on to touch global
+// memory -- before it reads anything another kernel of the step wrote and before it writes anything at all; what it
+// does before that (setting barriers up, fetching weights, which no kernel writes) overlaps with the tail of the kernel
+// before.  Data that a kernel before it produced is read around the L1 (TMA, cp.async.cg, ld.global.cg), never through
+// the read-only path: a line may have reached an SM's L1 before its producer had finished.  pdl_launch_dependents()
+// lets the kernel AFTER this one start; without the attribute on the launch both instructions do nothing.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
+// Every kernel library has one switch: MB_PDL_SWITCH(mb_<library>_set_pdl) defines it and the function that sets it.
+#define MB_PDL_SWITCH(name) static int mb_pdl = 0; MB_API int name(int on) { mb_pdl = on; return 0; }
+
+// kernel<<<grid, block, smem, st>>>(args...), with the programmatic-serialization attribute when pdl is set
+template <typename... Params, typename... Args>
+static inline cudaError_t mb_launch(bool pdl, void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem,
+                                    cudaStream_t st, Args... args) {
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cfg.attrs = &attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);
+}
+
 #define MB_LAUNCH_CHECK() do { cudaError_t e__ = cudaGetLastError(); if (e__ != cudaSuccess) return (int)e__; } while (0)

@@ -237,6 +237,9 @@ __global__ void rope_kv_write_vec_kernel(__nv_bfloat16* __restrict__ qkv, const 
                                          __nv_bfloat16* __restrict__ vpool, const float* __restrict__ freqs, int H, int KV,
                                          int HD, int RD, int pairing, int page, int num_pages, int* err) {
     extern __shared__ float2 rope_cs[];                              // (cos, sin) of the token's RD/2 pairs
+    // What comes before pdl_wait() reads the step's own arrays and the frequency table only (no kernel writes them) and
+    // may run while the q/k/v product before this kernel still does; q, k and v are read after it, around the L1.
+    pdl_launch_dependents();
     const int n = blockIdx.x, pos = positions[n];
     __nv_bfloat16* row = qkv + (size_t)n * (H + 2 * KV) * HD;
     size_t slot = 0;
@@ -259,6 +262,7 @@ __global__ void rope_kv_write_vec_kernel(__nv_bfloat16* __restrict__ qkv, const 
         }
         __syncthreads();
     }
+    pdl_wait();
     const int cph = HD / 8, rhalf = RD / 2, total = (H + 2 * KV) * cph;
     for (int w = threadIdx.x + blockIdx.y * blockDim.x; w < total; w += blockDim.x * gridDim.y) {
         const int h = w / cph, e0 = (w % cph) * 8;
@@ -272,7 +276,7 @@ __global__ void rope_kv_write_vec_kernel(__nv_bfloat16* __restrict__ qkv, const 
         if (!is_q) dst = (is_v ? vpool : kpool) + (slot + (size_t)((h - H) % KV) * page) * HD + e0;
         float a[8], b[8];
         {
-            const uint4 v = *reinterpret_cast<const uint4*>(src);
+            const uint4 v = __ldcg(reinterpret_cast<const uint4*>(src));
             const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&v);
 #pragma unroll
             for (int i = 0; i < 4; i++) { const float2 x = __bfloat1622float2(p2[i]); a[2 * i] = x.x; a[2 * i + 1] = x.y; }
@@ -282,7 +286,7 @@ __global__ void rope_kv_write_vec_kernel(__nv_bfloat16* __restrict__ qkv, const 
             for (int i = 0; i < 8; i++) a[i] += bias[(size_t)h * HD + e0 + i];
         }
         if (paired) {
-            const uint4 v = *reinterpret_cast<const uint4*>(src + rhalf);
+            const uint4 v = __ldcg(reinterpret_cast<const uint4*>(src + rhalf));
             const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&v);
 #pragma unroll
             for (int i = 0; i < 4; i++) { const float2 x = __bfloat1622float2(p2[i]); b[2 * i] = x.x; b[2 * i + 1] = x.y; }
@@ -393,6 +397,8 @@ MB_API int mb_add_rmsnorm_bf16(float* x, const void* delta, const float* dbias, 
     return add_rmsnorm_launch<__nv_bfloat16>(x, delta, dbias, rows, w, eps, out, n_out, D, st);
 }
 
+MB_PDL_SWITCH(mb_elementwise_set_pdl)
+
 template <typename T>
 static int rope_kv_write_launch(void* qkv, const float* bias, const int* positions, const int* tok_seq,
                                 const int* table, int max_blocks, void* kpool, void* vpool, const float* freqs, int N,
@@ -405,11 +411,11 @@ static int rope_kv_write_launch(void* qkv, const float* bias, const int* positio
         const int items = (H + 2 * KV) * (HD / 8);
         int split = N >= 512 ? 1 : (items + 255) / 256;
         if (split > 16) split = 16;
-        rope_kv_write_vec_kernel<<<dim3(N, split), 256, (RD / 2) * sizeof(float2), st>>>(
-            (__nv_bfloat16*)qkv, bias, positions, tok_seq, table, max_blocks, (__nv_bfloat16*)kpool, (__nv_bfloat16*)vpool,
-            freqs, H, KV, HD, RD, pairing, page, num_pages, err);
-        MB_LAUNCH_CHECK();
-        return 0;
+        const cudaError_t e = mb_launch(mb_pdl != 0, rope_kv_write_vec_kernel, dim3(N, split), dim3(256),
+                                        (RD / 2) * sizeof(float2), st, (__nv_bfloat16*)qkv, bias, positions, tok_seq, table,
+                                        max_blocks, (__nv_bfloat16*)kpool, (__nv_bfloat16*)vpool, freqs, H, KV, HD, RD,
+                                        pairing, page, num_pages, err);
+        return e == cudaSuccess ? 0 : (int)e;
     }
     int threads = 256;
     if (HD / 2 > threads) threads = ((HD / 2 + 31) / 32) * 32;

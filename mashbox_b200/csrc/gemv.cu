@@ -51,13 +51,20 @@ struct GemvRope {
     int* err;
 };
 
-// the activations: from global memory through the read-only path, or from the block's shared memory
+// The activations: from global memory, or from the block's shared memory.  What the kernel before this one wrote (the
+// activations, the residual stream) is read around the L1 (ld.global.cg): launched with the programmatic-serialization
+// attribute this kernel's blocks may be resident before that kernel has finished, and an SM's L1 may hold lines of its
+// output from before it was complete.
 template <bool SHARED> __device__ __forceinline__ uint4 gv_act(const bf16* p) {
-    return SHARED ? *reinterpret_cast<const uint4*>(p) : __ldg(reinterpret_cast<const uint4*>(p));
+    return SHARED ? *reinterpret_cast<const uint4*>(p) : __ldcg(reinterpret_cast<const uint4*>(p));
 }
 
-__device__ __forceinline__ void gv_load8(const float* p, float (&v)[8]) {
+__device__ __forceinline__ void gv_load8(const float* p, float (&v)[8]) {                 // a norm's weight
     const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void gv_load8_stream(const float* p, float (&v)[8]) {          // the residual stream
+    const float4 a = __ldcg(reinterpret_cast<const float4*>(p)), b = __ldcg(reinterpret_cast<const float4*>(p + 4));
     v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
 }
 
@@ -69,6 +76,9 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_kernel(const bf16* __restr
                                                              const float* __restrict__ bias, GemvRope rope) {
     extern __shared__ __align__(16) unsigned char gv_smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // These kernels are launched plainly.  With the programmatic-serialization attribute (wait at the top, dependents
+    // let go at the start or at the end of a block's work) a one-token step of the 8B shape took 4.3 ms against 3.7
+    // ms: the streaming products, which gain from it, take such steps instead when it is on.
     if (NORM) {
         __shared__ float scratch[32];
         bf16* hs = reinterpret_cast<bf16*>(gv_smem);                 // [NT][K]
@@ -81,7 +91,7 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_kernel(const bf16* __restr
             for (int j = 0; j < 4; j++) {
                 const int c = threadIdx.x + j * GV_WARPS * 32;
                 if (c < chunks8) {
-                    gv_load8(nrm.x + (size_t)n * K + c * 8, v[j]);
+                    gv_load8_stream(nrm.x + (size_t)n * K + c * 8, v[j]);
 #pragma unroll
                     for (int e = 0; e < 8; e++) ss = fmaf(v[j][e], v[j][e], ss);
                 }
@@ -216,7 +226,10 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_kernel(const bf16* __restr
 #pragma unroll
             for (int r = 0; r < GV_ROWS; r++) {
                 if (m0 + r >= M) continue;
-                if (MODE == 3) reinterpret_cast<float*>(out)[(size_t)n * M + m0 + r] += acc[r][n] + (bias ? bias[m0 + r] : 0.0f);
+                if (MODE == 3) {
+                    float* xo = reinterpret_cast<float*>(out) + (size_t)n * M + m0 + r;
+                    *xo = __ldcg(xo) + (acc[r][n] + (bias ? bias[m0 + r] : 0.0f));
+                }
                 else if (MODE == 2) reinterpret_cast<float*>(out)[(size_t)n * M + m0 + r] = acc[r][n];
                 else reinterpret_cast<bf16*>(out)[(size_t)n * M + m0 + r] = __float2bfloat16_rn(acc[r][n]);
             }
@@ -258,7 +271,7 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_long_kernel(const bf16* __
         for (int u = 0; u < 4; u++)
 #pragma unroll
             for (int n = 0; n < NT; n++) {
-                const uint4 x = __ldg(reinterpret_cast<const uint4*>(act + (size_t)n * K + (size_t)(c + STEP * u) * 8));
+                const uint4 x = __ldcg(reinterpret_cast<const uint4*>(act + (size_t)n * K + (size_t)(c + STEP * u) * 8));
 #pragma unroll
                 for (int r = 0; r < GV_ROWS; r++) acc[r][n] = dot8(w[u][r], x, acc[r][n]);
             }
@@ -269,7 +282,7 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_long_kernel(const bf16* __
         for (int r = 0; r < GV_ROWS; r++) w[r] = ld_stream16(rows[r] + (size_t)c * 8);
 #pragma unroll
         for (int n = 0; n < NT; n++) {
-            const uint4 x = __ldg(reinterpret_cast<const uint4*>(act + (size_t)n * K + (size_t)c * 8));
+            const uint4 x = __ldcg(reinterpret_cast<const uint4*>(act + (size_t)n * K + (size_t)c * 8));
 #pragma unroll
             for (int r = 0; r < GV_ROWS; r++) acc[r][n] = dot8(w[r], x, acc[r][n]);
         }
@@ -295,7 +308,10 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_long_kernel(const bf16* __
             reinterpret_cast<bf16*>(out)[(size_t)n * M + m0] = __float2bfloat16_rn((g / (1.0f + expf(-g))) * up);
         }
     } else if (m0 + r < M) {
-        if (MODE == 3) reinterpret_cast<float*>(out)[(size_t)n * M + m0 + r] += s + (bias ? bias[m0 + r] : 0.0f);
+        if (MODE == 3) {
+            float* xo = reinterpret_cast<float*>(out) + (size_t)n * M + m0 + r;
+            *xo = __ldcg(xo) + (s + (bias ? bias[m0 + r] : 0.0f));
+        }
         else if (MODE == 2) reinterpret_cast<float*>(out)[(size_t)n * M + m0 + r] = s;
         else reinterpret_cast<bf16*>(out)[(size_t)n * M + m0 + r] = __float2bfloat16_rn(s);
     }
@@ -316,14 +332,14 @@ static int gemv_launch(const void* act, const void* W, void* out, int N, int M, 
     if (K >= GV_LONG_K) {
         if (NORM || MODE == 4) return -2;                            // the normalised row is kept for K < GV_LONG_K only
         const unsigned g2 = (unsigned)units;
+        cudaError_t le = cudaSuccess;
         switch (N) {
-            case 1: gemv_long_kernel<1, MODE><<<g2, GV_WARPS * 32, 0, st>>>(a, w, out, M, K, bias); break;
-            case 2: gemv_long_kernel<2, MODE><<<g2, GV_WARPS * 32, 0, st>>>(a, w, out, M, K, bias); break;
-            case 3: gemv_long_kernel<3, MODE><<<g2, GV_WARPS * 32, 0, st>>>(a, w, out, M, K, bias); break;
-            default: gemv_long_kernel<4, MODE><<<g2, GV_WARPS * 32, 0, st>>>(a, w, out, M, K, bias); break;
+            case 1: le = mb_launch(false, gemv_long_kernel<1, MODE>, dim3(g2), dim3(GV_WARPS * 32), 0, st, a, w, out, M, K, bias); break;
+            case 2: le = mb_launch(false, gemv_long_kernel<2, MODE>, dim3(g2), dim3(GV_WARPS * 32), 0, st, a, w, out, M, K, bias); break;
+            case 3: le = mb_launch(false, gemv_long_kernel<3, MODE>, dim3(g2), dim3(GV_WARPS * 32), 0, st, a, w, out, M, K, bias); break;
+            default: le = mb_launch(false, gemv_long_kernel<4, MODE>, dim3(g2), dim3(GV_WARPS * 32), 0, st, a, w, out, M, K, bias); break;
         }
-        MB_LAUNCH_CHECK();
-        return 0;
+        return le == cudaSuccess ? 0 : (int)le;
     }
     unsigned grid = (unsigned)((units + GV_WARPS - 1) / GV_WARPS);
     size_t smem = 0;
@@ -341,14 +357,14 @@ static int gemv_launch(const void* act, const void* W, void* out, int N, int M, 
         }
         if (grid > (unsigned)(4 * sms)) grid = (unsigned)(4 * sms);
     }
+    cudaError_t le = cudaSuccess;
     switch (N) {
-        case 1: gemv_kernel<1, MODE, NORM><<<grid, GV_WARPS * 32, smem, st>>>(a, w, out, M, K, nrm, bias, rope); break;
-        case 2: gemv_kernel<2, MODE, NORM><<<grid, GV_WARPS * 32, smem, st>>>(a, w, out, M, K, nrm, bias, rope); break;
-        case 3: gemv_kernel<3, MODE, NORM><<<grid, GV_WARPS * 32, smem, st>>>(a, w, out, M, K, nrm, bias, rope); break;
-        default: gemv_kernel<4, MODE, NORM><<<grid, GV_WARPS * 32, smem, st>>>(a, w, out, M, K, nrm, bias, rope); break;
+        case 1: le = mb_launch(false, gemv_kernel<1, MODE, NORM>, dim3(grid), dim3(GV_WARPS * 32), smem, st, a, w, out, M, K, nrm, bias, rope); break;
+        case 2: le = mb_launch(false, gemv_kernel<2, MODE, NORM>, dim3(grid), dim3(GV_WARPS * 32), smem, st, a, w, out, M, K, nrm, bias, rope); break;
+        case 3: le = mb_launch(false, gemv_kernel<3, MODE, NORM>, dim3(grid), dim3(GV_WARPS * 32), smem, st, a, w, out, M, K, nrm, bias, rope); break;
+        default: le = mb_launch(false, gemv_kernel<4, MODE, NORM>, dim3(grid), dim3(GV_WARPS * 32), smem, st, a, w, out, M, K, nrm, bias, rope); break;
     }
-    MB_LAUNCH_CHECK();
-    return 0;
+    return le == cudaSuccess ? 0 : (int)le;
 }
 
 MB_API int mb_gemv_bf16(const void* act, const void* W, void* out, int N, int M, int K, cudaStream_t st) {

@@ -28,6 +28,7 @@ class ModelRunner:
         from .loading import torch_dtype
         self.model, self.cfg = model, engine_config
         self.options = dict(options or {})
+        kernels.configure(self.options)
         self.device = torch.device(engine_config.device)
         if self.device.type != "cuda" or not torch.cuda.is_available():
             raise RequestError("mashbox_b200 runs on a CUDA device only; there is no CPU path")

@@ -6,7 +6,6 @@ there, the call fails.  The only library call is the bf16 matrix product (cuBLAS
 the reference engine, too, hands its contractions to a library (src/mashbox/ops/dense16.py:73-75).
 """
 import ctypes
-import os
 
 import torch
 
@@ -69,6 +68,32 @@ def scratch_generation():
     return _scratch["generation"]
 
 
+# Programmatic dependent launch along the chain of kernels of a small step: a kernel of these libraries may start while
+# the kernel before it in the stream still runs, sets itself up (the weight-streaming products send for their first
+# weights), and waits for that kernel by itself before it touches anything a kernel writes.  One switch per library,
+# set through set_pdl(); the engine's option "pdl" turns it on.
+PDL = {"on": False}
+_PDL_SETTERS = {"gemm_stream": "mb_gemm_stream_set_pdl", "elementwise": "mb_elementwise_set_pdl",
+                "attention_tma": "mb_attn_tma_set_pdl"}
+_pdl_applied = {}
+
+
+def _apply_pdl(lib):
+    name = _PDL_SETTERS.get(lib)
+    if name is not None and _pdl_applied.get(lib) != PDL["on"]:
+        f = getattr(load_library(lib), name, None)
+        if f is not None:
+            f.argtypes = [c_int]
+            f(1 if PDL["on"] else 0)
+        _pdl_applied[lib] = PDL["on"]
+
+
+def set_pdl(on):
+    PDL["on"] = bool(on)
+    for lib in list(_pdl_applied):
+        _apply_pdl(lib)
+
+
 _fn_cache = {}
 
 
@@ -76,6 +101,8 @@ def _fn(lib, name, argtypes):
     key = (lib, name)
     f = _fn_cache.get(key)
     if f is None:
+        _pdl_applied.setdefault(lib, None)
+        _apply_pdl(lib)
         f = getattr(load_library(lib), name)
         f.argtypes = argtypes
         f.restype = c_int
@@ -227,8 +254,6 @@ def linear_tc5(a, w, out, mode="plain"):
 # the FMA pipe) already costs more than the stream.  GEMV[mode] = the most tokens the engine gives the kernel (0: never);
 # "fused": the forms that normalise the residual stream themselves or add their product into it (see small_fused_supports).
 GEMV = {"swiglu": 1, "plain": 1, "fused": 1}
-if os.environ.get("MASHBOX_GEMV_TOKENS"):          # a tuning knob: the same limit for the three kinds
-    GEMV = {k: int(os.environ["MASHBOX_GEMV_TOKENS"]) for k in GEMV}
 
 
 def gemv_supports(N, K, mode="plain"):
@@ -291,8 +316,21 @@ def linear_gemv(a, w, out, mode="plain"):
 # 2.3, down with the residual add 26.5 / 23.3; the whole decode step at batch 8 (the output head too): 1,720 tokens/s
 # against 1,608 with the library's products.  STREAM["tokens"]: the most tokens the engine gives them (0: never).
 STREAM = {"tokens": 16}
-if os.environ.get("MASHBOX_STREAM_TOKENS"):        # a tuning knob
-    STREAM = {"tokens": int(os.environ["MASHBOX_STREAM_TOKENS"])}
+
+
+def configure(options):
+    """Engine options that choose between this package's kernels, applied process-wide (the kernels' faces are module
+    functions).  pdl (default on): programmatic dependent launch along the chain of kernels of a small step; with it
+    the weight-streaming products take steps of one token too (measured on the 8B shape at one token per step: 3.41 ms
+    against 3.68 ms for the matrix-vector kernels, which lose 0.7 ms when they are launched that way themselves).
+    gemv_tokens / stream_tokens: the most tokens of a step the matrix-vector / weight-streaming products take (0: never)."""
+    pdl = bool(options.get("pdl", True))
+    set_pdl(pdl)
+    for k in GEMV:
+        GEMV[k] = int(options.get("gemv_tokens", 0 if pdl else 1))
+    STREAM["tokens"] = int(options.get("stream_tokens", 16))
+
+
 _stream_scratch = {}
 
 
