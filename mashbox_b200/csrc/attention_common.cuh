@@ -17,6 +17,14 @@ struct AttnParams {
     int page_shift;                         // log2(page) when the page size is a power of two, else -1
     float scale_log2;
     int* err;
+    // the decode form of the TMA kernel with the rotate-and-store step folded in (every sequence brings ONE token): q
+    // points at rows [q heads | k heads | v heads] as the q/k/v product left them; the kernel adds rope_bias ((H + 2 KV)
+    // HD floats, or null), rotates q and k by the token's position (rope_freqs: rope_rd / 2 angles per position step,
+    // or null; rope_pairing 0 adjacent pairs, 1 halves) and writes k and v into the token's page
+    int fuse_rope = 0;
+    const float* rope_bias = nullptr;
+    const float* rope_freqs = nullptr;
+    int rope_rd = 0, rope_pairing = 0;
 };
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, int bytes) {

@@ -51,7 +51,25 @@ template <int HD> __device__ __forceinline__ int kv_off(int row, int c) {
     return (c >> 3) * (64 * 64) + row * 64 + (((c & 7) ^ (row & 7)) << 3);
 }
 
-template <int HD, bool DECODE, int STAGES>
+// bias and rotation of the pair (e0, e1) of a head's row: pair i of HD / 2; rotated pairs are (2i, 2i + 1) or, with the
+// halves pairing, (i, i + RD / 2); the pairs past the rotated part pass through.  The arithmetic of
+// rope_kv_write_vec_kernel (elementwise.cu): float from bf16, + bias, rotation by pos * freq, back to bf16.
+struct RopePair { int e0, e1, pair; };
+__device__ __forceinline__ RopePair rope_pair(int i, int rd, int pairing) {
+    const int rh = rd / 2;
+    if (pairing == 0) return RopePair{2 * i, 2 * i + 1, i < rh ? i : -1};
+    if (i < rh) return RopePair{i, i + rh, i};
+    return RopePair{rd + 2 * (i - rh), rd + 2 * (i - rh) + 1, -1};
+}
+__device__ __forceinline__ void rope_apply(float& a, float& b, int pair, int pos, const float* __restrict__ freqs) {
+    if (pair < 0 || freqs == nullptr) return;
+    float s, c;
+    sincosf((float)pos * freqs[pair], &s, &c);
+    const float ra = a * c - b * s, rb = a * s + b * c;
+    a = ra; b = rb;
+}
+
+template <int HD, bool DECODE, int STAGES, bool ROPE>
 __global__ void __launch_bounds__(160, 2) attn_tma_kernel(const AttnParams P, const __grid_constant__ CUtensorMap kmap,
                                                         const __grid_constant__ CUtensorMap vmap) {
     constexpr int BM = DECODE ? 16 : 64, BN = 64, CH = HD / 8;
@@ -65,7 +83,8 @@ __global__ void __launch_bounds__(160, 2) attn_tma_kernel(const AttnParams P, co
         (reinterpret_cast<uintptr_t>(smem_unaligned) + 1023) & ~static_cast<uintptr_t>(1023));
     bf16* kvs = reinterpret_cast<bf16*>(smem_raw);                       // STAGES x (K tile, V tile), 1024-byte aligned
     bf16* qs = kvs + (size_t)STAGES * 2 * TILE;                          // BM x HD, swizzled as in attention_mma.cu
-    uint64_t* bars = reinterpret_cast<uint64_t*>(qs + BM * HD);          // full[STAGES], empty[STAGES]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(qs + BM * HD);          // full[STAGES], empty[STAGES], the merge's flag
+    bf16* newkv = reinterpret_cast<bf16*>(bars + 2 * STAGES + 2);         // ROPE: the token's own key and value rows
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
 
     // Up to pdl_wait() the kernel reads the step's own arrays only (which no kernel writes); the queries, the pages --
@@ -99,7 +118,10 @@ __global__ void __launch_bounds__(160, 2) attn_tma_kernel(const AttnParams P, co
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
     }
     __syncthreads();
-    pdl_wait();
+    // With the rotation folded in, nothing the producer warp reads is written by a kernel of this step: the pages hold
+    // the keys and values of earlier steps (the token's own rows never come from the page, see below) and the block table
+    // is the step's input.  So it does not wait: the first tiles are on their way while the q/k/v product still runs.
+    if (!ROPE || warp != 4) pdl_wait();
 
     if (warp == 4) {
         // ---------------------------------------------------------------- producer
@@ -173,6 +195,52 @@ __global__ void __launch_bounds__(160, 2) attn_tma_kernel(const AttnParams P, co
 
     cp_async_wait<0>();
     consumer_sync();
+    if (ROPE) {
+        // The rotate-and-store step of a one-token sequence, folded in.  Every block rotates the G query rows it has
+        // just fetched, in shared memory.  The block whose splits hold the token's own key tile also makes the token's
+        // key and value rows (bias, rotation), writes them to the token's page for the steps to come, and keeps them in
+        // shared memory: when that tile arrives it holds whatever the page held before at the token's slot, and the warp
+        // that owns the slot's keys puts the new rows there before it reads the tile.
+        const int pos = pos0, rd = P.rope_rd, pairing = P.rope_pairing;
+        for (int idx = tid; idx < G * (HD / 2); idx += 128) {
+            const int row = idx / (HD / 2);
+            const RopePair rp = rope_pair(idx % (HD / 2), rd, pairing);
+            bf16* p0 = qs + swz<HD>(row, rp.e0 >> 3) + (rp.e0 & 7);
+            bf16* p1 = qs + swz<HD>(row, rp.e1 >> 3) + (rp.e1 & 7);
+            float a = __bfloat162float(*p0), b = __bfloat162float(*p1);
+            if (P.rope_bias) {
+                const float* bh = P.rope_bias + (size_t)(kvh * G + row) * HD;
+                a += bh[rp.e0]; b += bh[rp.e1];
+            }
+            rope_apply(a, b, rp.pair, pos, P.rope_freqs);
+            *p0 = __float2bfloat16_rn(a);
+            *p1 = __float2bfloat16_rn(b);
+        }
+        if (t_begin <= n_tiles - 1 && n_tiles - 1 < t_end) {
+            const int pg = tb[pos / P.page];
+            const bool paged = pg >= 0 && pg < P.num_pages;
+            if (!paged && tid == 0) mb_set_error(P.err, pg < 0 ? MB_ERR_PAGE_MISSING : MB_ERR_PAGE_RANGE);
+            const size_t slot = (((size_t)(paged ? pg : 0) * P.KV + kvh) * P.page + pos % P.page) * HD;
+            const unsigned short* raw = reinterpret_cast<const unsigned short*>(P.q + (size_t)tok0 * P.q_stride);
+            for (int idx = tid; idx < HD; idx += 128) {
+                const bool is_v = idx >= HD / 2;
+                const RopePair rp = is_v ? RopePair{2 * (idx - HD / 2), 2 * (idx - HD / 2) + 1, -1} : rope_pair(idx, rd, pairing);
+                const int head = is_v ? P.H + P.KV + kvh : P.H + kvh;
+                float a = __uint_as_float((uint32_t)__ldcg(raw + (size_t)head * HD + rp.e0) << 16);
+                float b = __uint_as_float((uint32_t)__ldcg(raw + (size_t)head * HD + rp.e1) << 16);
+                if (P.rope_bias) { a += P.rope_bias[(size_t)head * HD + rp.e0]; b += P.rope_bias[(size_t)head * HD + rp.e1]; }
+                rope_apply(a, b, rp.pair, pos, P.rope_freqs);
+                const bf16 ra = __float2bfloat16_rn(a), rb = __float2bfloat16_rn(b);
+                bf16* mine = newkv + (is_v ? HD : 0);
+                mine[rp.e0] = ra; mine[rp.e1] = rb;
+                if (paged) {
+                    bf16* pool = const_cast<bf16*>(is_v ? P.vpool : P.kpool) + slot;
+                    pool[rp.e0] = ra; pool[rp.e1] = rb;
+                }
+            }
+        }
+        consumer_sync();
+    }
     uint32_t qf[KS][4];
 #pragma unroll
     for (int ks = 0; ks < KS; ks++)
@@ -184,6 +252,16 @@ __global__ void __launch_bounds__(160, 2) attn_tma_kernel(const AttnParams P, co
         const bf16* kt = kvs + (size_t)s * 2 * TILE;
         const bf16* vt = kt + TILE;
         const int kb = lo_al + t * BN;
+        if (ROPE && DECODE && t == n_tiles - 1 && pos0 - kb >= nbase && pos0 - kb < nbase + 16) {
+            // the token's own slot is among this warp's keys of the tile: its new key and value rows go in
+            const int rowk = pos0 - kb;
+            for (int c = lane; c < 2 * CH; c += 32) {
+                bf16* tile = const_cast<bf16*>(c < CH ? kt : vt);
+                *reinterpret_cast<uint4*>(tile + kv_off<HD>(rowk, c % CH)) =
+                    *reinterpret_cast<const uint4*>(newkv + (c < CH ? 0 : HD) + (c % CH) * 8);
+            }
+            __syncwarp();
+        }
 
         float sc[NT][4];
 #pragma unroll
@@ -438,21 +516,21 @@ static int pool_map(const void* pool, long long rows, int HD, int page, CUtensor
 
 MB_PDL_SWITCH(mb_attn_tma_set_pdl)
 
-template <int HD, bool DECODE, int STAGES>
+template <int HD, bool DECODE, int STAGES, bool ROPE = false>
 static int launch_tma(const AttnParams& P, const CUtensorMap& kmap, const CUtensorMap& vmap, int n_items, cudaStream_t st) {
     constexpr int BM = DECODE ? 16 : 64;
-    const size_t smem = 1024 + (size_t)STAGES * 2 * 64 * HD * 2 + (size_t)BM * HD * 2 + 2 * STAGES * 8 + 16;
+    const size_t smem = 1024 + (size_t)STAGES * 2 * 64 * HD * 2 + (size_t)BM * HD * 2 + 2 * STAGES * 8 + 16 + (ROPE ? 4 * HD : 0);
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_tma_kernel<HD, DECODE, STAGES>,
+        cudaError_t e = cudaFuncSetAttribute(attn_tma_kernel<HD, DECODE, STAGES, ROPE>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         // two blocks per SM need most of the SM's memory as shared memory: ask for the largest carve-out
-        cudaFuncSetAttribute(attn_tma_kernel<HD, DECODE, STAGES>, cudaFuncAttributePreferredSharedMemoryCarveout,
+        cudaFuncSetAttribute(attn_tma_kernel<HD, DECODE, STAGES, ROPE>, cudaFuncAttributePreferredSharedMemoryCarveout,
                              cudaSharedmemCarveoutMaxShared);
         configured = true;
     }
-    const cudaError_t e = mb_launch(mb_pdl != 0, attn_tma_kernel<HD, DECODE, STAGES>, dim3(n_items, P.KV), dim3(160), smem, st,
+    const cudaError_t e = mb_launch(mb_pdl != 0, attn_tma_kernel<HD, DECODE, STAGES, ROPE>, dim3(n_items, P.KV), dim3(160), smem, st,
                                     P, kmap, vmap);
     return e == cudaSuccess ? 0 : (int)e;
 }
@@ -461,13 +539,18 @@ MB_API int mb_attn_tma_supports(int HD, int page) {
     return (HD == 64 || HD == 128) && (page == 8 || page == 16 || page == 32 || page == 64);
 }
 
-MB_API int mb_attn_tma_bf16(const void* q, int q_stride, void* out, const void* kpool, const void* vpool,
-                            const void* items, int n_items, int decode, const int* q_start, const int* q_len,
-                            const int* pos0, const int* part_base, const int* seq_row, const int* table, int max_blocks,
-                            float* part_o, float* part_ml, int max_splits, int H, int KV, int HD, int page, int num_pages,
-                            int window, float scale, int* counters, int* err, cudaStream_t st) {
+// fuse: 0, or 1 for the decode form with the rotate-and-store step folded in (then every sequence of the step brings ONE
+// token, q points at the rows [q | k | v] the q/k/v product left, and bias / freqs / RD / pairing are those of
+// mb_rope_kv_write_bf16)
+static int attn_tma_run(const void* q, int q_stride, void* out, const void* kpool, const void* vpool,
+                        const void* items, int n_items, int decode, const int* q_start, const int* q_len,
+                        const int* pos0, const int* part_base, const int* seq_row, const int* table, int max_blocks,
+                        float* part_o, float* part_ml, int max_splits, int H, int KV, int HD, int page, int num_pages,
+                        int window, float scale, int* counters, int* err, cudaStream_t st, int fuse, const float* bias,
+                        const float* freqs, int RD, int pairing) {
     if (n_items == 0) return 0;
     if (!mb_attn_tma_supports(HD, page) || KV < 1 || H % KV || KV > 65535) return -2;
+    if (fuse && (!decode || H / KV > 16 || RD % 2 || RD > HD || RD < 0 || !kpool || !vpool)) return -2;
     AttnParams P;
     P.q = (const bf16*)q; P.q_stride = q_stride; P.out = (bf16*)out;
     P.kpool = (const bf16*)kpool; P.vpool = (const bf16*)vpool;
@@ -480,14 +563,41 @@ MB_API int mb_attn_tma_bf16(const void* q, int q_stride, void* out, const void* 
     for (int sft = 0; sft < 31; sft++) if ((1 << sft) == page) P.page_shift = sft;
     P.scale_log2 = scale * 1.4426950408889634f;
     P.err = err;
+    P.fuse_rope = fuse; P.rope_bias = bias; P.rope_freqs = freqs; P.rope_rd = freqs ? RD : 0; P.rope_pairing = pairing;
     CUtensorMap kmap, vmap;
     const long long rows = (long long)num_pages * KV * page;
     int rc = pool_map(kpool, rows, HD, page, &kmap);
     if (rc) return rc;
     rc = pool_map(vpool, rows, HD, page, &vmap);
     if (rc) return rc;
+    if (fuse) return HD == 128 ? launch_tma<128, true, 3, true>(P, kmap, vmap, n_items, st)
+                               : launch_tma<64, true, 4, true>(P, kmap, vmap, n_items, st);
     if (HD == 128) return decode ? launch_tma<128, true, 3>(P, kmap, vmap, n_items, st)
                                  : launch_tma<128, false, 2>(P, kmap, vmap, n_items, st);
     return decode ? launch_tma<64, true, 4>(P, kmap, vmap, n_items, st)
                   : launch_tma<64, false, 3>(P, kmap, vmap, n_items, st);
+}
+
+MB_API int mb_attn_tma_bf16(const void* q, int q_stride, void* out, const void* kpool, const void* vpool,
+                            const void* items, int n_items, int decode, const int* q_start, const int* q_len,
+                            const int* pos0, const int* part_base, const int* seq_row, const int* table, int max_blocks,
+                            float* part_o, float* part_ml, int max_splits, int H, int KV, int HD, int page, int num_pages,
+                            int window, float scale, int* counters, int* err, cudaStream_t st) {
+    return attn_tma_run(q, q_stride, out, kpool, vpool, items, n_items, decode, q_start, q_len, pos0, part_base, seq_row,
+                        table, max_blocks, part_o, part_ml, max_splits, H, KV, HD, page, num_pages, window, scale,
+                        counters, err, st, 0, nullptr, nullptr, 0, 0);
+}
+
+// The decode form for a step in which every sequence brings one token, with the rotate-and-store step folded in: qkv
+// (N, (H + 2 KV) HD) as the q/k/v product left it.  The result equals mb_rope_kv_write_bf16 followed by
+// mb_attn_tma_bf16 bit for bit (qkv itself is left as it was: the rotated queries exist in shared memory only).
+MB_API int mb_attn_tma_rope_bf16(const void* qkv, int q_stride, void* out, void* kpool, void* vpool, const void* items,
+                                 int n_items, const int* q_start, const int* q_len, const int* pos0, const int* part_base,
+                                 const int* seq_row, const int* table, int max_blocks, float* part_o, float* part_ml,
+                                 int max_splits, int H, int KV, int HD, int page, int num_pages, int window, float scale,
+                                 int* counters, int* err, const float* bias, const float* freqs, int RD, int pairing,
+                                 cudaStream_t st) {
+    return attn_tma_run(qkv, q_stride, out, kpool, vpool, items, n_items, 1, q_start, q_len, pos0, part_base, seq_row, table,
+                        max_blocks, part_o, part_ml, max_splits, H, KV, HD, page, num_pages, window, scale, counters,
+                        err, st, 1, bias, freqs, RD, pairing);
 }

@@ -493,11 +493,20 @@ def attention_tma_merges(n_items, KV):
     return n_items * KV <= MERGE_COUNTERS
 
 
+def attention_tma_folds_rotation(G):
+    """True when attention_tma can take the rotate-and-store step of a step of one-token sequences in (rope=...)"""
+    return 1 <= G <= 16
+
+
 def attention_tma(q, q_stride, out, kpool, vpool, items, n_items, decode, q_start, q_len, pos0, part_base, seq_row,
-                  table, part_o, part_ml, max_splits, H, KV, HD, page, num_pages, window, scale, err, merge=False):
+                  table, part_o, part_ml, max_splits, H, KV, HD, page, num_pages, window, scale, err, merge=False,
+                  rope=None):
     """The same contract as attention_mma, with K/V tiles loaded by TMA (head sizes 64 and 128, pages of 8 to 64).
     merge: the last block of every split group merges the group's partial results and writes `out`, so no
-    attention_merge is needed afterwards (only when attention_tma_merges(n_items, KV))."""
+    attention_merge is needed afterwards (only when attention_tma_merges(n_items, KV)).
+    rope = (bias or None, freqs or None, RD, pairing): the step's sequences bring ONE token each and q is the whole
+    (N, (H + 2 KV) HD) output of the q/k/v product; the kernel does what rope_kv_write would have done before it (bias,
+    rotation of q and k, k and v into the token's page) -- the same bits, one launch fewer.  q itself is not changed."""
     _cuda(q, out, kpool, vpool, items, q_start, q_len, pos0, part_base, table, part_o, part_ml)
     counters = None
     if merge:
@@ -508,12 +517,26 @@ def attention_tma(q, q_stride, out, kpool, vpool, items, n_items, decode, q_star
             _merge_counters[key] = torch.zeros(MERGE_COUNTERS, dtype=torch.int32, device=q.device)
             _scratch["generation"] += 1
         counters = _merge_counters[key]
-    f = _fn("attention_tma", "mb_attn_tma_bf16",
-            [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
-             c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p] + [c_int] * 7 + [c_float, c_void_p, c_void_p, c_void_p])
-    code = f(_p(q), q_stride, _p(out), _p(kpool), _p(vpool), _p(items), n_items, 1 if decode else 0, _p(q_start),
-             _p(q_len), _p(pos0), _p(part_base), _p(seq_row), _p(table), table.shape[1], _p(part_o), _p(part_ml),
-             max_splits, H, KV, HD, page, num_pages, window or 0, float(scale), _p(counters), _p(err), _stream())
+    if rope is not None:
+        if not decode:
+            raise KernelError("attention_tma: the rotation is folded into the decode form only")
+        bias, freqs, RD, pairing = rope
+        _cuda(bias, freqs)
+        f = _fn("attention_tma", "mb_attn_tma_rope_bf16",
+                [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                 c_void_p, c_void_p, c_int, c_void_p, c_void_p] + [c_int] * 7 + [c_float, c_void_p, c_void_p, c_void_p,
+                                                                                c_void_p, c_int, c_int, c_void_p])
+        code = f(_p(q), q_stride, _p(out), _p(kpool), _p(vpool), _p(items), n_items, _p(q_start), _p(q_len), _p(pos0),
+                 _p(part_base), _p(seq_row), _p(table), table.shape[1], _p(part_o), _p(part_ml), max_splits, H, KV, HD,
+                 page, num_pages, window or 0, float(scale), _p(counters), _p(err), _p(bias), _p(freqs), int(RD),
+                 int(pairing), _stream())
+    else:
+        f = _fn("attention_tma", "mb_attn_tma_bf16",
+                [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                 c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p] + [c_int] * 7 + [c_float, c_void_p, c_void_p, c_void_p])
+        code = f(_p(q), q_stride, _p(out), _p(kpool), _p(vpool), _p(items), n_items, 1 if decode else 0, _p(q_start),
+                 _p(q_len), _p(pos0), _p(part_base), _p(seq_row), _p(table), table.shape[1], _p(part_o), _p(part_ml),
+                 max_splits, H, KV, HD, page, num_pages, window or 0, float(scale), _p(counters), _p(err), _stream())
     if code == -6:
         raise KernelError("attention_tma: the driver refused the tensor map of the cache pool")
     _check(code, "attention_tma")

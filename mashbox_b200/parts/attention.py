@@ -143,6 +143,12 @@ class Attention:
         table = group.device_table
         page, pages = ctx.cache.page_size, ctx.cache.num_pages
         rot = self.position.rotation() if self.position is not None else (None, HD, 0)
+        # A step in which every sequence brings one token (N == S: that follows from the lengths of the step's arrays):
+        # the decode form of the TMA attention kernel rotates, stores and attends in one launch.
+        folded = (rot is not None and run.write and N == ctx.S and self.uses_mma(ctx)
+                  and ctx.options.get("attention_kernel", "tma") == "tma" and ops.attention_tma_supports(HD, page)
+                  and ops.attention_tma_folds_rotation(H // KV) and ctx.options.get("attention_folds_rotation", True)
+                  and not (normed is not None and ops.small_qkv_supports(N, self.D)))
         if normed is not None and rot is not None and ops.small_qkv_supports(N, self.D):
             # a step of very few tokens: norm, product, rotation and the cache write in one kernel
             x, norm = normed
@@ -165,9 +171,10 @@ class Attention:
                 self.position.apply(ctx, qkv, H, KV, HD)
             else:
                 freqs, rd, pairing = rot
-            ops.rope_kv_write(qkv, self.bqkv, ctx.dev("positions"), ctx.dev("tok_row"), table,
-                              kpool if run.write else None, vpool if run.write else None, freqs, H, KV, HD, rd, pairing,
-                              page, pages, ctx.err)
+            if not folded:
+                ops.rope_kv_write(qkv, self.bqkv, ctx.dev("positions"), ctx.dev("tok_row"), table,
+                                  kpool if run.write else None, vpool if run.write else None, freqs, H, KV, HD, rd,
+                                  pairing, page, pages, ctx.err)
         out = ctx.ws.get("attn_out", N, (H * HD,), ctx.dtype)
         if self.uses_mma(ctx):
             plan = ctx.memo[self.plan_key()]
@@ -184,6 +191,8 @@ class Attention:
             fused = (tma and n_part > 0 and ctx.options.get("attention_fused_merge", True)
                      and ops.attention_tma_merges(max(plan["n_pre"], plan["n_dec"]), KV))
             extra = dict(merge=True) if fused else {}
+            if folded:
+                extra["rope"] = (self.bqkv, freqs, rd, pairing)
             if plan["tc5"] and plan["n_pre"]:
                 ops.attention_tc5(qkv, width, out, kpool, vpool, ctx.dev(nm + "pre"), plan["n_pre"], ctx.dev("q_start"),
                                   ctx.dev("q_len"), ctx.dev("pos0"), ctx.dev("seq_row"), table, H, KV, HD, page, pages,

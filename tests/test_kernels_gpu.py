@@ -682,3 +682,51 @@ def test_logit_trace_hash_and_gap(V):
         flipped[0, V // 3] = torch.nextafter(flipped[0, V // 3], torch.tensor(float("inf")))
         K.logit_trace(flipped.to(DEV), out)
         assert K.read_logit_trace(out)[0][0] != got[0][0]    # one changed bit changes the hash
+
+
+@pytest.mark.parametrize("HD,H,KV,page,window,splits,pairing,RD,bias", [
+    (128, 8, 2, 16, None, 4, 0, 128, False), (128, 32, 8, 16, None, 8, 0, 128, True), (64, 6, 2, 32, 300, 2, 1, 32, True),
+    (64, 32, 8, 8, None, 1, 0, 64, False), (128, 16, 1, 64, None, 2, 1, 128, False), (128, 5, 5, 16, 70, 1, 0, 64, True)])
+def test_decode_attention_with_the_rotation_folded_in(HD, H, KV, page, window, splits, pairing, RD, bias):
+    """one-token sequences: attention_tma(rope=...) on the raw output of the q/k/v product gives the bits of
+    rope_kv_write followed by attention_tma, in the outputs and in the pages (a token at the first slot of a page, at
+    the last, alone in its sequence, at a tile's edge; with a window; biases; partial rotation; both pairings)"""
+    K = ops()
+    lengths = [900, 64, 65, 1, 333, 128, 16]
+    Gq = H // KV
+    seqs = G.PagedSequences(lengths, [1] * len(lengths), H, KV, HD, page, torch.bfloat16, seed=31).round().build()
+    g = torch.Generator().manual_seed(5)
+    N, width = len(lengths), (H + 2 * KV) * HD
+    qkv = torch.randn(N, width, generator=g).to(G.DEV, torch.bfloat16)
+    b = (0.3 * torch.randn(width, generator=g)).to(G.DEV) if bias else None
+    freqs = torch.from_numpy(plain.rope_frequencies(10000.0, RD, None)).to(G.DEV)
+    dec, pre, part_base, part_tok = G.mma_items(seqs, Gq, splits)
+    assert not pre
+    items = G.i32(np.asarray(dec).reshape(-1))
+
+    def attend(qkv_in, kpool, vpool, rope):
+        out = torch.full((N, H * HD), float("nan"), device=G.DEV, dtype=torch.bfloat16)
+        err = K.new_error_word(G.DEV)
+        ms = max(splits, 1)
+        n_part = len(part_tok) // 2
+        part_o = torch.full((max(1, n_part) * H * ms, HD), float("nan"), device=G.DEV)
+        part_ml = torch.full((max(1, n_part) * H * ms, 2), float("nan"), device=G.DEV)
+        K.attention_tma(qkv_in, width, out, kpool, vpool, items, len(dec), True, seqs.q_start, seqs.q_len, seqs.pos0,
+                        G.i32(part_base), seqs.seq_row, seqs.table, part_o, part_ml, ms, H, KV, HD, page, seqs.num_pages,
+                        window, HD ** -0.5, err, merge=n_part > 0, rope=rope)
+        K.check_error_word(err)
+        return out
+
+    k1, v1, q1 = seqs.kpool.clone(), seqs.vpool.clone(), qkv.clone()
+    err = K.new_error_word(G.DEV)
+    K.rope_kv_write(q1, b, seqs.positions, seqs.tok_row, seqs.table, k1, v1, freqs, H, KV, HD, RD, pairing, page,
+                    seqs.num_pages, err)
+    K.check_error_word(err)
+    want = attend(q1, k1, v1, None)
+    k2, v2, q2 = seqs.kpool.clone(), seqs.vpool.clone(), qkv.clone()
+    got = attend(q2, k2, v2, (b, freqs, RD, pairing))
+    assert torch.equal(q2, qkv)                                         # the product's output is left alone
+    assert torch.equal(k2, k1) and torch.equal(v2, v1)
+    assert not torch.isnan(got.float()).any() and torch.equal(got, want)
+    # and the new token's key really took part: attending without it gives something else
+    assert not torch.equal(want, attend(q1, seqs.kpool, seqs.vpool, None))
