@@ -6,6 +6,7 @@ decode at batch 1 and 64 on the same JSON line.
     python bench.py --workload 3b-serving   # 64 requests of mixed lengths through Engine.admit/step, Llama-3.2-3B shape
     python bench.py --workload 1b-long      # 4 prompts of 32,768 tokens in 2,048-token portions, then 256 sampled steps
     python bench.py --kernels               # single kernels against the library on the layer's shapes
+    python bench.py --attention --head-dim 64 --queries 2048 --keys 32768     # the attention kernels alone
     python bench.py --impl reference        # the reference arm (unavailable here: it needs JAX and a TPU)
 
 A "step" is one decode step of the whole batch.  `value` is timed on the device with CUDA events around K calls of the
@@ -368,6 +369,84 @@ def run_workload(a):
     return 0
 
 
+def run_attention(a):
+    """Times the attention kernels alone on one layer's cache (one JSON line; also the workload of their ncu captures):
+    the prompt form -- a portion of `--queries` tokens at the end of `--keys` tokens of context, tcgen05 kernel against
+    the mma.sync kernel -- and the decode form, `--batch` one-token sequences of `--keys` tokens each."""
+    import numpy as np
+    import torch
+    from mashbox_b200 import ops
+    dev = "cuda:0"
+    H, KV, HD, page = a.heads, a.kv_heads, a.head_dim, 16
+    Q, ctx, B = a.queries, a.keys, a.batch
+    G = H // KV
+    gen = torch.Generator(device=dev).manual_seed(0)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    err = ops.new_error_word(dev)
+
+    def timed(f, n):
+        for _ in range(3):
+            f()
+        ts = []
+        for _ in range(n):
+            flush.zero_()
+            e0, e1 = ev(), ev()
+            e0.record()
+            f()
+            e1.record()
+            torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1) * 1e3)
+        return statistics.median(ts)
+
+    out = {"config": dict(heads=H, kv_heads=KV, head_dim=HD, page_size=page)}
+    # ---- prompt form: one sequence, its last Q tokens are the step's
+    pages = -(-ctx // page)
+    pool = (torch.randn(2, pages, KV, page, HD, device=dev, generator=gen) * 0.5).to(torch.bfloat16)
+    table = torch.randperm(pages, generator=torch.Generator().manual_seed(1)).to(torch.int32).to(dev).reshape(1, pages)
+    q = (torch.randn(Q, H * HD, device=dev, generator=gen) * 0.5).to(torch.bfloat16)
+    o = torch.empty(Q, H * HD, device=dev, dtype=torch.bfloat16)
+    args = (i32([0]), i32([Q]), i32([ctx - Q]))
+    zero, none = i32([0]), i32([-1])
+    flops = 4.0 * HD * H * sum(min(ctx, ctx - Q + t + 1) for t in range(Q))
+    res = {"queries": Q, "keys": ctx}
+    if ops.attention_tc5_supports(HD, page):
+        rows = ops.attention_tc5_rows()
+        items = i32([v for m in range(-(-Q * G // rows) - 1, -1, -1) for v in (0, m, 0, 1)])
+        n = items.numel() // 4
+        us = timed(lambda: ops.attention_tc5(q, H * HD, o, pool[0], pool[1], items, n, *args, zero, table, H, KV, HD, page,
+                                             pages, None, HD ** -0.5, err), a.steps)
+        res["tcgen05_us"], res["tcgen05_tflops"] = us, flops / us / 1e6
+    items = i32([v for m in range(-(-Q * G // 64) - 1, -1, -1) for v in (0, m, 0, 1)])
+    n = items.numel() // 4
+    us = timed(lambda: ops.attention_tma(q, H * HD, o, pool[0], pool[1], items, n, False, *args, none, zero, table,
+                                         None, None, 1, H, KV, HD, page, pages, None, HD ** -0.5, err), a.steps)
+    res["mma_sync_us"], res["mma_sync_tflops"] = us, flops / us / 1e6
+    out["prompt_form"] = res
+    del pool
+    # ---- decode form: B sequences of ctx tokens, one token each, the keys cut into the splits the mixer would choose
+    pages = B * -(-ctx // page)
+    pool = (torch.randn(2, pages, KV, page, HD, device=dev, generator=gen) * 0.5).to(torch.bfloat16)
+    table = torch.arange(pages, dtype=torch.int32, device=dev).reshape(B, -1)
+    q = (torch.randn(B, H * HD, device=dev, generator=gen) * 0.5).to(torch.bfloat16)
+    o = torch.empty(B, H * HD, device=dev, dtype=torch.bfloat16)
+    ns = max(1, min(32, -(-296 // (B * KV)), ctx // 128))
+    ns = 1 << (ns.bit_length() - 1)
+    items = i32([v for s in range(B) for sp in range(ns) for v in (s, 0, sp, ns)])
+    part_o, part_ml = torch.empty(B * H * ns, HD, device=dev), torch.empty(B * H * ns, 2, device=dev)
+    rows, ones, last = i32(list(range(B))), i32([1] * B), i32([ctx - 1] * B)
+    us = timed(lambda: ops.attention_tma(q, H * HD, o, pool[0], pool[1], items, B * ns, True, rows, ones, last, rows, rows,
+                                         table, part_o, part_ml, ns, H, KV, HD, page, pages, None, HD ** -0.5, err,
+                                         merge=ns > 1), a.steps)
+    nbytes = B * ctx * KV * HD * 2 * 2
+    out["decode_form"] = {"batch": B, "keys": ctx, "splits": ns, "us": us, "gbs": nbytes / us / 1e3,
+                          "frac_of_hbm_peak": nbytes / us / 1e3 / peaks()["hbm_gbs"]}
+    ops.check_error_word(err)
+    print(json.dumps({"impl": "ours", "attention": out, "note": "CUDA-event time of single launches after an L2 flush"}))
+    return 0
+
+
 def run_kernels(a):
     """Times this repo's matrix-product and attention kernels next to the library's on the layer shapes of the
     configuration (2,048 tokens and a decode batch), one JSON line; also the workload of the ncu captures of single
@@ -489,6 +568,13 @@ def main():
     ap.add_argument("--no-graphs", action="store_true", help="launch every kernel directly (for profilers)")
     ap.add_argument("--options", default="", help="JSON of engine options (kernel choices), for experiments")
     ap.add_argument("--kernels", action="store_true", help="time single kernels against the library instead of the model")
+    ap.add_argument("--attention", action="store_true", help="time the attention kernels alone (--heads --kv-heads --head-dim "
+                    "--queries --keys --batch)")
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--kv-heads", type=int, default=8)
+    ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--queries", type=int, default=2048)
+    ap.add_argument("--keys", type=int, default=8192)
     ap.add_argument("--workload", default="", choices=("", "3b-serving", "1b-long"),
                     help="run one of the other workloads of the baseline through Engine.admit/step instead")
     ap.add_argument("--requests", type=int, default=0, help="workloads: fewer requests than the workload names")
@@ -505,6 +591,8 @@ def main():
     a.warmup = max(a.warmup, 3)
     if a.workload:
         return run_workload(a)
+    if a.attention:
+        return run_attention(a)
     return run_kernels(a) if a.kernels else run_ours(a)
 
 

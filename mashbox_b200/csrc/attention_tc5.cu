@@ -30,8 +30,8 @@
 #define T5_BN 128
 #define T5_HALF (128 * 128)                    // bytes of 128 rows of 64 bf16: what one 128-byte-swizzled column half of a tile takes
 #ifndef T5_POLY
-#define T5_POLY 0                              // pairs in eight whose 2^x is a polynomial on the FMA units
-#endif
+#define T5_POLY 0                              // pairs in eight whose 2^x is a polynomial on the FMA units (it paid at
+#endif                                         // neither head size: 938 us -> 994 / 1,016 / 1,082 us with 2 / 4 / 6 at 64)
 // 2^x with the special-function unit (ex2.approx.ftz: 2 ulp; -inf gives 0)
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
