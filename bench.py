@@ -7,6 +7,7 @@ decode at batch 1 and 64 on the same JSON line.
     python bench.py --workload 1b-long      # 4 prompts of 32,768 tokens in 2,048-token portions, then 256 sampled steps
     python bench.py --kernels               # single kernels against the library on the layer's shapes
     python bench.py --attention --head-dim 64 --queries 2048 --keys 32768     # the attention kernels alone
+    python bench.py --timeline --batch 8    # when the kernels of one layer of a decode step start and end
     python bench.py --impl reference        # the reference arm (unavailable here: it needs JAX and a TPU)
 
 A "step" is one decode step of the whole batch.  `value` is timed on the device with CUDA events around K calls of the
@@ -369,6 +370,61 @@ def run_workload(a):
     return 0
 
 
+def run_timeline(a):
+    """Start and end of every kernel of one decode step inside its captured graph (CUPTI through torch.profiler; no
+    ncu): with programmatic dependent launch the kernels of a step overlap, so their durations alone say little; the
+    line gives, for one layer in the middle of the model, when each kernel started, when it ended and how long after
+    the END of the kernel before it that was.  One JSON line."""
+    import dataclasses
+
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    from mashbox_b200.config.registry import architecture
+    from mashbox_b200.engine.engine import Engine
+    from mashbox_b200.weights.random_init import RandomSource
+    dev = "cuda:0"
+    c = baseline_config()
+    cfg = dataclasses.replace(c, num_layers=a.layers or c.num_layers)
+    B, ctx = a.batch, a.context
+    per_request = -(-(ctx + 1024) // 64) * 64
+    eng = Engine.from_config(cfg, RandomSource(architecture(cfg.architecture).stored_tensors(cfg), 0, torch.bfloat16, dev),
+                             dtype="bfloat16", device=dev, page_size=16, max_tokens=B * per_request + 4096, max_requests=B,
+                             max_tokens_per_step=2048 + B, chunk=2048, max_context=per_request,
+                             options=json.loads(a.options) if a.options else None)
+    gen = torch.Generator().manual_seed(1)
+    rows = eng.admit([dict(ids=torch.randint(0, cfg.vocab, (ctx - 64,), generator=gen).tolist(), max_new=256) for _ in range(B)])
+    while any(r.t_first is None for r in rows):
+        eng.step()
+    runner = eng.runner
+    entries = lambda: [(r.rid, [5], [0]) for r in rows]
+    for _ in range(5):
+        runner.step(entries())
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(3):
+            runner.step(entries())
+        torch.cuda.synchronize()
+    ev = [e for e in prof.events() if e.device_type.name == "CUDA" and "emcpy" not in e.name and "emset" not in e.name]
+    ev.sort(key=lambda e: e.time_range.start)
+    first = max(i for i, e in enumerate(ev) if "embed" in e.name)
+    step = ev[first:]
+    t0 = step[0].time_range.start
+    att = [i for i, e in enumerate(step) if "attn" in e.name]
+    lo, hi = att[len(att) // 2], att[len(att) // 2 + 1]
+    layer, prev_end = [], step[lo - 1].time_range.end
+    for e in step[lo:hi]:
+        layer.append({"kernel": e.name.split("(")[0][:60], "start_us": round(e.time_range.start - t0, 1),
+                      "end_us": round(e.time_range.end - t0, 1), "after_end_of_previous_us": round(e.time_range.end - prev_end, 1)})
+        prev_end = max(prev_end, e.time_range.end)
+    tail = [{"kernel": e.name.split("(")[0][:60], "start_us": round(e.time_range.start - t0, 1),
+             "end_us": round(e.time_range.end - t0, 1)} for e in step[att[-1] + 1:]]
+    print(json.dumps({"impl": "ours", "timeline": {"batch": B, "context": ctx, "layers": cfg.num_layers, "kernels_in_step": len(step),
+                                                   "step_us": round(step[-1].time_range.end - t0, 1),
+                                                   "layer_us": round(step[hi].time_range.start - step[lo].time_range.start, 1),
+                                                   "one_layer": layer, "after_the_last_attention": tail}}))
+    return 0
+
+
 def run_attention(a):
     """Times the attention kernels alone on one layer's cache (one JSON line; also the workload of their ncu captures):
     the prompt form -- a portion of `--queries` tokens at the end of `--keys` tokens of context, tcgen05 kernel against
@@ -518,10 +574,13 @@ def run_kernels(a):
         nw, nw_out = torch.ones(K, device=dev), torch.ones(M, device=dev)
         sums_in = torch.full(((K + 31) // 32, 16), 32.0, device=dev)
         sums_out, scaled_out = torch.empty((M + 31) // 32, 16, device=dev), torch.empty(B, M, device=dev, dtype=torch.bfloat16)
+        ops.set_pdl(False)
         r = {"library_us": chained(lambda i: torch.mm(x, ws[i].t(), out=y), n_w),
-             "stream_us": chained(lambda i: ops.linear_stream(x, ws[i], y, "plain"), n_w),
-             "stream_of_normalised_us": chained(lambda i: ops.linear_stream(x, ws[i], y, "plain", sums_in, 1e-5), n_w),
-             "stream_residual_us": chained(lambda i: ops.linear_stream_residual(x, ws[i], hs, None, sums_out, nw_out, scaled_out), n_w)}
+             "stream_plain_launch_us": chained(lambda i: ops.linear_stream(x, ws[i], y, "plain"), n_w)}
+        ops.set_pdl(True)           # from here on as the engine launches them: programmatic dependent launch
+        r.update({"stream_us": chained(lambda i: ops.linear_stream(x, ws[i], y, "plain"), n_w),
+                  "stream_of_normalised_us": chained(lambda i: ops.linear_stream(x, ws[i], y, "plain", sums_in, 1e-5), n_w),
+                  "stream_residual_us": chained(lambda i: ops.linear_stream_residual(x, ws[i], hs, None, sums_out, nw_out, scaled_out), n_w)})
         if B <= 4:
             r["gemv_us"] = chained(lambda i: ops.linear_gemv(x, ws[i], y, "plain"), n_w)
         if name == "gate_up":
@@ -570,6 +629,8 @@ def main():
     ap.add_argument("--kernels", action="store_true", help="time single kernels against the library instead of the model")
     ap.add_argument("--attention", action="store_true", help="time the attention kernels alone (--heads --kv-heads --head-dim "
                     "--queries --keys --batch)")
+    ap.add_argument("--timeline", action="store_true", help="start and end of every kernel of one layer of a decode step "
+                    "inside its graph (--batch --context --layers)")
     ap.add_argument("--heads", type=int, default=32)
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--head-dim", type=int, default=128)
@@ -593,6 +654,8 @@ def main():
         return run_workload(a)
     if a.attention:
         return run_attention(a)
+    if a.timeline:
+        return run_timeline(a)
     return run_kernels(a) if a.kernels else run_ours(a)
 
 
