@@ -165,24 +165,37 @@ def test_frequency_table_equals_the_reference_factors():
 def test_bad_files(tmp_path):
     d = tmp_path / "empty"
     d.mkdir()
-    with pytest.raises(WeightError, match="holds no"):
+    with pytest.raises(WeightError, match="no safetensors weights"):
         SafetensorsSource(str(d))
     (d / "model.safetensors").write_bytes(b"\x01\x02")
-    with pytest.raises(WeightError, match="not a safetensors file"):
+    with pytest.raises(WeightError, match="no safetensors header .the file is 2 bytes"):
         SafetensorsSource(str(d))
     (d / "model.safetensors").write_bytes((10 ** 12).to_bytes(8, "little") + b"{}")
-    with pytest.raises(WeightError, match="bad safetensors header"):
+    with pytest.raises(WeightError, match="announce a header of 1000000000000"):
+        SafetensorsSource(str(d))
+    (d / "model.safetensors").write_bytes((6).to_bytes(8, "little") + b"{nope}")
+    with pytest.raises(WeightError, match="header is not JSON"):
         SafetensorsSource(str(d))
     write_safetensors(str(d / "model.safetensors"), {"a": torch.zeros(3, dtype=torch.float32)})
     raw = bytearray((d / "model.safetensors").read_bytes())
     (d / "model.safetensors").write_bytes(bytes(raw).replace(b'"F32"', b'"F8X"'))
-    with pytest.raises(WeightError, match="stored as F8X"):
+    with pytest.raises(WeightError, match="tensor a has dtype F8X"):
         SafetensorsSource(str(d))
     (d / "model.safetensors").write_bytes(bytes(raw)[:-4])
-    with pytest.raises(WeightError, match="does not match its shape"):
+    with pytest.raises(WeightError, match=r"tensor a of shape \[3\] and dtype F32 needs 12 bytes, its entry gives bytes 0..12 of 8"):
+        SafetensorsSource(str(d))
+    (d / "model.safetensors").write_bytes(bytes(raw))
+    # a second copy of the weights under another name is not read (nor a tensor taken twice)
+    write_safetensors(str(d / "consolidated.safetensors"), {"a": torch.ones(3, dtype=torch.float32)})
+    src = SafetensorsSource(str(d))
+    assert src.names() == ["a"] and float(src.get("a").sum()) == 0.0
+    (d / "model.safetensors").unlink()
+    assert float(SafetensorsSource(str(d)).get("a").sum()) == 3.0            # ... unless it is all there is
+    write_safetensors(str(d / "other.safetensors"), {"a": torch.ones(3, dtype=torch.float32)})
+    with pytest.raises(WeightError, match="tensor a is in consolidated.safetensors and in other.safetensors"):
         SafetensorsSource(str(d))
     (d / "model.safetensors.index.json").write_text(json.dumps({"weight_map": {"a": "model-00001-of-00002.safetensors"}}))
-    with pytest.raises(WeightError, match="shard model-00001-of-00002.safetensors is missing"):
+    with pytest.raises(WeightError, match="names model-00001-of-00002.safetensors, which the folder does not have"):
         SafetensorsSource(str(d))
 
 
