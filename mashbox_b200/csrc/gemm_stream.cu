@@ -406,8 +406,9 @@ MB_API long long mb_gemm_stream_counters(int M) { return (M + 31) / 32; }
 
 // What bounds these kernels (measured with the weights resident in L2: o 7.9 us against 8.5 from DRAM, q/k/v 9.4
 // against 11.4): an SM takes in about 32 bytes a clock, 50 GB/s, whatever the source, so a product is as fast as the
-// number of SMs that have a tile allows (q/k/v: 96 tiles of 64 rows, 5.1 TB/s at best; gate/up: 112 tiles, 5.9), and
-// with tiles of 32 rows the 16 token rows that travel with every box of W are half as much traffic again (o, down).
+// number of SMs that have a tile allows (q/k/v: 96 tiles of 64 rows, 5.1 TB/s at best; gate/up: 112 tiles, 5.9; o and
+// down: 128 tiles of 32 rows, 6.8), plus about 2.5 us per launch before the first bytes and after the last.  (The
+// token rows that travel with every box of W are not it: one token and eight take the same time.)
 // Cutting the same matrices into more tiles than SMs and dealing equal shares (q/k/v as 192 tiles of 32 rows: 14.4 us
 // against 11.5; gate/up as 224 of 64: 42.5 against 38.7) loses more to the tiles that blocks share -- an epilogue per
 // segment while the ring stalls, partial sums through global memory -- than the idle SMs cost.
