@@ -404,14 +404,16 @@ static int stream_sms() {
 MB_API long long mb_gemm_stream_workspace() { return (long long)stream_sms() * 2 * 2 * S_NT * 128; }
 MB_API long long mb_gemm_stream_counters(int M) { return (M + 31) / 32; }
 
-// What bounds these kernels (measured with the weights resident in L2: o 7.9 us against 8.5 from DRAM, q/k/v 9.4
-// against 11.4): an SM takes in about 32 bytes a clock, 50 GB/s, whatever the source, so a product is as fast as the
-// number of SMs that have a tile allows (q/k/v: 96 tiles of 64 rows, 5.1 TB/s at best; gate/up: 112 tiles, 5.9; o and
-// down: 128 tiles of 32 rows, 6.8), plus about 2.5 us per launch before the first bytes and after the last.  (The
-// token rows that travel with every box of W are not it: one token and eight take the same time.)
-// Cutting the same matrices into more tiles than SMs and dealing equal shares (q/k/v as 192 tiles of 32 rows: 14.4 us
-// against 11.5; gate/up as 224 of 64: 42.5 against 38.7) loses more to the tiles that blocks share -- an epilogue per
-// segment while the ring stalls, partial sums through global memory -- than the idle SMs cost.
+// What was measured about the pace of these kernels (8B shapes, launch to launch inside a graph).  With the weights
+// resident in L2 they take almost as long as from DRAM (o 7.8 against 8.5 us, q/k/v 9.4 against 11.4, down 23.0 against
+// 23.0); one token takes as long as sixteen; leaving out the products of the token columns 8..15 when there are at most
+// 8 tokens, or asking for the fragments of the next k step before the products of this one are issued, changed nothing;
+// a kernel that only streams the matrix into shared memory takes as long as the product.  So neither DRAM nor the
+// consumer warps set it: about 2.5 us per launch before the first bytes and after the last, and an intake of some 50
+// GB/s per SM in between.  More blocks did not help either way: cutting the same matrices into more tiles than SMs and
+// dealing equal shares (q/k/v as 192 tiles of 32 rows: 14.4 us against 11.5; gate/up as 224 of 64: 42.5 against 38.7)
+// loses more to the tiles that blocks share than the idle SMs cost, and tiles of 48 rows for q/k/v (128 blocks instead
+// of 96) and of 112 rows for gate/up (128 instead of 112), one block each, were slower as well (12.6 against 11.4).
 // The height of a row tile: the largest of 128, 64, 32 that gives at least 0.6 tiles per SM, so that a matrix of few
 // rows still has a tile for most SMs and no tile is shared (then the grid is one block per tile); matrices with more
 // tiles than SMs, or too few even at 32 rows, are cut into equal shares of items.  least: the smallest height allowed.

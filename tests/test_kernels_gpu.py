@@ -434,10 +434,13 @@ def test_penalties_and_their_state():
     assert int(cnt[0].sum()) == 0 and int(cnt[3].sum()) == 0
 
 
-@pytest.mark.parametrize("N,M,K", [(1, 4096, 4096), (8, 6144, 4096), (3, 1000, 200), (16, 4096, 14336), (5, 504, 320), (2, 56, 72)])
+@pytest.mark.parametrize("N,M,K", [(1, 4096, 4096), (8, 6144, 4096), (3, 1000, 200), (16, 4096, 14336), (5, 504, 320), (2, 56, 72),
+                                   (8, 5000, 520), (3, 14336, 256), (16, 10008, 136), (2, 28672, 264)])
 def test_weight_streaming_product(N, M, K):
-    """the product for decode batches that streams W by TMA in equal shares per SM: row tiles that blocks share are
-    finished by the block that arrives last; called twice so that the self-resetting counters are exercised"""
+    """the product for decode batches that streams W by TMA: a block per row tile where that leaves at most a tile per
+    SM (tiles of 32, 48, 64, 112 or 128 rows, the last one of a matrix cut short), else equal shares per SM, row tiles
+    that blocks share finished by the block that arrives last; called twice so that the self-resetting counters are
+    exercised"""
     K_ = ops()
     g = torch.Generator().manual_seed(14)
     a = torch.randn(N, K, generator=g).bfloat16().to(G.DEV)
@@ -604,7 +607,7 @@ def test_streaming_products_that_add_to_the_stream_and_take_the_norm_in(N, M, K)
     # the product after the norm: x (N, M) is now the stream, W2 (M2, M)
     if M % 8:
         return
-    for M2 in (136, 4096 if M <= 4096 else 264):
+    for M2 in (136, 4096 if M <= 4096 else 264) + ((6144, 28672) if (N, M) == (8, 4096) else ()):
         w2 = (torch.randn(M2, M, generator=g) / M ** 0.5).bfloat16().to(G.DEV)
         inv = torch.rsqrt((x.double() ** 2).mean(-1, keepdim=True) + eps)
         want2 = (scaled.double() @ w2.double().T) * inv
