@@ -2,14 +2,17 @@
 option names with the same meanings where this engine has the thing.
 
     python -m mashbox_b200 run <model-dir> --prompt TEXT | --prompt-ids 5,17,3
-        [--max-tokens N] [--temperature T] [--top-p P] [--top-k K] [--seed N] [--ctx N] [--slots N]
-        [--dtype bfloat16|float32] [--page-size N] [--chunk N]
+        [--thinking] [--max-tokens N] [--temperature T] [--top-p P] [--top-k K] [--seed N] [--ctx N] [--slots N]
+        [--cache-dir DIR] [--no-warm] [--dtype bfloat16|float32] [--page-size N] [--chunk N] [--trace]
     python -m mashbox_b200 random <out-dir> --config config.json --seed N [--store bfloat16|float32]
     python -m mashbox_b200 env
 
+Of the reference's `run` options, `--steps` (decode steps per device call) and `--no-kernels` (its plain JAX path) have
+no counterpart: this engine always keeps two steps queued on the GPU, and its exact path is `--dtype float32`.
+
 `--prompt TEXT` needs tokenizer.json in the model folder (and uses its chat template when tokenizer_config.json has
-one); `--prompt-ids` needs none and prints ids.  Events go to stderr as JSON lines (`loaded`, `done`), the answer to
-stdout.  A refusal prints one line and exits with 2.
+one); `--prompt-ids` needs none and prints ids.  Events go to stderr as JSON lines (`weights`, `loaded`, `warm`, `done`),
+the answer to stdout.  A refusal prints one line and exits with 2.
 """
 import argparse
 import json
@@ -31,6 +34,7 @@ def build_parser():
     p.add_argument("model", help="a model folder with config.json and safetensors weights")
     p.add_argument("--prompt", metavar="TEXT", help="answer one chat turn, print it and exit")
     p.add_argument("--prompt-ids", metavar="IDS", help="token ids separated by commas instead of text; prints ids")
+    p.add_argument("--thinking", action="store_true", help="ask the chat template for the model's thinking mode")
     p.add_argument("--max-tokens", type=int, default=512, metavar="N", help="most new tokens")
     p.add_argument("--temperature", type=float, default=0.0, metavar="T", help="sampling temperature; 0 is greedy")
     p.add_argument("--top-p", type=float, default=1.0, metavar="P", help="nucleus sampling cut")
@@ -39,6 +43,12 @@ def build_parser():
     p.add_argument("--ctx", default="auto", metavar="N|auto", help="context per request in tokens (prompt plus answer); "
                    "auto = the prompt plus --max-tokens")
     p.add_argument("--slots", type=int, default=1, metavar="N", help="requests decoded together")
+    p.add_argument("--cache-dir", metavar="DIR", help="where compiled kernel libraries are kept (default: inside the "
+                   "package when it can be written, else a per-user folder under the temporary directory)")
+    p.add_argument("--no-warm", action="store_true", help="answer at once: without it a two-token answer is generated "
+                   "first, so that compiling kernels and capturing graphs stay out of the reported times")
+    p.add_argument("--trace", action="store_true", help="report per generated token the hash of its logits and the gap "
+                   "between the two largest (also: MASHBOX_TRACE=1)")
     p.add_argument("--dtype", default="bfloat16", choices=("bfloat16", "float32"),
                    help="bfloat16: the serving kernels; float32: everything in true 32-bit")
     p.add_argument("--page-size", type=int, default=16, metavar="N", help="tokens per cache page")
@@ -60,7 +70,7 @@ def tokenizer_of(folder):
     return Tokenizer.from_file(path)
 
 
-def chat_ids(folder, tok, text):
+def chat_ids(folder, tok, text, thinking=False):
     """ids of one user turn: through the folder's chat template when it has one, else the bare text"""
     cfg = os.path.join(folder, "tokenizer_config.json")
     if os.path.isfile(cfg):
@@ -69,7 +79,7 @@ def chat_ids(folder, tok, text):
             from jinja2.sandbox import ImmutableSandboxedEnvironment
             env = ImmutableSandboxedEnvironment(trim_blocks=True, lstrip_blocks=True)
             text = env.from_string(tc["chat_template"]).render(
-                messages=[dict(role="user", content=text)], add_generation_prompt=True,
+                messages=[dict(role="user", content=text)], add_generation_prompt=True, enable_thinking=bool(thinking),
                 bos_token=tc.get("bos_token") or "", eos_token=tc.get("eos_token") or "")
             return tok.encode(text, add_special_tokens=False).ids
     return tok.encode(text).ids
@@ -92,11 +102,14 @@ def cmd_run(a):
     if (a.prompt is None) == (a.prompt_ids is None):
         raise MashboxError("give --prompt TEXT or --prompt-ids IDS")
     t0 = time.time()
+    if a.cache_dir:
+        from .ops import build
+        build.set_build_dir(a.cache_dir)
     cfg = read_config_file(a.model)
     tok = None
     if a.prompt is not None:
         tok = tokenizer_of(a.model)
-        ids = chat_ids(a.model, tok, a.prompt)
+        ids = chat_ids(a.model, tok, a.prompt, a.thinking)
         stops = stop_ids_of(a.model, cfg)
     else:
         try:
@@ -108,18 +121,26 @@ def cmd_run(a):
     ctx = -(-ctx // a.page_size) * a.page_size
     eng = Engine.from_folder(a.model, dtype=a.dtype, page_size=a.page_size, max_tokens=ctx * a.slots,
                              max_requests=a.slots, max_context=ctx, chunk=a.chunk,
-                             max_tokens_per_step=a.chunk + a.slots, log=log)
+                             max_tokens_per_step=a.chunk + a.slots, log=log, trace=True if a.trace else None)
     log(dict(event="loaded", seconds=round(time.time() - t0, 2), dtype=a.dtype, context=ctx, slots=a.slots))
     samp = None if a.temperature == 0 else [dict(temperature=a.temperature, top_p=a.top_p, top_k=a.top_k, seed=a.seed)]
     try:
+        if not a.no_warm:
+            t1 = time.time()
+            eng.generate([ids], max_new=min(2, a.max_tokens), samp=samp)
+            eng.generate([ids], max_new=min(2, a.max_tokens), samp=samp)      # shapes that came twice are graphs now
+            log(dict(event="warm", seconds=round(time.time() - t1, 2)))
         r = eng.generate([ids], max_new=a.max_tokens, stop_ids=stops, samp=samp)
     except ValueError as e:
         raise MashboxError(str(e)) from None
     out = r["ids"][0]
     print(tok.decode(out) if tok is not None else ",".join(str(t) for t in out))
     t = r["timing"]
-    log(dict(event="done", new_tokens=t["new_tokens"], prefill_s=round(t["prefill_s"], 3),
-             decode_s=round(t["decode_s"], 3), finish=r["finish"][0]))
+    done = dict(event="done", new_tokens=t["new_tokens"], prefill_s=round(t["prefill_s"], 3),
+                decode_s=round(t["decode_s"], 3), finish=r["finish"][0])
+    if "lh" in r:
+        done["lh"] = r["lh"][0]
+    log(done)
     return 0
 
 

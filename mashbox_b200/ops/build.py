@@ -52,7 +52,18 @@ def find_nvcc():
                       "kernels of mashbox_b200 cannot be built")
 
 
+_build_dir = {"path": os.environ.get("MASHBOX_B200_BUILD_DIR")}
+
+
+def set_build_dir(path):
+    """Compiled libraries go to (and are looked for in) this folder from now on."""
+    _build_dir["path"] = path
+
+
 def build_dir():
+    if _build_dir["path"]:
+        os.makedirs(_build_dir["path"], exist_ok=True)
+        return _build_dir["path"]
     d = os.path.join(CSRC, "_build")
     try:
         os.makedirs(d, exist_ok=True)

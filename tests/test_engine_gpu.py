@@ -281,8 +281,17 @@ def test_command_line(tmp_path):
     cfg, W = plain.read_model(folder)
     assert ids == plain.greedy(cfg, W, [5, 17, 3, 200], 6)
     events = [json.loads(l) for l in r.stderr.splitlines() if l.startswith("{")]
-    assert [e["event"] for e in events if e["event"] in ("loaded", "done")] == ["loaded", "done"]
-    assert events[-1]["new_tokens"] == 6
+    assert [e["event"] for e in events if e["event"] in ("loaded", "warm", "done")] == ["loaded", "warm", "done"]
+    assert events[-1]["new_tokens"] == 6 and "lh" not in events[-1]
+    # --no-warm answers at once; --trace adds the logit hashes; --cache-dir says where the compiled kernels go
+    cache = tmp_path / "kernels"
+    t = subprocess.run(cmd + ["--no-warm", "--trace", "--cache-dir", str(cache)], capture_output=True, text=True, env=env,
+                       timeout=900)
+    assert t.returncode == 0, t.stderr[-2000:]
+    assert t.stdout == r.stdout
+    events = [json.loads(l) for l in t.stderr.splitlines() if l.startswith("{")]
+    assert "warm" not in [e["event"] for e in events] and len(events[-1]["lh"]) == 6
+    assert any(f.endswith(".so") for f in os.listdir(cache))
     s = subprocess.run(cmd[:-4] + ["--temperature", "0.8", "--seed", "7", "--top-k", "50", "--dtype", "float32", "--ctx", "256"],
                        capture_output=True, text=True, env=env, timeout=600)
     assert s.returncode == 0 and len(s.stdout.strip().split(",")) == 6
