@@ -21,6 +21,9 @@ struct AttnParams {
     // points at rows [q heads | k heads | v heads] as the q/k/v product left them; the kernel adds rope_bias ((H + 2 KV)
     // HD floats, or null), rotates q and k by the token's position (rope_freqs: rope_rd / 2 angles per position step,
     // or null; rope_pairing 0 adjacent pairs, 1 halves) and writes k and v into the token's page
+    // the decode form of the TMA kernel launched as thread-block clusters of `cluster` blocks, one per split of a
+    // sequence (every sequence of the launch has that many splits): the splits' results meet in shared memory
+    int cluster = 0;
     int fuse_rope = 0;
     const float* rope_bias = nullptr;
     const float* rope_freqs = nullptr;

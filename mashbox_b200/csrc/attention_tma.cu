@@ -45,6 +45,23 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
 }
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 128;\n" ::: "memory"); }
 
+// thread-block clusters: the barrier over all threads of the cluster that have not exited (a hardware barrier, no
+// spinning), and reads of another block's shared memory
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_map(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ float cluster_ld(uint32_t addr) {
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(addr) : "memory");
+    return v;
+}
+
 // element offset of 16-byte chunk c of key row `row` in a K or V stage as the TMA lays it out: halves of 64 columns,
 // each 64 rows x 128 bytes, 16-byte chunks XORed with the row (the 128-byte swizzle)
 template <int HD> __device__ __forceinline__ int kv_off(int row, int c) {
@@ -394,12 +411,44 @@ __global__ void __launch_bounds__(160, 2) attn_tma_kernel(const AttnParams P, co
             const int tq = r / G, h = kvh * G + r % G;
             if (n_splits == 1) {
                 P.out[((size_t)(tok0 + tq) * H + h) * HD + d] = __float2bfloat16_rn(L > 0.0f ? acc / L : 0.0f);
+            } else if (P.cluster > 1) {
+                // the split's result stays in this block's shared memory (behind the warps' partial results)
+                float* fin = mo + 4 * 16 * HD + 2 * 4 * 16;             // [16 rows][HD], then [16 rows][2]
+                fin[row * HD + d] = acc;
+                if (d == 0) { fin[16 * HD + 2 * row] = M; fin[16 * HD + 2 * row + 1] = L; }
             } else {
                 const size_t base = ((size_t)(P.part_base[seq] + tq) * H + h) * P.max_splits + split;
                 P.part_o[base * HD + d] = acc;
                 if (d == 0) { P.part_ml[base * 2] = M; P.part_ml[base * 2 + 1] = L; }
             }
         }
+    }
+    // Launched as clusters (one block per split of a sequence and kv head), the splits meet in shared memory: after a
+    // barrier over the cluster every block reads, for its share of the head's columns, all splits' sums in the order of
+    // the splits and writes the rows; a second barrier keeps a block's memory alive until its neighbours have read it.
+    // (The producer warp has exited by now; the barrier counts the threads that have not.)
+    if (DECODE && n_splits > 1 && P.cluster > 1) {
+        cluster_sync();
+        const float* fin = reinterpret_cast<const float*>(kvs) + 4 * 16 * HD + 2 * 4 * 16;
+        const uint32_t fin_addr = smem_u32(fin);
+        const int rows = min(BM, R - row0), per = HD / n_splits;      // columns of a row this block writes (HD / splits >= 4)
+        for (int it = tid; it < rows * per; it += 128) {
+            const int row = it / per, d = split * per + it % per, r = row0 + row;
+            float M = -INFINITY;
+            for (int s = 0; s < n_splits; s++) M = fmaxf(M, cluster_ld(cluster_map(fin_addr + (16 * HD + 2 * row) * 4, s)));
+            float acc = 0.0f, L = 0.0f;
+            for (int s = 0; s < n_splits; s++) {                      // in the order of the splits
+                const uint32_t base = cluster_map(fin_addr, s);
+                const float ms = cluster_ld(base + (16 * HD + 2 * row) * 4);
+                const float sc = (ms == -INFINITY) ? 0.0f : exp2f(ms - M);
+                L += cluster_ld(base + (16 * HD + 2 * row + 1) * 4) * sc;
+                acc += cluster_ld(base + (row * HD + d) * 4) * sc;
+            }
+            const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+            P.out[((size_t)(tok0 + r / G) * H + kvh * G + r % G) * HD + d] = __float2bfloat16_rn(acc * inv);
+        }
+        cluster_sync();
+        return;
     }
     // The splits of a tile are merged by whichever of their blocks finishes last: every block publishes its partial
     // result, then draws a ticket; the one that draws the last ticket reads all of them back (in the order of the
@@ -521,6 +570,7 @@ static int launch_tma(const AttnParams& P, const CUtensorMap& kmap, const CUtens
     constexpr int BM = DECODE ? 16 : 64;
     const size_t smem = 1024 + (size_t)STAGES * 2 * 64 * HD * 2 + (size_t)BM * HD * 2 + 2 * STAGES * 8 + 16 + (ROPE ? 4 * HD : 0);
     static bool configured = false;
+    static int max_cluster = 1;         // the largest cluster of these blocks the device can place (a power of two up to 8)
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_tma_kernel<HD, DECODE, STAGES, ROPE>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -528,10 +578,30 @@ static int launch_tma(const AttnParams& P, const CUtensorMap& kmap, const CUtens
         // two blocks per SM need most of the SM's memory as shared memory: ask for the largest carve-out
         cudaFuncSetAttribute(attn_tma_kernel<HD, DECODE, STAGES, ROPE>, cudaFuncAttributePreferredSharedMemoryCarveout,
                              cudaSharedmemCarveoutMaxShared);
+        if (DECODE) {
+            // Clusters of up to 8 blocks (the portable size).  Clusters of 16 can be placed too, but were slower wherever
+            // they applied (two sequences of 8,192 keys: 29.5 us against 18.6 us for 16 splits that meet through global
+            // memory): a cluster of 16 of these blocks needs eight SMs of one GPC free at once.
+            for (int c = 8; c > 1; c /= 2) {
+                cudaLaunchAttribute attr;
+                attr.id = cudaLaunchAttributeClusterDimension;
+                attr.val.clusterDim.x = c; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+                cudaLaunchConfig_t cfg = {};
+                cfg.gridDim = dim3(c, 1); cfg.blockDim = dim3(160); cfg.dynamicSmemBytes = smem; cfg.attrs = &attr; cfg.numAttrs = 1;
+                int n = 0;
+                if (cudaOccupancyMaxActiveClusters(&n, attn_tma_kernel<HD, DECODE, STAGES, ROPE>, &cfg) == cudaSuccess && n >= 1) {
+                    max_cluster = c;
+                    break;
+                }
+                cudaGetLastError();
+            }
+        }
         configured = true;
     }
-    const cudaError_t e = mb_launch(mb_pdl != 0, attn_tma_kernel<HD, DECODE, STAGES, ROPE>, dim3(n_items, P.KV), dim3(160), smem, st,
-                                    P, kmap, vmap);
+    if (n_items < 0) return max_cluster;                 // a query (mb_attn_tma_max_cluster)
+    if (P.cluster > max_cluster || (P.cluster > 1 && n_items % P.cluster)) return -2;
+    const cudaError_t e = mb_launch_cluster(mb_pdl != 0, P.cluster > 1 ? P.cluster : 1, attn_tma_kernel<HD, DECODE, STAGES, ROPE>,
+                                            dim3(n_items, P.KV), dim3(160), smem, st, P, kmap, vmap);
     return e == cudaSuccess ? 0 : (int)e;
 }
 
@@ -547,8 +617,9 @@ static int attn_tma_run(const void* q, int q_stride, void* out, const void* kpoo
                         const int* pos0, const int* part_base, const int* seq_row, const int* table, int max_blocks,
                         float* part_o, float* part_ml, int max_splits, int H, int KV, int HD, int page, int num_pages,
                         int window, float scale, int* counters, int* err, cudaStream_t st, int fuse, const float* bias,
-                        const float* freqs, int RD, int pairing) {
+                        const float* freqs, int RD, int pairing, int cluster = 0) {
     if (n_items == 0) return 0;
+    if (cluster > 1 && (!decode || cluster > 8 || (cluster & (cluster - 1)) || HD / cluster < 4)) return -2;
     if (!mb_attn_tma_supports(HD, page) || KV < 1 || H % KV || KV > 65535) return -2;
     if (fuse && (!decode || H / KV > 16 || RD % 2 || RD > HD || RD < 0 || !kpool || !vpool)) return -2;
     AttnParams P;
@@ -563,6 +634,7 @@ static int attn_tma_run(const void* q, int q_stride, void* out, const void* kpoo
     for (int sft = 0; sft < 31; sft++) if ((1 << sft) == page) P.page_shift = sft;
     P.scale_log2 = scale * 1.4426950408889634f;
     P.err = err;
+    P.cluster = cluster > 1 ? cluster : 0;
     P.fuse_rope = fuse; P.rope_bias = bias; P.rope_freqs = freqs; P.rope_rd = freqs ? RD : 0; P.rope_pairing = pairing;
     CUtensorMap kmap, vmap;
     const long long rows = (long long)num_pages * KV * page;
@@ -600,4 +672,28 @@ MB_API int mb_attn_tma_rope_bf16(const void* qkv, int q_stride, void* out, void*
     return attn_tma_run(qkv, q_stride, out, kpool, vpool, items, n_items, 1, q_start, q_len, pos0, part_base, seq_row, table,
                         max_blocks, part_o, part_ml, max_splits, H, KV, HD, page, num_pages, window, scale, counters,
                         err, st, 1, bias, freqs, RD, pairing);
+}
+
+// The decode form launched as thread-block clusters: every sequence of the launch is cut into `cluster` splits (2, 4 or
+// 8; the items of a sequence in the order of the splits), a cluster is the splits of one sequence and kv head, and
+// their results meet in the cluster's shared memory instead of global memory: no partial buffers, no counters.  rope:
+// as mb_attn_tma_rope_bf16 (bias / freqs may be null), 0: q is the rotated queries as for mb_attn_tma_bf16.
+MB_API int mb_attn_tma_cluster_bf16(const void* q, int q_stride, void* out, void* kpool, void* vpool, const void* items,
+                                    int n_items, const int* q_start, const int* q_len, const int* pos0, const int* seq_row,
+                                    const int* table, int max_blocks, int cluster, int H, int KV, int HD, int page,
+                                    int num_pages, int window, float scale, int* err, int rope, const float* bias,
+                                    const float* freqs, int RD, int pairing, cudaStream_t st) {
+    if (cluster < 2) return -2;
+    return attn_tma_run(q, q_stride, out, kpool, vpool, items, n_items, 1, q_start, q_len, pos0, nullptr, seq_row, table,
+                        max_blocks, nullptr, nullptr, cluster, H, KV, HD, page, num_pages, window, scale, nullptr, err, st,
+                        rope, bias, freqs, RD, pairing, cluster);
+}
+
+// the largest cluster mb_attn_tma_cluster_bf16 can be given on this device for this head size (1: none)
+MB_API int mb_attn_tma_max_cluster(int HD, int rope) {
+    if (HD != 64 && HD != 128) return 1;
+    AttnParams P{};
+    CUtensorMap m{};
+    if (HD == 128) return rope ? launch_tma<128, true, 3, true>(P, m, m, -1, nullptr) : launch_tma<128, true, 3>(P, m, m, -1, nullptr);
+    return rope ? launch_tma<64, true, 4, true>(P, m, m, -1, nullptr) : launch_tma<64, true, 4>(P, m, m, -1, nullptr);
 }

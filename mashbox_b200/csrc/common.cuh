@@ -91,4 +91,32 @@ static inline cudaError_t mb_launch(bool pdl, void (*kernel)(Params...), dim3 gr
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);
 }
 
+// the same as a launch of thread-block clusters of cluster_x blocks along x (1: no clusters)
+template <typename... Params, typename... Args>
+static inline cudaError_t mb_launch_cluster(bool pdl, unsigned cluster_x, void (*kernel)(Params...), dim3 grid, dim3 block,
+                                            size_t smem, cudaStream_t st, Args... args) {
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (pdl) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        n++;
+    }
+    if (cluster_x > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = cluster_x;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = 1;
+        n++;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cfg.attrs = attr;
+    cfg.numAttrs = n;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);
+}
+
 #define MB_LAUNCH_CHECK() do { cudaError_t e__ = cudaGetLastError(); if (e__ != cudaSuccess) return (int)e__; } while (0)

@@ -498,16 +498,47 @@ def attention_tma_folds_rotation(G):
     return 1 <= G <= 16
 
 
+_max_cluster = {}
+
+
+def attention_tma_max_cluster(HD):
+    """the most splits of a sequence whose blocks attention_tma can launch as one thread-block cluster (1: none)"""
+    if HD not in _max_cluster:
+        lib = load_library("attention_tma")
+        lib.mb_attn_tma_max_cluster.argtypes = [c_int, c_int]
+        lib.mb_attn_tma_max_cluster.restype = c_int
+        _max_cluster[HD] = max(1, min(lib.mb_attn_tma_max_cluster(HD, 0), lib.mb_attn_tma_max_cluster(HD, 1)))
+    return _max_cluster[HD]
+
+
 def attention_tma(q, q_stride, out, kpool, vpool, items, n_items, decode, q_start, q_len, pos0, part_base, seq_row,
                   table, part_o, part_ml, max_splits, H, KV, HD, page, num_pages, window, scale, err, merge=False,
-                  rope=None):
+                  rope=None, cluster=0):
     """The same contract as attention_mma, with K/V tiles loaded by TMA (head sizes 64 and 128, pages of 8 to 64).
     merge: the last block of every split group merges the group's partial results and writes `out`, so no
     attention_merge is needed afterwards (only when attention_tma_merges(n_items, KV)).
+    cluster = n > 1 (decode form): every sequence of the launch is cut into n splits and the blocks of a sequence and kv
+    head are launched as one thread-block cluster whose results meet in shared memory (no partial buffers, no merge);
+    n at most attention_tma_max_cluster(HD).
     rope = (bias or None, freqs or None, RD, pairing): the step's sequences bring ONE token each and q is the whole
     (N, (H + 2 KV) HD) output of the q/k/v product; the kernel does what rope_kv_write would have done before it (bias,
     rotation of q and k, k and v into the token's page) -- the same bits, one launch fewer.  q itself is not changed."""
     _cuda(q, out, kpool, vpool, items, q_start, q_len, pos0, part_base, table, part_o, part_ml)
+    if cluster and cluster > 1:
+        if not decode:
+            raise KernelError("attention_tma: clusters are for the decode form")
+        bias, freqs, RD, pairing = rope if rope is not None else (None, None, 0, 0)
+        _cuda(bias, freqs)
+        f = _fn("attention_tma", "mb_attn_tma_cluster_bf16",
+                [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                 c_void_p, c_int] + [c_int] * 7 + [c_float, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p])
+        code = f(_p(q), q_stride, _p(out), _p(kpool), _p(vpool), _p(items), n_items, _p(q_start), _p(q_len), _p(pos0),
+                 _p(seq_row), _p(table), table.shape[1], int(cluster), H, KV, HD, page, num_pages, window or 0,
+                 float(scale), _p(err), 1 if rope is not None else 0, _p(bias), _p(freqs), int(RD), int(pairing), _stream())
+        if code == -6:
+            raise KernelError("attention_tma: the driver refused the tensor map of the cache pool")
+        _check(code, "attention_tma")
+        return
     counters = None
     if merge:
         if not attention_tma_merges(n_items, KV):

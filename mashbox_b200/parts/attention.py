@@ -104,11 +104,32 @@ class Attention:
         # the two forms are two launches: each is cut into splits by its own number of blocks
         base = {f: max(1, sum(t for t, d in zip(tiles, decode_form) if d == f) * KV) for f in (True, False)}
         dec, pre, part_base, part_tok = [], [], [-1] * S, []
-        for s in range(S):
+
+        def key_tiles(s):
             hi = ctx.pos0[s] + ctx.q_len[s]
             lo = max(0, ctx.pos0[s] - self.window + 1) if self.window else 0
-            kv_tiles = -(-(hi - lo // KEY_TILE * KEY_TILE) // KEY_TILE)
+            return -(-(hi - lo // KEY_TILE * KEY_TILE) // KEY_TILE)
+
+        # Decode-form sequences on the TMA kernel: when they can all be cut into the same number of splits (set by the
+        # longest of them; a shorter one leaves some of its splits empty) the blocks of a sequence and kv head are
+        # launched as one thread-block cluster and their results meet in shared memory.
+        cluster = 0
+        page = ctx.cache.page_size
+        if (any(decode_form) and base[True] < target and ctx.options.get("attention_kernel", "tma") == "tma"
+                and ctx.ops.attention_tma_supports(self.HD, page) and ctx.options.get("attention_clusters", True)):
+            want = min(max_splits, -(-target // base[True]), max(key_tiles(s) for s in range(S) if decode_form[s]) // 2)
+            want = 1 << (max(1, want).bit_length() - 1)
+            # only when the cluster holds all the splits the launch wants anyway: at one or two sequences (32 and 16
+            # splits) more, smaller blocks that meet through global memory are faster than clusters of 8
+            if 2 <= want <= min(ctx.ops.attention_tma_max_cluster(self.HD), self.HD // 4):
+                cluster = want
+        for s in range(S):
+            kv_tiles = key_tiles(s)
             ns = 1
+            if cluster and decode_form[s]:
+                for sp in range(cluster):
+                    dec.append((0, s, 0, sp, cluster))
+                continue
             if ctx.q_len[s] <= DECODE_ROWS and base[decode_form[s]] < target and (decode_form[s] or not tc5):
                 ns = max(1, min(max_splits, -(-target // base[decode_form[s]]), kv_tiles // 2))
                 ns = 1 << (ns.bit_length() - 1)                    # a power of two: few distinct work-list shapes
@@ -128,7 +149,7 @@ class Attention:
         ctx.inputs.add(name + "part_base", np.asarray(part_base, np.int32))
         ctx.inputs.add(name + "part_tok", np.asarray(part_tok, np.int32))
         ctx.memo[key] = dict(name=name, n_dec=len(dec), n_pre=len(pre), n_part=len(part_tok) // 2,
-                             max_splits=max_splits, tc5=tc5)
+                             max_splits=max_splits, tc5=tc5, cluster=cluster)
 
     # ------------------------------------------------------------------------------------------ forward
     fuses_small = True      # forward() takes normed= and residual= (see PreNormBlock)
@@ -199,7 +220,12 @@ class Attention:
                                   self.window, self.scale, ctx.err)
             for form, n_items, decode in ((nm + "pre", 0 if plan["tc5"] else plan["n_pre"], False),
                                           (nm + "dec", plan["n_dec"], True)):
-                if n_items:
+                if n_items and decode and plan["cluster"]:
+                    ops.attention_tma(qkv, width, out, kpool, vpool, ctx.dev(form), n_items, True, ctx.dev("q_start"),
+                                      ctx.dev("q_len"), ctx.dev("pos0"), None, ctx.dev("seq_row"), table, None, None, 1,
+                                      H, KV, HD, page, pages, self.window, self.scale, ctx.err,
+                                      rope=extra.get("rope"), cluster=plan["cluster"])
+                elif n_items:
                     flash(qkv, width, out, kpool, vpool, ctx.dev(form), n_items, decode, ctx.dev("q_start"),
                           ctx.dev("q_len"), ctx.dev("pos0"), ctx.dev(nm + "part_base"), ctx.dev("seq_row"),
                           table, part_o, part_ml, ms, H, KV, HD, page, pages, self.window, self.scale, ctx.err, **extra)

@@ -733,3 +733,51 @@ def test_decode_attention_with_the_rotation_folded_in(HD, H, KV, page, window, s
     assert not torch.isnan(got.float()).any() and torch.equal(got, want)
     # and the new token's key really took part: attending without it gives something else
     assert not torch.equal(want, attend(q1, seqs.kpool, seqs.vpool, None))
+
+
+@pytest.mark.parametrize("HD,H,KV,page,window,cluster,rope", [
+    (128, 32, 8, 16, None, 8, True), (128, 8, 2, 16, None, 4, False), (64, 6, 2, 32, 300, 8, True),
+    (64, 32, 8, 8, None, 2, False), (128, 16, 1, 64, None, 8, False), (128, 5, 5, 16, 70, 2, True)])
+def test_decode_attention_in_clusters(HD, H, KV, page, window, cluster, rope):
+    """the decode form launched as thread-block clusters, one block per split of a sequence and kv head, the splits
+    meeting in the cluster's shared memory: the same bits as the launch whose splits meet through global memory and a
+    ticket, with and without the rotation folded in; sequences shorter than the splits leave splits empty"""
+    K = ops()
+    if cluster > K.attention_tma_max_cluster(HD):
+        pytest.skip(f"this device places clusters of at most {K.attention_tma_max_cluster(HD)} of these blocks")
+    lengths = [2100, 64, 65, 1, 333, 128, 900]
+    Gq = H // KV
+    seqs = G.PagedSequences(lengths, [1] * len(lengths), H, KV, HD, page, torch.bfloat16, seed=33).round().build()
+    dominant_key(seqs, 0, 7)
+    seqs.round().build()
+    g = torch.Generator().manual_seed(6)
+    N, width = len(lengths), (H + 2 * KV) * HD
+    if rope:
+        q_in = torch.randn(N, width, generator=g).to(G.DEV, torch.bfloat16)
+        b = (0.3 * torch.randn(width, generator=g)).to(G.DEV)
+        freqs = torch.from_numpy(plain.rope_frequencies(10000.0, HD, None)).to(G.DEV)
+        extra, stride = dict(rope=(b, freqs, HD, 0)), width
+    else:
+        q_in, extra, stride = seqs.q_dev, {}, H * HD
+    items = G.i32(np.asarray([(s, 0, sp, cluster) for s in range(N) for sp in range(cluster)]).reshape(-1))
+    part_base = G.i32(list(range(N)))
+
+    def attend(kpool, vpool, **how):
+        out = torch.full((N, H * HD), float("nan"), device=G.DEV, dtype=torch.bfloat16)
+        err = K.new_error_word(G.DEV)
+        part_o = torch.full((N * H * cluster, HD), float("nan"), device=G.DEV)
+        part_ml = torch.full((N * H * cluster, 2), float("nan"), device=G.DEV)
+        K.attention_tma(q_in, stride, out, kpool, vpool, items, N * cluster, True, seqs.q_start, seqs.q_len, seqs.pos0,
+                        part_base, seqs.seq_row, seqs.table, part_o, part_ml, cluster, H, KV, HD, page, seqs.num_pages,
+                        window, HD ** -0.5, err, **how, **extra)
+        K.check_error_word(err)
+        return out
+
+    k1, v1 = seqs.kpool.clone(), seqs.vpool.clone()
+    want = attend(k1, v1, merge=True)
+    k2, v2 = seqs.kpool.clone(), seqs.vpool.clone()
+    got = attend(k2, v2, cluster=cluster)
+    assert not torch.isnan(got.float()).any() and torch.equal(got, want)
+    assert torch.equal(k1, k2) and torch.equal(v1, v2)
+    if not rope:
+        close(got, seqs.reference(HD ** -0.5, window), torch.bfloat16, "decode attention in clusters")
