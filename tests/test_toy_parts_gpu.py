@@ -231,3 +231,114 @@ def test_routed_feed_forward_and_learned_position_encoding_per_layer(tmp_path, d
     bar(np.concatenate(got["a"]), wa, "routed toy, request a in portions beside b")
     bar(np.concatenate(got["b"]), wb, "routed toy, request b in portions beside a")
     runner.cache.check()
+
+
+# ---------------------------------------------------------------------------------------- two head sizes in one model
+@dataclass(frozen=True)
+class TwoSizesConfig:
+    architecture: str
+    hidden: int
+    vocab: int
+    inner: int
+    kv_heads: int
+    groups: int
+    head_dims: tuple
+    eps: float
+
+    @classmethod
+    def from_hf(cls, c):
+        return cls(c["architectures"][0], c["hidden_size"], c["vocab_size"], c["inner"], c["kv_heads"], c["groups"],
+                   tuple(c["head_dims"]), c["eps"])
+
+    def to_hf(self):
+        return dict(architectures=[self.architecture], hidden_size=self.hidden, vocab_size=self.vocab, inner=self.inner,
+                    kv_heads=self.kv_heads, groups=self.groups, head_dims=list(self.head_dims), eps=self.eps)
+
+
+def two_sizes_architecture():
+    from mashbox_b200.config.registry import Architecture, register_architecture
+    from mashbox_b200.parts import LayerRun, LayerSpec, ModelSpec, PartSpec
+
+    def spec(c):
+        norm = PartSpec("rms", width=c.hidden, eps=c.eps)
+        ffn = PartSpec("swiglu", hidden=c.hidden, intermediate=c.inner)
+        layers = []
+        for i, hd in enumerate(c.head_dims):
+            rope = PartSpec("rope", head_dim=hd, rotary_dim=hd, theta=10000.0)
+            att = PartSpec("attention", hidden=c.hidden, heads=c.kv_heads * c.groups, kv_heads=c.kv_heads, head_dim=hd,
+                           position=rope)
+            layers.append(LayerSpec(f"blk.{i}.", PartSpec("prenorm", norm=norm, mixer=att, ffn=ffn)))
+        return ModelSpec(hidden=c.hidden, vocab=c.vocab, embedding=PartSpec("table", vocab=c.vocab, hidden=c.hidden),
+                         layers=layers, schedule=[LayerRun(layer=i, cache=i, write=True) for i in range(len(layers))],
+                         final_norm=PartSpec("rms", width=c.hidden, eps=c.eps, name="output_norm.weight"),
+                         head=PartSpec("linear", vocab=c.vocab, hidden=c.hidden, tied=True))
+
+    def stored(c):
+        D, F = c.hidden, c.inner
+        out = {"token_embd.weight": ((c.vocab, D), "matrix"), "output_norm.weight": ((D,), "norm")}
+        for i, hd in enumerate(c.head_dims):
+            p, A, B = f"blk.{i}.", c.kv_heads * c.groups * hd, c.kv_heads * hd
+            out[p + "attn_norm.weight"] = ((D,), "norm")
+            out[p + "ffn_norm.weight"] = ((D,), "norm")
+            for n, s in (("attn_q", (A, D)), ("attn_k", (B, D)), ("attn_v", (B, D)), ("attn_output", (D, A)),
+                         ("ffn_gate", (F, D)), ("ffn_up", (F, D)), ("ffn_down", (D, F))):
+                out[p + n + ".weight"] = (s, "matrix")
+        return out
+
+    return register_architecture(Architecture("ToyTwoSizesForCausalLM", TwoSizesConfig, spec,
+                                              lambda c: (lambda n: (n, None)), stored))
+
+
+def two_sizes_plain(cfg, W, tokens):
+    T = len(tokens)
+    W = {k: v.double() for k, v in W.items()}
+    pos = np.arange(T)
+    x = W["token_embd.weight"][torch.tensor(tokens)]
+    for i, hd in enumerate(cfg.head_dims):
+        p, Hh = f"blk.{i}.", cfg.kv_heads * cfg.groups
+        fr = plain.rope_frequencies(10000.0, hd, None)
+        h = plain.rms_norm(x, W[p + "attn_norm.weight"], cfg.eps)
+        q = plain.rope_adjacent((h @ W[p + "attn_q.weight"].T).reshape(T, Hh, hd), pos, fr)
+        k = plain.rope_adjacent((h @ W[p + "attn_k.weight"].T).reshape(T, cfg.kv_heads, hd), pos, fr)
+        v = (h @ W[p + "attn_v.weight"].T).reshape(T, cfg.kv_heads, hd)
+        x = x + plain.attention(q, k, v, hd ** -0.5) @ W[p + "attn_output.weight"].T
+        h = plain.rms_norm(x, W[p + "ffn_norm.weight"], cfg.eps)
+        x = x + plain.swiglu(h, W[p + "ffn_gate.weight"], W[p + "ffn_up.weight"], W[p + "ffn_down.weight"])
+    return (plain.rms_norm(x, W["output_norm.weight"], cfg.eps) @ W["token_embd.weight"].T).numpy()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_attention_layers_of_two_head_sizes_in_one_model(tmp_path, dtype):
+    """layers with the same groups, kv heads and window but heads of 128, 32 and 64: each head size has its own plan of
+    attention work in a step (tiles of 256 packed rows on the tcgen05 kernel at 128 and 64, of 64 rows on the mma.sync
+    kernel at 32; a plan made for one and used for the other would leave rows out) and its own cache group"""
+    from mashbox_b200.engine.replay import make_runner, run_step
+    from mashbox_b200.weights.random_init import write_model_folder
+    two_sizes_architecture()
+    cfg = TwoSizesConfig("ToyTwoSizesForCausalLM", hidden=128, vocab=157, inner=160, kv_heads=2, groups=2,
+                         head_dims=(128, 32, 64), eps=1e-5)
+    folder = write_model_folder(str(tmp_path / "two"), cfg, 9, dtype=getattr(torch, dtype), std=0.08, norm_std=0.1,
+                                std_by_name=(("token_embd", 1.0), ("attn_output", 0.03), ("ffn_down", 0.03)))
+    runner = make_runner(folder, dtype, 1024, page_size=16)
+    assert sorted(g.need.tensors[0] for g in runner.cache.groups) == [(2, 32), (2, 64), (2, 128)]
+    W = plain.read_safetensors(os.path.join(folder, "model.safetensors"))
+    rng = np.random.default_rng(4)
+    a, b = rng.integers(0, 157, 300).tolist(), rng.integers(0, 157, 41).tolist()
+    wa, wb = two_sizes_plain(cfg, W, a), two_sizes_plain(cfg, W, b)
+    bar = lambda got, want, what: assert_logits(got, want, "float32", what) if dtype == "float32" else \
+        close(torch.from_numpy(got), torch.from_numpy(want), "bfloat16", what)
+    # a long portion (prompt-form tiles of 256 packed rows on tcgen05 at both head sizes) beside single tokens and a
+    # short portion of another request
+    out = run_step(runner, dict(step=0, entries=[dict(id="a", tokens=a[:280], want=[0, 100, 279]),
+                                                 dict(id="b", tokens=b[:30], want=[29])], end=[])).numpy()
+    bar(out[:3], wa[[0, 100, 279]], "two head sizes, portion of a")
+    bar(out[3:], wb[29:30], "two head sizes, portion of b")
+    got_a, got_b = [], []
+    for i in range(11):
+        entries = [dict(id="a", tokens=[a[280 + i]], want=[0]), dict(id="b", tokens=[b[30 + i]], want=[0])]
+        o = run_step(runner, dict(step=1 + i, entries=entries, end=[])).numpy()
+        got_a.append(o[0])
+        got_b.append(o[1])
+    bar(np.stack(got_a), wa[280:291], "two head sizes, a decoded")
+    bar(np.stack(got_b), wb[30:41], "two head sizes, b decoded")
+    runner.cache.check()
