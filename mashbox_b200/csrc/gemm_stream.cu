@@ -414,6 +414,9 @@ MB_API long long mb_gemm_stream_counters(int M) { return (M + 31) / 32; }
 // dealing equal shares (q/k/v as 192 tiles of 32 rows: 14.4 us against 11.5; gate/up as 224 of 64: 42.5 against 38.7)
 // loses more to the tiles that blocks share than the idle SMs cost, and tiles of 48 rows for q/k/v (128 blocks instead
 // of 96) and of 112 rows for gate/up (128 instead of 112), one block each, were slower as well (12.6 against 11.4).
+// Nor did it help to have a product's producer warp, once its own last weights are on their way, ask the L2 for the
+// first ring of the product that follows (cp.async.bulk.prefetch.tensor with that product's tensor map): a layer's four
+// products took 85.3 us against 82.2.
 // The height of a row tile: the largest of 128, 64, 32 that gives at least 0.6 tiles per SM, so that a matrix of few
 // rows still has a tile for most SMs and no tile is shared (then the grid is one block per tile); matrices with more
 // tiles than SMs, or too few even at 32 rows, are cut into equal shares of items.  least: the smallest height allowed.
