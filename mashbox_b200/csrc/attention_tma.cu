@@ -431,9 +431,10 @@ __global__ void __launch_bounds__(160, 2) attn_tma_kernel(const AttnParams P, co
         cluster_sync();
         const float* fin = reinterpret_cast<const float*>(kvs) + 4 * 16 * HD + 2 * 4 * 16;
         const uint32_t fin_addr = smem_u32(fin);
-        const int rows = min(BM, R - row0), per = HD / n_splits;      // columns of a row this block writes (HD / splits >= 4)
+        const int rows = min(BM, R - row0), per = (HD + n_splits - 1) / n_splits;      // columns of a row this block writes
         for (int it = tid; it < rows * per; it += 128) {
             const int row = it / per, d = split * per + it % per, r = row0 + row;
+            if (d >= HD) continue;
             float M = -INFINITY;
             for (int s = 0; s < n_splits; s++) M = fmaxf(M, cluster_ld(cluster_map(fin_addr + (16 * HD + 2 * row) * 4, s)));
             float acc = 0.0f, L = 0.0f;
@@ -598,7 +599,17 @@ static int launch_tma(const AttnParams& P, const CUtensorMap& kmap, const CUtens
         }
         configured = true;
     }
-    if (n_items < 0) return max_cluster;                 // a query (mb_attn_tma_max_cluster)
+    if (n_items == -1) return max_cluster;               // a query (mb_attn_tma_max_cluster)
+    if (n_items < -1) {                                  // a query: how many clusters of -n_items blocks the device holds at once
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = -n_items; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(-n_items, 1); cfg.blockDim = dim3(160); cfg.dynamicSmemBytes = smem; cfg.attrs = &attr; cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, attn_tma_kernel<HD, DECODE, STAGES, ROPE>, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
+        return n;
+    }
     if (P.cluster > max_cluster || (P.cluster > 1 && n_items % P.cluster)) return -2;
     const cudaError_t e = mb_launch_cluster(mb_pdl != 0, P.cluster > 1 ? P.cluster : 1, attn_tma_kernel<HD, DECODE, STAGES, ROPE>,
                                             dim3(n_items, P.KV), dim3(160), smem, st, P, kmap, vmap);
@@ -619,7 +630,7 @@ static int attn_tma_run(const void* q, int q_stride, void* out, const void* kpoo
                         int window, float scale, int* counters, int* err, cudaStream_t st, int fuse, const float* bias,
                         const float* freqs, int RD, int pairing, int cluster = 0) {
     if (n_items == 0) return 0;
-    if (cluster > 1 && (!decode || cluster > 8 || (cluster & (cluster - 1)) || HD / cluster < 4)) return -2;
+    if (cluster > 1 && (!decode || cluster > 8)) return -2;
     if (!mb_attn_tma_supports(HD, page) || KV < 1 || H % KV || KV > 65535) return -2;
     if (fuse && (!decode || H / KV > 16 || RD % 2 || RD > HD || RD < 0 || !kpool || !vpool)) return -2;
     AttnParams P;
@@ -674,7 +685,7 @@ MB_API int mb_attn_tma_rope_bf16(const void* qkv, int q_stride, void* out, void*
                         err, st, 1, bias, freqs, RD, pairing);
 }
 
-// The decode form launched as thread-block clusters: every sequence of the launch is cut into `cluster` splits (2, 4 or
+// The decode form launched as thread-block clusters: every sequence of the launch is cut into `cluster` splits (2 to
 // 8; the items of a sequence in the order of the splits), a cluster is the splits of one sequence and kv head, and
 // their results meet in the cluster's shared memory instead of global memory: no partial buffers, no counters.  rope:
 // as mb_attn_tma_rope_bf16 (bias / freqs may be null), 0: q is the rotated queries as for mb_attn_tma_bf16.
@@ -689,11 +700,21 @@ MB_API int mb_attn_tma_cluster_bf16(const void* q, int q_stride, void* out, void
                         rope, bias, freqs, RD, pairing, cluster);
 }
 
+static int attn_tma_query(int HD, int rope, int what) {
+    AttnParams P{};
+    CUtensorMap m{};
+    if (HD == 128) return rope ? launch_tma<128, true, 3, true>(P, m, m, what, nullptr) : launch_tma<128, true, 3>(P, m, m, what, nullptr);
+    return rope ? launch_tma<64, true, 4, true>(P, m, m, what, nullptr) : launch_tma<64, true, 4>(P, m, m, what, nullptr);
+}
+
 // the largest cluster mb_attn_tma_cluster_bf16 can be given on this device for this head size (1: none)
 MB_API int mb_attn_tma_max_cluster(int HD, int rope) {
     if (HD != 64 && HD != 128) return 1;
-    AttnParams P{};
-    CUtensorMap m{};
-    if (HD == 128) return rope ? launch_tma<128, true, 3, true>(P, m, m, -1, nullptr) : launch_tma<128, true, 3>(P, m, m, -1, nullptr);
-    return rope ? launch_tma<64, true, 4, true>(P, m, m, -1, nullptr) : launch_tma<64, true, 4>(P, m, m, -1, nullptr);
+    return attn_tma_query(HD, rope, -1);
+}
+
+// how many clusters of `cluster` (2 to 8) such blocks the device holds at the same time (0: none)
+MB_API int mb_attn_tma_active_clusters(int HD, int rope, int cluster) {
+    if ((HD != 64 && HD != 128) || cluster < 2 || cluster > 8) return 0;
+    return attn_tma_query(HD, rope, -cluster);
 }

@@ -511,6 +511,19 @@ def attention_tma_max_cluster(HD):
     return _max_cluster[HD]
 
 
+_active_clusters = {}
+
+
+def attention_tma_active_clusters(HD, cluster):
+    """how many clusters of `cluster` blocks of attention_tma's decode form the device holds at the same time"""
+    if (HD, cluster) not in _active_clusters:
+        lib = load_library("attention_tma")
+        lib.mb_attn_tma_active_clusters.argtypes = [c_int, c_int, c_int]
+        lib.mb_attn_tma_active_clusters.restype = c_int
+        _active_clusters[HD, cluster] = min(lib.mb_attn_tma_active_clusters(HD, r, cluster) for r in (0, 1))
+    return _active_clusters[HD, cluster]
+
+
 def attention_tma(q, q_stride, out, kpool, vpool, items, n_items, decode, q_start, q_len, pos0, part_base, seq_row,
                   table, part_o, part_ml, max_splits, H, KV, HD, page, num_pages, window, scale, err, merge=False,
                   rope=None, cluster=0):

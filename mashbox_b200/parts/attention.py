@@ -117,12 +117,18 @@ class Attention:
         page = ctx.cache.page_size
         if (any(decode_form) and base[True] < target and ctx.options.get("attention_kernel", "tma") == "tma"
                 and ctx.ops.attention_tma_supports(self.HD, page) and ctx.options.get("attention_clusters", True)):
-            want = min(max_splits, -(-target // base[True]), max(key_tiles(s) for s in range(S) if decode_form[s]) // 2)
-            want = 1 << (max(1, want).bit_length() - 1)
+            raw = min(max_splits, -(-target // base[True]), max(key_tiles(s) for s in range(S) if decode_form[s]) // 2)
+            want = 1 << (max(1, raw).bit_length() - 1)
             # only when the cluster holds all the splits the launch wants anyway: at one or two sequences (32 and 16
             # splits) more, smaller blocks that meet through global memory are faster than clusters of 8
-            if 2 <= want <= min(ctx.ops.attention_tma_max_cluster(self.HD), self.HD // 4):
-                cluster = want
+            most = ctx.ops.attention_tma_max_cluster(self.HD)
+            if 2 <= want <= most:
+                # the largest cluster, of any size, that leaves all clusters of the launch on the device at once with
+                # room to spare: the kernel before this one still holds SMs when the first clusters are placed
+                room = float(ctx.options.get("attention_cluster_room", 0.91))
+                fits = [c for c in range(2, min(raw, most) + 1)
+                        if base[True] <= room * ctx.ops.attention_tma_active_clusters(self.HD, c)]
+                cluster = int(ctx.options.get("attention_cluster_size", 0)) or (max(fits) if fits else 0)
         for s in range(S):
             kv_tiles = key_tiles(s)
             ns = 1

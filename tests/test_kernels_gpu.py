@@ -737,7 +737,8 @@ def test_decode_attention_with_the_rotation_folded_in(HD, H, KV, page, window, s
 
 @pytest.mark.parametrize("HD,H,KV,page,window,cluster,rope", [
     (128, 32, 8, 16, None, 8, True), (128, 8, 2, 16, None, 4, False), (64, 6, 2, 32, 300, 8, True),
-    (64, 32, 8, 8, None, 2, False), (128, 16, 1, 64, None, 8, False), (128, 5, 5, 16, 70, 2, True)])
+    (64, 32, 8, 8, None, 2, False), (128, 16, 1, 64, None, 8, False), (128, 5, 5, 16, 70, 2, True),
+    (128, 32, 8, 16, None, 7, True), (64, 6, 2, 32, None, 3, False), (128, 8, 2, 16, 300, 5, True), (64, 4, 4, 16, None, 6, True)])
 def test_decode_attention_in_clusters(HD, H, KV, page, window, cluster, rope):
     """the decode form launched as thread-block clusters, one block per split of a sequence and kv head, the splits
     meeting in the cluster's shared memory: the same bits as the launch whose splits meet through global memory and a
