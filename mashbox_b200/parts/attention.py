@@ -22,6 +22,24 @@ from .base import PartSpec, make, register
 DECODE_ROWS, PREFILL_ROWS, KEY_TILE = 16, 64, 64
 
 
+def many_splits(blocks, work, slots, head_dim, most=4):
+    """Into how many splits (1 to `most`) to cut each of `blocks` decode-form tiles of the TMA attention kernel, `work`
+    key tiles in all, when there are more of them than half the `slots` the device has for such blocks.  The model: the
+    blocks run in rounds of `slots`; a round of n blocks of w key tiles takes w * max(n, enough) / bandwidth, `enough`
+    being the number of blocks whose tiles in flight (three or four stages of 64 keys) keep the memory busy, about 19
+    MB in all; every further split costs 2 % (its partial results meet through global memory).  The fewest splits
+    within 1 % of the best."""
+    enough = max(1, int(19.2e6 // ((3 if head_dim > 64 else 4) * 2 * 64 * head_dim * 2)))
+    costs = []
+    for ns in range(1, max(1, most) + 1):
+        n = blocks * ns
+        full, rest = divmod(n, slots)
+        rounds = full * slots + (max(rest, enough) if rest else 0)
+        costs.append((work / n) * rounds * (1.0 + 0.02 * (ns - 1)))
+    best = min(costs)
+    return 1 + next(i for i, c in enumerate(costs) if c <= 1.01 * best)
+
+
 class Attention:
     @property
     def graph_safe(self):
@@ -128,7 +146,20 @@ class Attention:
                 room = float(ctx.options.get("attention_cluster_room", 0.91))
                 fits = [c for c in range(2, min(raw, most) + 1)
                         if base[True] <= room * ctx.ops.attention_tma_active_clusters(self.HD, c)]
-                cluster = int(ctx.options.get("attention_cluster_size", 0)) or (max(fits) if fits else 0)
+                cluster = max(fits) if fits else 0
+        if ctx.options.get("attention_cluster_size") is not None and any(decode_form):
+            cluster = int(ctx.options["attention_cluster_size"])
+        # More decode-form tiles than half the blocks the device holds: cutting them to fill `target` blocks would mean
+        # one or two splits, and what then decides is the last, partly filled round of blocks: too few blocks to keep
+        # the memory busy (8 kv heads, 8,192 keys: 20 sequences as 320 blocks take 8.2 ms a step, as 480 blocks 6.9; 40
+        # as 320 blocks 12.4, as 1,280 10.6).  many_splits() picks the number of splits by a model of that.
+        crowd = 0
+        if (not cluster and any(decode_form) and ctx.options.get("attention_kernel", "tma") == "tma"
+                and ctx.ops.attention_tma_supports(self.HD, page) and ctx.options.get("attention_splits") is None):
+            slots = 2 * ctx.ops.attention_tma_active_clusters(self.HD, 2)
+            if slots and 2 * base[True] > slots:
+                work = sum(key_tiles(s) for s in range(S) if decode_form[s]) * KV
+                crowd = many_splits(base[True], work, slots, self.HD, min(4, max_splits))
         for s in range(S):
             kv_tiles = key_tiles(s)
             ns = 1
@@ -139,6 +170,8 @@ class Attention:
             if ctx.q_len[s] <= DECODE_ROWS and base[decode_form[s]] < target and (decode_form[s] or not tc5):
                 ns = max(1, min(max_splits, -(-target // base[decode_form[s]]), kv_tiles // 2))
                 ns = 1 << (ns.bit_length() - 1)                    # a power of two: few distinct work-list shapes
+            if decode_form[s] and (crowd or ctx.options.get("attention_splits") is not None):
+                ns = max(1, min(crowd or int(ctx.options["attention_splits"]), kv_tiles // 2))
             if ns > 1:
                 part_base[s] = len(part_tok) // 2
                 for t in range(ctx.q_len[s]):
