@@ -140,6 +140,11 @@ class Attention:
             # only when the cluster holds all the splits the launch wants anyway: at one or two sequences (32 and 16
             # splits) more, smaller blocks that meet through global memory are faster than clusters of 8
             most = ctx.ops.attention_tma_max_cluster(self.HD)
+            longest = max(key_tiles(s) for s in range(S) if decode_form[s])
+            if want > most and longest <= 6 * most:
+                # ... unless the sequences are short: up to six key tiles per block, the cheaper meeting of a cluster
+                # outweighs the longer blocks (one sequence of 2,048 keys: 9.2 us in a cluster of 8, 10.4 as 16 splits)
+                raw = want = most
             if 2 <= want <= most:
                 # the largest cluster, of any size, that leaves all clusters of the launch on the device at once with
                 # room to spare: the kernel before this one still holds SMs when the first clusters are placed
