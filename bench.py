@@ -301,10 +301,13 @@ def run_workload(a):
 
     def timed_launch(prep, before=None):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        st = eng.runner.stats
+        was = (st["graph_captures"], st["graph_replays"])
         e0.record()
         f = inner(prep, before)
         e1.record()
-        spans.append((e0, e1, sum(p.count for p in prep[0])))
+        kind = "captured" if st["graph_captures"] > was[0] else "replayed" if st["graph_replays"] > was[1] else "launched"
+        spans.append((e0, e1, sum(p.count for p in prep[0]), kind))
         return f
 
     def once(timed):
@@ -323,7 +326,12 @@ def run_workload(a):
                 new_at_first = sum(len(r.generated) for r in rows)
         torch.cuda.synchronize()
         wall = time.perf_counter() - t0
-        gpu_ms = sum(e0.elapsed_time(e1) for e0, e1, _ in spans)
+        gpu_ms = sum(e0.elapsed_time(e1) for e0, e1, _, _ in spans)
+        kinds = {}
+        for e0, e1, _, kind in spans:
+            k = kinds.setdefault(kind, [0, 0.0])
+            k[0] += 1
+            k[1] = round(k[1] + e0.elapsed_time(e1), 1)
         new = sum(len(r.generated) for r in rows)
         assert all(r.finish == "length" for r in rows), [r.finish for r in rows]
         rs, ss = eng.runner.stats, eng.scheduler.stats
@@ -332,6 +340,7 @@ def run_workload(a):
                     preemptions=ss["preemptions"] - before[1]["preemptions"],
                     graph_captures=rs["graph_captures"] - before[0]["graph_captures"],
                     graph_replays=rs["graph_replays"] - before[0]["graph_replays"],
+                    capture_s=rs["capture_s"] - before[0]["capture_s"], kinds=kinds,
                     launches=ops.COUNTERS["launches"] - l0, deferred=eng.stats["deferred"])
 
     eng._launch = timed_launch
@@ -361,7 +370,7 @@ def run_workload(a):
                                                            (r["new_tokens"] - r["new_at_first"]) / decode_s),
                      "until_all_first_tokens_s": r["until_all_first_tokens_s"],
                      "preemptions": r["preemptions"], "graph_captures": r["graph_captures"],
-                     "graph_replays": r["graph_replays"], "steps_deferred": r["deferred"],
+                     "graph_replays": r["graph_replays"], "graph_capture_s": round(r["capture_s"], 3), "steps_and_gpu_ms_by_kind": r["kinds"], "steps_deferred": r["deferred"],
                      "gpu_s_inside_steps": r["gpu_ms_in_steps"] / 1e3,
                      "share_of_wall_outside_steps": 1.0 - r["gpu_ms_in_steps"] / 1e3 / wall},
         "gpu_launches": r["launches"], "impl": "ours",

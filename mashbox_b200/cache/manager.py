@@ -92,14 +92,21 @@ class CacheManager:
         self.state_needs = dict(states)
         self.state = {}
         self.requests = {}
+        # Beside the pages, rows and state slots that requests are given there is one more of each on the device,
+        # outside the bookkeeping: a sequence of one token at position 0 that reads and writes only the spare page.
+        # The step function fills decode batches up with such sequences (their results are dropped), so that batches
+        # of nearby sizes share one captured graph.
+        self.pool_pages = self.num_pages + 1
+        self.spare_row = self.spare_state_slot = self.max_requests
         if device is not None:
             import torch
             for g in self.groups:
-                g.pools = [torch.zeros((len(g.cache_ids), self.num_pages, heads, self.page_size, width), dtype=dtype,
+                g.pools = [torch.zeros((len(g.cache_ids), self.pool_pages, heads, self.page_size, width), dtype=dtype,
                                        device=device) for heads, width in g.need.tensors]
-                g.device_table = torch.full((self.max_requests, self.max_blocks), -1, dtype=torch.int32, device=device)
+                g.device_table = torch.full((self.max_requests + 1, self.max_blocks), -1, dtype=torch.int32, device=device)
+                g.device_table[self.spare_row, 0] = self.num_pages
             for cid, s in self.state_needs.items():
-                self.state[cid] = torch.zeros((self.max_requests,) + tuple(s.shape), dtype=getattr(torch, s.dtype),
+                self.state[cid] = torch.zeros((self.max_requests + 1,) + tuple(s.shape), dtype=getattr(torch, s.dtype),
                                               device=device)
 
     # -------------------------------------------------------------------------------------------- requests

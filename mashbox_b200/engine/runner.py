@@ -12,6 +12,8 @@ captured when it comes a second time -- decode batches, and the equal portions a
 least recently captured graph goes when there are MAX_GRAPHS of them.  Models with a part that does not declare itself
 graph_safe run without graphs.
 """
+import time
+
 import numpy as np
 import torch
 
@@ -44,7 +46,8 @@ class ModelRunner:
         self.graphs, self.seen_signatures = {}, {}
         self.use_graphs = (bool(engine_config.cuda_graphs) and not self.options.get("no_graphs", False)
                            and getattr(model, "graph_safe", False))
-        self.stats = dict(steps=0, tokens=0, graph_replays=0, graph_captures=0)
+        self.stats = dict(steps=0, tokens=0, graph_replays=0, graph_captures=0, capture_s=0.0)
+        self.capture_stream = None
 
     # -------------------------------------------------------------------------------------------- the step
     def step(self, entries):
@@ -68,7 +71,7 @@ class ModelRunner:
         self.cache.flush_tables()
         logits = self._run_graph(ctx) if self.use_graphs else self.model.forward(ctx)
         self.commit(entries)
-        return logits
+        return logits if logits is None or ctx.real_out == ctx.n_out else logits[:ctx.real_out]
 
     def begin(self, entries):
         """prepare + upload: a StepContext ready for model.forward (tests of single parts use it)"""
@@ -117,11 +120,30 @@ class ModelRunner:
         positions = np.concatenate([p + np.arange(n, dtype=np.int32) for p, n in zip(pos0, q_len)])
         tok_row = np.repeat(rows, q_len)
         want = np.asarray([q_start[i] + int(w) for i, (_, _, ws) in enumerate(entries) for w in ws], np.int32)
+        state_slots = [r.state_slot for r in reqs]
+        patches = list(patches)
+        real_out = len(want)
+
+        # A decode batch is filled up to the next size of a coarse grid with sequences of one token on the cache's
+        # spare page (their logits are computed and dropped), so that batches of nearby sizes are one graph.
+        fill = self.filled_size(S) - S if self.use_graphs and N == S and len(want) == S else 0
+        if fill > 0:
+            more = np.arange(N, N + fill, dtype=np.int32)
+            zeros = np.zeros(fill, np.int32)
+            spare = np.full(fill, cache.spare_row, np.int32)
+            token_ids, positions = np.concatenate([token_ids, zeros]), np.concatenate([positions, zeros])
+            tok_row, rows = np.concatenate([tok_row, spare]), np.concatenate([rows, spare])
+            want, q_start = np.concatenate([want, more]), np.concatenate([q_start, more])
+            q_len, pos0 = q_len + [1] * fill, np.concatenate([pos0, zeros])
+            state_slots = state_slots + [cache.spare_state_slot] * fill
+            if len(patches) == S:                                    # every token of the step is filled in on the device
+                patches += [(int(i), 0) for i in more]
+            S, N = S + fill, N + fill
 
         ctx = StepContext(self.env, cache, self.ws, self.inputs, self.err, self.options)
-        ctx.N, ctx.S, ctx.n_out = N, S, len(want)
+        ctx.N, ctx.S, ctx.n_out, ctx.real_out = N, S, len(want), real_out
         ctx.rows, ctx.q_start, ctx.q_len, ctx.pos0 = rows.tolist(), q_start.tolist(), q_len, pos0.tolist()
-        ctx.state_slots = [r.state_slot for r in reqs]
+        ctx.state_slots = state_slots
         inp = self.inputs
         inp.reset()
         inp.add("token_ids", token_ids)
@@ -134,10 +156,19 @@ class ModelRunner:
         inp.add("seq_row", rows)
         inp.add("state_slot", ctx.state_slots)
         inp.add("patch", np.asarray([v for pair in patches for v in pair], np.int32))
+        self.model.prepare(ctx)
+        inp.mark()                          # what follows is read after the model has run: not part of a graph's shape
         for name, array in (extra or {}).items():
             inp.add(name, array)
-        self.model.prepare(ctx)
         return ctx
+
+    def filled_size(self, S):
+        """the size a decode batch of S sequences is filled up to: itself up to 16 (those steps run other kernels than
+        larger ones), then steps of 4 up to 32, of 8 up to 128, of 16 beyond; never more than the logits buffer holds"""
+        if S <= 16 or not self.options.get("fill_decode_batches", True):
+            return S
+        step = 4 if S <= 32 else 8 if S <= 128 else 16
+        return max(S, min(-(-S // step) * step, int(self.options["logit_rows"])))
 
     def patch_token(self, index, token):
         """Sets token `index` of the prepared step (its place among the step's N tokens) before launch()."""
@@ -163,12 +194,28 @@ class ModelRunner:
         self.seen_signatures[sig] = count + 1
         if count == 0:                      # first time: run eagerly (loads kernels, sizes buffers)
             return self.model.forward(ctx)
-        torch.cuda.synchronize(self.device)
+        # Captured on a stream of its own that first waits for the step's stream; the GPU goes on with the steps it
+        # has queued meanwhile (no device-wide wait, no emptying of the allocator's cache).
+        t0 = time.perf_counter()
+        main = torch.cuda.current_stream(self.device)
+        if self.capture_stream is None:
+            self.capture_stream = torch.cuda.Stream(self.device)
+        self.capture_stream.wait_stream(main)
         graph = torch.cuda.CUDAGraph()
         before = kernels.COUNTERS["launches"]
-        with torch.cuda.graph(graph):
-            logits = self.model.forward(ctx)
+        with torch.cuda.stream(self.capture_stream):
+            graph.capture_begin(capture_error_mode="thread_local")
+            try:
+                logits = self.model.forward(ctx)
+            except BaseException:
+                try:
+                    graph.capture_end()
+                except Exception:
+                    pass
+                raise
+            graph.capture_end()
         captured = kernels.COUNTERS["launches"] - before
+        main.wait_stream(self.capture_stream)
         graph.replay()
         while len(self.graphs) >= self.MAX_GRAPHS:
             self.graphs.pop(next(iter(self.graphs)))
@@ -176,6 +223,7 @@ class ModelRunner:
             self.seen_signatures = {s: n for s, n in self.seen_signatures.items() if s in self.graphs}
         self.graphs[sig] = (graph, logits, captured)
         self.stats["graph_captures"] += 1
+        self.stats["capture_s"] += time.perf_counter() - t0          # the host's time
         return logits
 
     def check(self):

@@ -206,7 +206,7 @@ class Attention:
         qkv = ctx.ws.get("qkv", N, (width,), ctx.dtype)
         group, kpool, vpool = ctx.cache.layer_cache(run.cache)
         table = group.device_table
-        page, pages = ctx.cache.page_size, ctx.cache.num_pages
+        page, pages = ctx.cache.page_size, ctx.cache.pool_pages
         rot = self.position.rotation() if self.position is not None else (None, HD, 0)
         # A step in which every sequence brings one token (N == S: that follows from the lengths of the step's arrays):
         # the decode form of the TMA attention kernel rotates, stores and attends in one launch.

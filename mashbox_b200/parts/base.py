@@ -148,6 +148,11 @@ class StepInputs:
 
     def reset(self):
         self.arrays, self.offsets, self.used, self.views = {}, {}, 0, {}
+        self.marked = None
+
+    def mark(self):
+        """the arrays added so far are those the model reads: the signature is theirs alone"""
+        self.marked = len(self.arrays)
 
     def add(self, name, array):
         a = np.ascontiguousarray(array, dtype=np.int32).reshape(-1)
@@ -160,7 +165,8 @@ class StepInputs:
         return name in self.arrays
 
     def signature(self):
-        return tuple((n, len(a)) for n, a in self.arrays.items())
+        sig = tuple((n, len(a)) for n, a in self.arrays.items())
+        return sig if self.marked is None else sig[:self.marked]
 
     def upload(self):
         """Copies the arrays to the device buffer through one of several pinned staging buffers: a staging buffer is
@@ -208,7 +214,7 @@ class StepContext:
     def __init__(self, env, cache, ws, inputs, err, options):
         self.env, self.ops, self.dtype, self.device = env, env.ops, env.dtype, env.device
         self.cache, self.ws, self.inputs, self.err, self.options = cache, ws, inputs, err, options
-        self.N = self.S = self.n_out = 0
+        self.N = self.S = self.n_out = self.real_out = 0
         self.rows = self.state_slots = self.q_start = self.q_len = self.pos0 = None
         self.memo = {}
 
