@@ -34,7 +34,14 @@ def _p(t):
     return None if t is None else t.data_ptr()
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream():
+    # the current stream's handle; torch.cuda.current_stream() costs several microseconds a call, a tenth of the host's
+    # time in a step of two hundred launches, the raw accessor next to nothing
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 

@@ -109,3 +109,19 @@ def test_a_pending_delta_goes_through_the_norm_kernel_and_drops_what_was_held():
     block.forward(ctx, x, ("delta", None), "run")
     assert log[0] == ("norm kernel", "norm1", True)
     assert log[1] == ("mixer", "normed by norm1", False, False, True)
+
+
+def test_signature_of_step_inputs_ends_at_the_mark():
+    """arrays added after mark() (the sampler's settings) are sent with the step but are not part of a graph's shape"""
+    from mashbox_b200.parts.base import StepInputs
+    inp = StepInputs(None)
+    inp.add("a", [1, 2, 3])
+    inp.add("b", [])
+    assert inp.signature() == (("a", 3), ("b", 0))
+    inp.mark()
+    inp.add("sample_rows", [0] * 7)
+    assert inp.signature() == (("a", 3), ("b", 0)) and inp.has("sample_rows")
+    inp.reset()
+    inp.add("a", [1])
+    inp.add("late", [2, 3])
+    assert inp.signature() == (("a", 1), ("late", 2))

@@ -391,3 +391,54 @@ def test_traced_generation_gives_the_same_hashes_alone_and_batched(tmp_path_fact
     # without tracing the result has no "lh" key
     folder2, plain_eng = engine(tmp, "A", "f32")
     assert "lh" not in plain_eng.generate(H.prompts_for("A", (7,)), max_new=2)
+
+
+@pytest.mark.parametrize("name,mode", [("B", "f32"), ("D", "bf16"), ("A", "f32")])
+def test_decode_batches_filled_up_to_a_grid_share_graphs_and_change_nothing(tmp_path, name, mode):
+    """Decode batches of 17 to 20 sequences run as batches of 20 (the rest are one-token sequences on the cache's spare
+    page, whose results are dropped): one captured graph serves all four sizes, the logits of the real sequences are
+    the same bits as without the filling (float32; bfloat16: the same tokens' logits within the test's bars, since a
+    library product of 20 rows need not round as one of 17), and the bookkeeping never sees the spare page."""
+    from mashbox_b200.engine.loading import load_model
+    from mashbox_b200.config.engine import EngineConfig
+    from mashbox_b200.engine.runner import ModelRunner
+    dtype, opts = H.MODES[mode]
+    folder = H.make_folder(tmp_path, name, H.store_for(dtype))
+    page = H.TINY[name][2]
+    prompts = H.prompts_for(name, tuple(8 + 2 * i for i in range(20)), seed=9)
+    SIZES = (20, 19, 18, 17, 18, 20)
+
+    def run(options):
+        cfg = EngineConfig(dtype=dtype, page_size=page, max_tokens=20 * 128, max_requests=24, max_tokens_per_step=1024,
+                           chunk=1024, device="cuda:0")
+        runner = ModelRunner(load_model(folder, dtype=dtype, device="cuda:0"), cfg, dict(opts, **options))
+        for i in range(20):
+            runner.cache.admit(i)
+        runner.step([(i, p[:-6], []) for i, p in enumerate(prompts)])
+        fed = [len(p) - 6 for p in prompts]
+        got = []
+        for live in SIZES:                                             # each size of the grid cell, two of them twice
+            lg = runner.step([(i, [prompts[i][fed[i]]], [0]) for i in range(live)])
+            assert lg.shape[0] == live
+            for i in range(live):
+                fed[i] += 1
+            got.append((lg.float().cpu().numpy(), list(fed)))
+        runner.check()
+        for i in range(20):
+            runner.cache.release(i)
+        runner.cache.check()
+        assert all(f == runner.cache.num_pages for f in runner.cache.free_pages())
+        return got, runner.stats
+
+    filled, st = run({})
+    exact, st0 = run({"fill_decode_batches": False})
+    # sizes 20, 19, 18, 17, 18, 20: filled, all six steps have one shape (the first sizes the buffers, the second is the
+    # first of its shape with those buffers, the third is captured, three replays); unfilled, only 18 comes twice
+    # after the first step and nothing is replayed
+    assert (st["graph_captures"], st["graph_replays"]) == (1, 3), st
+    assert (st0["graph_captures"], st0["graph_replays"]) == (1, 0), st0
+    for (a, fed), (b, _), live in zip(filled, exact, SIZES):
+        if mode == "f32":
+            assert np.array_equal(a, b)
+        for i in (0, live - 1):
+            H.check(a[i:i + 1], folder, prompts[i][:fed[i]], mode, f"filled batch of {live}, row {i}", slice(-1, None))
