@@ -87,7 +87,6 @@ class Model:
             after = self.layers[self.schedule[i + 1].layer] if i + 1 < len(self.schedule) else None
             ctx.next_first_norm = after.first_norm() if hasattr(after, "first_norm") else None
             pending = self.layers[run.layer].forward(ctx, x, pending, run)
-        ctx.ops.flush_chain()                   # products that still wait to be launched together (ops.CHAIN)
         if ctx.n_out == 0:
             return None
         h = self.final_norm.forward(ctx, x, pending, rows=ctx.dev("want"))

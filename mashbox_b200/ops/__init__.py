@@ -37,19 +37,12 @@ def _p(t):
 _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
 
 
-def _stream_now():
+def _stream():
     # the current stream's handle; torch.cuda.current_stream() costs several microseconds a call, a tenth of the host's
     # time in a step of two hundred launches, the raw accessor next to nothing
     if _raw_stream is not None:
         return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
-
-
-def _stream():
-    """the stream a face launches on; products that wait in the chain (flush_chain) are launched first"""
-    if _chain:
-        flush_chain()
-    return _stream_now()
 
 
 def _cuda(*tensors):
@@ -87,7 +80,7 @@ def scratch_generation():
 # weights), and waits for that kernel by itself before it touches anything a kernel writes.  One switch per library,
 # set through set_pdl(); the engine's option "pdl" turns it on.
 PDL = {"on": False}
-_PDL_SETTERS = {"gemm_stream": "mb_gemm_stream_set_pdl", "gemm_chain": "mb_gemm_chain_set_pdl", "elementwise": "mb_elementwise_set_pdl",
+_PDL_SETTERS = {"gemm_stream": "mb_gemm_stream_set_pdl", "elementwise": "mb_elementwise_set_pdl",
                 "attention_tma": "mb_attn_tma_set_pdl"}
 _pdl_applied = {}
 
@@ -142,7 +135,6 @@ def error_word(device):
 
 def check_error_word(err):
     """Reads the device error word (a synchronisation) and raises if a kernel left a code there."""
-    flush_chain()
     code = int(err.item())
     if code:
         err.zero_()
@@ -204,7 +196,6 @@ def linear(a, w, out=None, out_dtype=None):
     """a (N, K) @ w (M, K)^T -> (N, M).  float32: the package's own fixed-order FFMA kernel (no TF32, no tensor
     cores).  bfloat16: cuBLAS with float accumulation; out_dtype float32 keeps the accumulator's precision."""
     _cuda(a, w)
-    flush_chain()                       # the library's product is not launched through _stream()
     N, K = a.shape
     M = w.shape[0]
     if a.dtype == torch.float32:
@@ -345,8 +336,6 @@ def configure(options):
     for k in GEMV:
         GEMV[k] = int(options.get("gemv_tokens", 0 if pdl else 1))
     STREAM["tokens"] = int(options.get("stream_tokens", 16))
-    CHAIN["on"] = bool(options.get("chain_products", True))
-    CHAIN["most"] = max(1, min(4, int(options.get("chain_most", 4))))
 
 
 _stream_scratch = {}
@@ -372,76 +361,14 @@ def _stream_buffers(device, M):
     return sc
 
 
-# ---- chains.  A streaming product called with chain=True is not launched at once: it waits in a list until a launch of
-# anything else of this package comes (every face asks for its stream through _stream()), until the list is full, or
-# until flush_chain() is called; what has gathered by then goes to the GPU as ONE kernel (gemm_chain.cu: the products
-# one after the other with a grid-wide barrier between them and the weights of the next one on their way meanwhile).
-# A product that a chain cannot take (shared row tiles, float output) is launched by itself, in its place.  Only
-# callers whose next access to the result is again a face of this package may say chain=True.
-CHAIN = {"on": True, "most": 4}
-_chain = []
-_chain_sync = {}
-_chain_takes = {}
-
-
-class _ChainMember(ctypes.Structure):
-    _fields_ = [("act", c_void_p), ("ssq", c_void_p), ("eps", c_float), ("W", c_void_p), ("out", c_void_p),
-                ("bias", c_void_p), ("ssq_out", c_void_p), ("next_w", c_void_p), ("scaled_out", c_void_p),
-                ("N", c_int), ("M", c_int), ("K", c_int), ("mode", c_int)]
-
-
-def chain_takes(N, M, K, mode):
-    """True when a streaming product of these sizes can wait for a chain (mode 0 plain, 1 swiglu, 3 residual)"""
-    if not CHAIN["on"] or not PDL["on"] or not stream_supports(N, K):
-        return False
-    key = (M, K, mode)
-    if key not in _chain_takes:
-        lib = load_library("gemm_chain")
-        lib.mb_gemm_chain_takes.argtypes = [c_int, c_int, c_int]
-        lib.mb_gemm_chain_takes.restype = c_int
-        _chain_takes[key] = bool(lib.mb_gemm_chain_takes(M, K, mode))
-    return _chain_takes[key]
-
-
-def _chain_add(member, alone, keep):
-    _chain.append((member, alone, keep))
-    if len(_chain) >= CHAIN["most"]:
-        flush_chain()
-
-
-def flush_chain():
-    """Launches the products that wait for a chain: one kernel for two or more, the product's own kernel for one."""
-    if not _chain:
-        return
-    waiting = list(_chain)
-    _chain.clear()
-    if len(waiting) == 1:
-        waiting[0][1]()
-        return
-    device = waiting[0][2][0].device
-    key = str(device)
-    if key not in _chain_sync:
-        _chain_sync[key] = torch.zeros(2, dtype=torch.int32, device=device)
-        _scratch["generation"] += 1
-    members = (_ChainMember * len(waiting))(*[w[0] for w in waiting])
-    f = _fn("gemm_chain", "mb_gemm_chain", [c_void_p, c_int, c_void_p, c_void_p, c_void_p])
-    _check(f(ctypes.cast(members, c_void_p), len(waiting), _p(_chain_sync[key]), _p(error_word(device)), _stream_now()),
-           "gemm_chain")
-
-
-def linear_stream(a, w, out, mode="plain", sums=None, eps=0.0, chain=False):
+def linear_stream(a, w, out, mode="plain", sums=None, eps=0.0):
     """a (N <= 16, K) bf16, w (M, K) bf16 ("swiglu": (2M, K)) -> out (N, M): bf16, or float32 for mode "float".
     sums (ceil(K / 32), 16) float32, if given: a holds rows of a residual stream times a norm's weight and sums the sums
     of squares of those rows by 32 columns, as linear_stream_residual leaves them; out is then the product of
-    rmsnorm(x; weight, eps): 1 / rms scales the float sums of the product.  chain: see CHAIN."""
+    rmsnorm(x; weight, eps): 1 / rms scales the float sums of the product."""
     _cuda(a, w, out, sums)
     N, K = a.shape
     M = out.shape[1]
-    if chain and mode != "float" and chain_takes(N, M, K, 0 if mode == "plain" else 1):
-        _chain_add(_ChainMember(_p(a), _p(sums), float(eps), _p(w), _p(out), None, None, None, None, N, M, K,
-                                0 if mode == "plain" else 1),
-                   lambda: linear_stream(a, w, out, mode, sums, eps), (a, w, out, sums))
-        return out
     ws, cnt = _stream_buffers(a.device, M)
     f = _fn("gemm_stream", "mb_gemm_stream", [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                               c_void_p, c_void_p, c_void_p, c_void_p])
@@ -450,17 +377,13 @@ def linear_stream(a, w, out, mode="plain", sums=None, eps=0.0, chain=False):
     return out
 
 
-def linear_stream_residual(a, w, x, bias=None, sums=None, next_w=None, scaled=None, chain=False):
+def linear_stream_residual(a, w, x, bias=None, sums=None, next_w=None, scaled=None):
     """x (N <= 16, M) float32 += a (N, K) bf16 @ w (M, K)^T (+ bias (M) float32), in place.  What the norm that reads x
     next needs, on request: sums (ceil(M / 32), 16) float32 receives the sums of squares of the new rows by 32 columns,
-    scaled (N, M) bf16 the new rows times that norm's weight next_w (M) float32.  chain: see CHAIN."""
+    scaled (N, M) bf16 the new rows times that norm's weight next_w (M) float32."""
     _cuda(a, w, x, bias, sums, next_w, scaled)
     N, K = a.shape
     M = x.shape[1]
-    if chain and chain_takes(N, M, K, 3):
-        _chain_add(_ChainMember(_p(a), None, 0.0, _p(w), _p(x), _p(bias), _p(sums), _p(next_w), _p(scaled), N, M, K, 3),
-                   lambda: linear_stream_residual(a, w, x, bias, sums, next_w, scaled), (a, w, x, bias, sums, next_w, scaled))
-        return x
     ws, cnt = _stream_buffers(a.device, M)
     f = _fn("gemm_stream", "mb_gemm_stream_residual", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
                                                        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
@@ -492,23 +415,23 @@ def small_qkv_supports(N, K):
     return _use_gemv_fused(N, K)
 
 
-def linear_small_normed(x, norm_w, eps, w, out, mode="plain", held=None, chain=False):
+def linear_small_normed(x, norm_w, eps, w, out, mode="plain", held=None):
     if _use_gemv_fused(*x.shape):
         return linear_gemv_normed(x, norm_w, eps, w, out, mode)
     sums, scaled = held
-    return linear_stream(scaled, w, out, mode, sums, eps, chain=chain)
+    return linear_stream(scaled, w, out, mode, sums, eps)
 
 
 def linear_small_normed_qkv(x, norm_w, eps, w, out, *args):
     return linear_gemv_normed_qkv(x, norm_w, eps, w, out, *args)
 
 
-def linear_small_residual(a, w, x, bias=None, sums=None, next_w=None, scaled=None, chain=False):
+def linear_small_residual(a, w, x, bias=None, sums=None, next_w=None, scaled=None):
     """-> True when sums and scaled were filled (see linear_stream_residual)"""
     if _use_gemv_fused(a.shape[0], x.shape[1]) and a.shape[1] % 8 == 0:
         linear_gemv_residual(a, w, x, bias)
         return False
-    linear_stream_residual(a, w, x, bias, sums, next_w, scaled, chain=chain)
+    linear_stream_residual(a, w, x, bias, sums, next_w, scaled)
     return sums is not None and scaled is not None
 
 

@@ -22,13 +22,12 @@ from ..errors import KernelError
 CSRC = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "csrc")
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 FLAGS = ["-O3", "-lineinfo", "-std=c++17", "-shared", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
-HEADERS = ["common.cuh", "attention_common.cuh", "tcgen05.cuh", "gemm_stream.cuh"]
+HEADERS = ["common.cuh", "attention_common.cuh", "tcgen05.cuh"]
 LIBRARIES = {            # library name -> (source file, extra compiler flags)
     "elementwise": ("elementwise.cu", []),
     "gemm_f32": ("gemm_f32.cu", []),
     "gemm_tc5": ("gemm_tc5.cu", []),
     "gemm_stream": ("gemm_stream.cu", []),
-    "gemm_chain": ("gemm_chain.cu", ["-DC_FEW"]),
     "gemv": ("gemv.cu", []),
     "attention_simple": ("attention_simple.cu", []),
     "attention_mma": ("attention_mma.cu", []),                         # head sizes 16, 32, 64, 128

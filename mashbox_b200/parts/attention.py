@@ -41,8 +41,6 @@ def many_splits(blocks, work, slots, head_dim, most=4):
 
 
 class Attention:
-    chain_safe = True       # reads the residual stream and its own buffers through this package's kernels alone
-
     @property
     def graph_safe(self):
         """forward() depends on the batch only through the lengths of the step's arrays; so must the position encoding"""
@@ -228,16 +226,13 @@ class Attention:
             if normed is not None:
                 x, norm = normed
                 w, eps = norm.fusable()
-                # (the product may wait for a chain: what reads qkv next is a kernel of this package, unless the
-                # position encoding brings code of its own)
-                ops.linear_small_normed(x, w, eps, self.wqkv, qkv, held=ctx.take_held(x, norm), chain=rot is not None)
+                ops.linear_small_normed(x, w, eps, self.wqkv, qkv, held=ctx.take_held(x, norm))
             else:
                 ops.linear(h, self.wqkv, out=qkv)
             freqs, rd, pairing = (None, HD, 0)
             if rot is None:
                 if self.bias:
                     raise ConfigError("a position encoding with its own kernel cannot be combined with q/k/v biases")
-                ops.flush_chain()                       # the encoding's own code may read anything
                 self.position.apply(ctx, qkv, H, KV, HD)
             else:
                 freqs, rd, pairing = rot
@@ -284,7 +279,7 @@ class Attention:
             ops.attention_simple(qkv, width, out, ctx.dev("positions"), ctx.dev("tok_row"), table, kpool, vpool, H, KV,
                                  HD, page, pages, self.window, self.scale, ctx.err)
         if residual is not None:
-            ctx.add_into_stream(out, self.wo, residual, self.bo, chain=True)
+            ctx.add_into_stream(out, self.wo, residual, self.bo)
             return None
         y = ctx.ws.get("delta", N, (self.D,), ctx.dtype)
         ops.linear(out, self.wo, out=y)

@@ -228,9 +228,8 @@ class StepContext:
     after_norm = None
     next_first_norm = None
 
-    def add_into_stream(self, a, w, x, bias=None, chain=False):
-        """x (N, D) float32 += a W^T (+ bias), in place.  chain=True: the product may wait and be launched together with
-        the products after it (ops.CHAIN); only for callers that read x through this package's kernels alone"""
+    def add_into_stream(self, a, w, x, bias=None):
+        """x (N, D) float32 += a W^T (+ bias), in place"""
         import torch
         nxt = self.after_norm if hasattr(self.after_norm, "fusable") else None
         sums = scaled = gw = None
@@ -240,7 +239,7 @@ class StepContext:
             scaled = self.ws.get("row_scaled", x.shape[0], (x.shape[1],), torch.bfloat16)
             gw = nxt.fusable()[0]
         self.memo.pop("held", None)
-        if self.ops.linear_small_residual(a, w, x, bias, sums=sums, next_w=gw, scaled=scaled, chain=chain):
+        if self.ops.linear_small_residual(a, w, x, bias, sums=sums, next_w=gw, scaled=scaled):
             self.memo["held"] = (x.data_ptr(), nxt, sums, scaled)
 
     def held_for(self, x, norm):

@@ -37,10 +37,6 @@ class PreNormBlock:
     @staticmethod
     def _sublayer(ctx, x, pending, norm, part, small, after, *run):
         ctx.after_norm = after                  # the norm that reads x after this part (None: not known)
-        if not (getattr(norm, "chain_safe", False) and getattr(part, "chain_safe", False)):
-            # products of earlier parts may still wait to be launched as a chain (ops.CHAIN); a part that does not say
-            # that it reads the stream through this package's kernels alone finds everything done
-            getattr(ctx.ops, "flush_chain", lambda: None)()
         if not (small and getattr(part, "fuses_small", False) and hasattr(norm, "fusable")):
             return part.forward(ctx, norm.forward(ctx, x, pending), *run)
         ready = pending is None and (not ctx.ops.small_normed_needs_held(ctx.N, x.shape[1]) or ctx.held_for(x, norm) is not None)

@@ -6,7 +6,6 @@ from .base import register
 
 class SwiGLU:
     graph_safe = True       # forward() depends on the batch only through the lengths of the step's arrays
-    chain_safe = True       # reads the residual stream and its own buffers through this package's kernels alone
     def __init__(self, hidden, intermediate, prefix="", names=None):
         self.D, self.F = int(hidden), int(intermediate)
         n = dict(gate="ffn_gate", up="ffn_up", down="ffn_down")
@@ -32,7 +31,7 @@ class SwiGLU:
         if normed is not None:
             x, norm = normed
             w, eps = norm.fusable()
-            ctx.ops.linear_small_normed(x, w, eps, self.wgu, a, "swiglu", held=ctx.take_held(x, norm), chain=True)
+            ctx.ops.linear_small_normed(x, w, eps, self.wgu, a, "swiglu", held=ctx.take_held(x, norm))
         elif ctx.dtype == torch.bfloat16 and ctx.ops.fused_swiglu_supports(N, self.F, self.D):
             ctx.ops.linear_swiglu(h, self.wgu, a)           # both products and the gate in one kernel
         else:
@@ -40,7 +39,7 @@ class SwiGLU:
             ctx.ops.linear(h, self.wgu, out=gu)
             ctx.ops.swiglu(gu, a)
         if residual is not None:
-            ctx.add_into_stream(a, self.wd, residual, chain=True)
+            ctx.add_into_stream(a, self.wd, residual)
             return None
         y = ctx.ws.get("delta", N, (self.D,), ctx.dtype)
         ctx.ops.linear(a, self.wd, out=y)

@@ -10,7 +10,6 @@ from .base import register
 
 class RMSNorm:
     graph_safe = True       # forward() depends on the batch only through the lengths of the step's arrays
-    chain_safe = True       # reads the residual stream through this package's kernels alone (ops.CHAIN)
     def __init__(self, width, eps, name):
         self.width, self.eps, self.name = int(width), float(eps), name
         self.weight = None
