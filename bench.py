@@ -27,6 +27,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+POINT_PAUSE_S = 2.0          # idle time before each of the extra points (decode at batch 1 and 64)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
@@ -218,8 +219,15 @@ def run_ours(a):
     main = decode(a.batch, True)
     points, detail = {}, {}
     for b in batches[1:]:
+        # a pause, so that the power state the measurement before left (the SM clock stays low for a while after a
+        # power-capped run) is not part of this one; the point's own clocks are sampled
+        torch.cuda.synchronize()
+        time.sleep(POINT_PAUSE_S)
+        own = Clocks()
+        own.start()
         r = decode(b, False)
-        points[f"decode_b{b}"], detail[f"decode_b{b}"] = r["value"], roof(r)
+        ck = own.stop()
+        points[f"decode_b{b}"], detail[f"decode_b{b}"] = r["value"], dict(roof(r), sm_mhz=ck["sm_mhz"])
     points[f"decode_b{a.batch}"], detail[f"decode_b{a.batch}"] = main["value"], roof(main)
     clk = clocks.stop()
     nbytes = bytes_decode(cfg, layers, main["batch"], main["kv_len"])
@@ -235,7 +243,8 @@ def run_ours(a):
                    "global_batch": main["batch"], "seq_len": ctx, "mean_kv_len_timed": round(main["kv_len"], 1),
                    "page_size": 16,
                    "prefill_tokens": P, "parallelism": "single-gpu", "l2": "inputs larger than L2 (no flush)",
-                   "cuda_graphs": bool(eng.runner.use_graphs), "peaks": pk["source"], "load_s": round(load_s, 1)},
+                   "cuda_graphs": bool(eng.runner.use_graphs), "peaks": pk["source"], "load_s": round(load_s, 1),
+                   "pause_before_points_s": POINT_PAUSE_S},
         "clocks": clk,
         "e2e": {k: main["e2e"][k] for k in ("value", "unit", "h2d_bytes_per_step", "d2h_bytes_per_step")},
         "gpu_launches": main["launches"],
