@@ -266,6 +266,18 @@ WORKLOADS = {
     # BASELINE.json configs[4]: 4 prompts of 32,768 tokens in 2,048-token portions, then 256 steps at temperature 1.0
     "1b-long": dict(model="llama-3.2-1b-shape", layers=16, hidden=2048, heads=32, kv_heads=8, head_dim=64,
                     intermediate=8192, factor=32.0, requests=4, prompt=(32768, 32768), new=(256, 256), temperature=1.0),
+    # the condition of the reference's published single-user rows: one request, 128 new tokens after a warm request
+    # (bf16 here, 4- to 8-bit files there); the last has the shape of Falcon3-1B, which its GGUF calls `llama`
+    "1b-single": dict(model="llama-3.2-1b-shape", layers=16, hidden=2048, heads=32, kv_heads=8, head_dim=64,
+                      intermediate=8192, factor=32.0, requests=1, prompt=(32, 32), new=(128, 128), temperature=0.0),
+    "3b-single": dict(model="llama-3.2-3b-shape", layers=28, hidden=3072, heads=24, kv_heads=8, head_dim=128,
+                      intermediate=8192, factor=32.0, requests=1, prompt=(32, 32), new=(128, 128), temperature=0.0),
+    "8b-single": dict(model="llama-3.1-8b-shape", layers=32, hidden=4096, heads=32, kv_heads=8, head_dim=128,
+                      intermediate=14336, factor=8.0, requests=1, prompt=(32, 32), new=(128, 128), temperature=0.0,
+                      tied=False),
+    "falcon3-1b-single": dict(model="falcon3-1b-shape", layers=18, hidden=2048, heads=8, kv_heads=4, head_dim=256,
+                              intermediate=8192, factor=32.0, requests=1, prompt=(32, 32), new=(128, 128),
+                              temperature=0.0, vocab=131072),
 }
 
 
@@ -287,9 +299,10 @@ def run_workload(a):
     dev = "cuda:0"
     layers = a.layers or w["layers"]
     cfg = LlamaConfig(architecture="LlamaForCausalLM", num_layers=layers, hidden=w["hidden"], num_heads=w["heads"],
-                      num_kv_heads=w["kv_heads"], head_dim=w["head_dim"], intermediate=w["intermediate"], vocab=128256,
+                      num_kv_heads=w["kv_heads"], head_dim=w["head_dim"], intermediate=w["intermediate"],
+                      vocab=w.get("vocab", 128256),
                       rms_eps=1e-5, rope_theta=500000.0, rope_scaling=RopeScaling("llama3", w["factor"], 1.0, 4.0, 8192),
-                      tie_embeddings=True, attention_bias=False, max_position=131072)
+                      tie_embeddings=w.get("tied", True), attention_bias=False, max_position=131072)
     rng = random.Random(a.seed)
     n_req = a.requests or w["requests"]
     plens = [rng.randint(*w["prompt"]) for _ in range(n_req)]
@@ -654,7 +667,7 @@ def main():
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--queries", type=int, default=2048)
     ap.add_argument("--keys", type=int, default=8192)
-    ap.add_argument("--workload", default="", choices=("", "3b-serving", "1b-long"),
+    ap.add_argument("--workload", default="", choices=("",) + tuple(WORKLOADS),
                     help="run one of the other workloads of the baseline through Engine.admit/step instead")
     ap.add_argument("--requests", type=int, default=0, help="workloads: fewer requests than the workload names")
     ap.add_argument("--pool-tokens", type=int, default=0, help="workloads: size of the cache pool (0: every request fits)")

@@ -260,11 +260,24 @@ def linear_tc5(a, w, out, mode="plain"):
 # 21.2 / 24.9, fused gate/up + SwiGLU 39.0 / 39.2 + 2.3; at two tokens the arithmetic (bf16 to float conversions on
 # the FMA pipe) already costs more than the stream.  GEMV[mode] = the most tokens the engine gives the kernel (0: never);
 # "fused": the forms that normalise the residual stream themselves or add their product into it (see small_fused_supports).
+# A limit of -1 leaves the choice at one token to the width of the product's input: below GEMV_AUTO_WIDTH the
+# matrix-vector kernels, from there on the weight-streaming products (which want a row tile for most SMs and find one
+# in matrices of 4,096 rows and more).  One request, 128 new tokens, through Engine.admit/step (python bench.py
+# --workload 1b-single and the like), matrix-vector / streaming: Llama-3.2-1B shape (width 2,048) 1,187 / 987 tokens/s,
+# Llama-3.2-3B shape (3,072) 539 / 498, Falcon3-1B shape (2,048) 924 / 765; Llama-3.1-8B shape (4,096) 300 / 315.
 GEMV = {"swiglu": 1, "plain": 1, "fused": 1}
+GEMV_AUTO_WIDTH = 4096
+
+
+def _gemv_limit(mode, K):
+    v = GEMV[mode]
+    if v >= 0:
+        return v
+    return 1 if (not PDL["on"] or K < GEMV_AUTO_WIDTH) else 0
 
 
 def gemv_supports(N, K, mode="plain"):
-    return 1 <= N <= min(4, GEMV["swiglu" if mode == "swiglu" else "plain"]) and K >= 8 and K % 8 == 0
+    return 1 <= N <= min(4, _gemv_limit("swiglu" if mode == "swiglu" else "plain", K)) and K >= 8 and K % 8 == 0
 
 
 def linear_gemv_normed(x, norm_w, eps, w, out, mode="plain"):
@@ -328,13 +341,15 @@ STREAM = {"tokens": 16}
 def configure(options):
     """Engine options that choose between this package's kernels, applied process-wide (the kernels' faces are module
     functions).  pdl (default on): programmatic dependent launch along the chain of kernels of a small step; with it
-    the weight-streaming products take steps of one token too (measured on the 8B shape at one token per step: 3.41 ms
-    against 3.68 ms for the matrix-vector kernels, which lose 0.7 ms when they are launched that way themselves).
-    gemv_tokens / stream_tokens: the most tokens of a step the matrix-vector / weight-streaming products take (0: never)."""
+    the weight-streaming products take steps of one token too when the model is at least GEMV_AUTO_WIDTH wide
+    (measured on the 8B shape at one token per step: 3.41 ms against 3.68 ms for the matrix-vector kernels, which lose
+    0.7 ms when they are launched that way themselves; narrower models stay with the matrix-vector kernels).
+    gemv_tokens / stream_tokens: the most tokens of a step the matrix-vector / weight-streaming products take (0: never;
+    gemv_tokens unset: by the width)."""
     pdl = bool(options.get("pdl", True))
     set_pdl(pdl)
     for k in GEMV:
-        GEMV[k] = int(options.get("gemv_tokens", 0 if pdl else 1))
+        GEMV[k] = int(options["gemv_tokens"]) if "gemv_tokens" in options else (-1 if pdl else 1)
     STREAM["tokens"] = int(options.get("stream_tokens", 16))
 
 
@@ -396,7 +411,7 @@ def linear_stream_residual(a, w, x, bias=None, sums=None, next_w=None, scaled=No
 # "held" is what the product that last added into the residual stream left for the norm after it (sums of squares by 32
 # columns, rows times the norm's weight in bf16): the streaming products need it, the matrix-vector kernels read x.
 def _use_gemv_fused(N, K):
-    return 1 <= N <= min(4, GEMV["fused"]) and K % 8 == 0 and 8 <= K < 8192 and N * K * 2 <= 48 * 1024
+    return 1 <= N <= min(4, _gemv_limit("fused", K)) and K % 8 == 0 and 8 <= K < 8192 and N * K * 2 <= 48 * 1024
 
 
 def small_fused_supports(N, K, dtype):

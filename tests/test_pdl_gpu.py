@@ -51,7 +51,7 @@ def test_pdl_changes_no_bit(tmp_path_factory, name):
         want = replay(off, steps)
         want2 = replay(off, steps)                     # the second pass replays captured graphs
         del off
-        folder, on = runner_for(tmp, name, "bf16", 512, options={"pdl": True})
+        folder, on = runner_for(tmp, name, "bf16", 512, options={"pdl": True, "gemv_tokens": 0})
         assert ops.PDL["on"]
         got = replay(on, steps)
         got2 = replay(on, steps)
@@ -84,7 +84,7 @@ def test_pdl_under_random_mixed_traffic(tmp_path_factory):
         _, off = runner_for(tmp, "C", "bf16", 4 * 64, options={"pdl": False, "gemv_tokens": 0})
         want = replay(off, steps)
         del off
-        _, on = runner_for(tmp, "C", "bf16", 4 * 64, options={"pdl": True})
+        _, on = runner_for(tmp, "C", "bf16", 4 * 64, options={"pdl": True, "gemv_tokens": 0})
         got = replay(on, steps)
     finally:
         ops.configure({})
