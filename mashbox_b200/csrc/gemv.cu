@@ -56,7 +56,7 @@ struct GemvRope {
 // attribute this kernel's blocks may be resident before that kernel has finished, and an SM's L1 may hold lines of its
 // output from before it was complete.
 template <bool SHARED> __device__ __forceinline__ uint4 gv_act(const bf16* p) {
-    return SHARED ? *reinterpret_cast<const uint4*>(p) : __ldcg(reinterpret_cast<const uint4*>(p));
+    return *reinterpret_cast<const uint4*>(p);
 }
 
 __device__ __forceinline__ void gv_load8(const float* p, float (&v)[8]) {                 // a norm's weight
@@ -70,7 +70,7 @@ __device__ __forceinline__ void gv_load8_stream(const float* p, float (&v)[8]) {
 
 // NT tokens (1..4).  MODE 0: bf16 out (N, M); 1: SwiGLU, W has 2 * M rows, bf16 out (N, M); 2: float out; 3: out is
 // the float32 residual stream (N, M), added to.
-template <int NT, int MODE, bool NORM>
+template <int NT, int MODE, int PRE>
 __global__ void __launch_bounds__(GV_WARPS * 32) gemv_kernel(const bf16* __restrict__ act, const bf16* __restrict__ W,
                                                              void* __restrict__ out, int M, int K, GemvNorm nrm,
                                                              const float* __restrict__ bias, GemvRope rope) {
@@ -79,6 +79,16 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_kernel(const bf16* __restr
     // These kernels are launched plainly.  With the programmatic-serialization attribute (wait at the top, dependents
     // let go at the start or at the end of a block's work) a one-token step of the 8B shape took 4.3 ms against 3.7
     // ms: the streaming products, which gain from it, take such steps instead when it is on.
+    constexpr bool NORM = PRE == 1;
+    if (PRE == 2) {
+        // the activations once per block into shared memory (16 bytes a thread and turn), instead of once per warp from
+        // the L2
+        bf16* hs = reinterpret_cast<bf16*>(gv_smem);
+        for (int c = threadIdx.x; c < NT * (K / 8); c += GV_WARPS * 32)
+            *reinterpret_cast<uint4*>(hs + (size_t)c * 8) = *reinterpret_cast<const uint4*>(act + (size_t)c * 8);
+        __syncthreads();
+        act = hs;
+    }
     if (NORM) {
         __shared__ float scratch[32];
         bf16* hs = reinterpret_cast<bf16*>(gv_smem);                 // [NT][K]
@@ -140,6 +150,17 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_kernel(const bf16* __restr
     for (int r = 0; r < GV_ROWS; r++)
 #pragma unroll
         for (int n = 0; n < NT; n++) acc[r][n] = 0.0f;
+    // MODE 3: the stream's old values are sent for before the rows of W.  Asked for at the end, behind everything the
+    // other warps have in flight, they took 6 us to arrive (a 2,048 x 2,048 product: 11.6 us against 5.8 for the plain
+    // form).
+    float old[GV_ROWS][NT];
+    if (MODE == 3 && lane == 0) {
+#pragma unroll
+        for (int r = 0; r < GV_ROWS; r++)
+#pragma unroll
+            for (int n = 0; n < NT; n++)
+                old[r][n] = m0 + r < M ? __ldcg(reinterpret_cast<const float*>(out) + (size_t)n * M + m0 + r) : 0.0f;
+    }
     const int chunks = K / 8;
     int c = lane;
     // eight chunks of both rows ahead (16 loads of 16 bytes in flight per lane): with four, a matrix of long rows
@@ -154,7 +175,7 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_kernel(const bf16* __restr
         for (int u = 0; u < 8; u++)
 #pragma unroll
             for (int n = 0; n < NT; n++) {
-                const uint4 x = gv_act<NORM>(act + (size_t)n * K + (size_t)(c + 32 * u) * 8);
+                const uint4 x = gv_act<PRE != 0>(act + (size_t)n * K + (size_t)(c + 32 * u) * 8);
 #pragma unroll
                 for (int r = 0; r < GV_ROWS; r++) acc[r][n] = dot8(w[u][r], x, acc[r][n]);
             }
@@ -169,7 +190,7 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_kernel(const bf16* __restr
         for (int u = 0; u < 4; u++)
 #pragma unroll
             for (int n = 0; n < NT; n++) {
-                const uint4 x = gv_act<NORM>(act + (size_t)n * K + (size_t)(c + 32 * u) * 8);
+                const uint4 x = gv_act<PRE != 0>(act + (size_t)n * K + (size_t)(c + 32 * u) * 8);
 #pragma unroll
                 for (int r = 0; r < GV_ROWS; r++) acc[r][n] = dot8(w[u][r], x, acc[r][n]);
             }
@@ -180,7 +201,7 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_kernel(const bf16* __restr
         for (int r = 0; r < GV_ROWS; r++) w[r] = ld_stream16(rows[r] + (size_t)c * 8);
 #pragma unroll
         for (int n = 0; n < NT; n++) {
-            const uint4 x = gv_act<NORM>(act + (size_t)n * K + (size_t)c * 8);
+            const uint4 x = gv_act<PRE != 0>(act + (size_t)n * K + (size_t)c * 8);
 #pragma unroll
             for (int r = 0; r < GV_ROWS; r++) acc[r][n] = dot8(w[r], x, acc[r][n]);
         }
@@ -228,7 +249,7 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_kernel(const bf16* __restr
                 if (m0 + r >= M) continue;
                 if (MODE == 3) {
                     float* xo = reinterpret_cast<float*>(out) + (size_t)n * M + m0 + r;
-                    *xo = __ldcg(xo) + (acc[r][n] + (bias ? bias[m0 + r] : 0.0f));
+                    *xo = old[r][n] + (acc[r][n] + (bias ? bias[m0 + r] : 0.0f));
                 }
                 else if (MODE == 2) reinterpret_cast<float*>(out)[(size_t)n * M + m0 + r] = acc[r][n];
                 else reinterpret_cast<bf16*>(out)[(size_t)n * M + m0 + r] = __float2bfloat16_rn(acc[r][n]);
@@ -258,6 +279,10 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_long_kernel(const bf16* __
     for (int r = 0; r < GV_ROWS; r++)
 #pragma unroll
         for (int n = 0; n < NT; n++) acc[r][n] = 0.0f;
+    // MODE 3: the stream's old value of the thread that will write it, sent for before the rows of W (see gemv_kernel)
+    float old = 0.0f;
+    if (MODE == 3 && threadIdx.x < GV_ROWS * NT && m0 + threadIdx.x / NT < M)
+        old = __ldcg(reinterpret_cast<const float*>(out) + (size_t)(threadIdx.x % NT) * M + m0 + threadIdx.x / NT);
     const int chunks = K / 8;
     constexpr int STEP = GV_WARPS * 32;
     int c = warp * 32 + lane;
@@ -271,7 +296,7 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_long_kernel(const bf16* __
         for (int u = 0; u < 4; u++)
 #pragma unroll
             for (int n = 0; n < NT; n++) {
-                const uint4 x = __ldcg(reinterpret_cast<const uint4*>(act + (size_t)n * K + (size_t)(c + STEP * u) * 8));
+                const uint4 x = *(reinterpret_cast<const uint4*>(act + (size_t)n * K + (size_t)(c + STEP * u) * 8));
 #pragma unroll
                 for (int r = 0; r < GV_ROWS; r++) acc[r][n] = dot8(w[u][r], x, acc[r][n]);
             }
@@ -282,7 +307,7 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_long_kernel(const bf16* __
         for (int r = 0; r < GV_ROWS; r++) w[r] = ld_stream16(rows[r] + (size_t)c * 8);
 #pragma unroll
         for (int n = 0; n < NT; n++) {
-            const uint4 x = __ldcg(reinterpret_cast<const uint4*>(act + (size_t)n * K + (size_t)c * 8));
+            const uint4 x = *(reinterpret_cast<const uint4*>(act + (size_t)n * K + (size_t)c * 8));
 #pragma unroll
             for (int r = 0; r < GV_ROWS; r++) acc[r][n] = dot8(w[r], x, acc[r][n]);
         }
@@ -310,7 +335,7 @@ __global__ void __launch_bounds__(GV_WARPS * 32) gemv_long_kernel(const bf16* __
     } else if (m0 + r < M) {
         if (MODE == 3) {
             float* xo = reinterpret_cast<float*>(out) + (size_t)n * M + m0 + r;
-            *xo = __ldcg(xo) + (s + (bias ? bias[m0 + r] : 0.0f));
+            *xo = old + (s + (bias ? bias[m0 + r] : 0.0f));
         }
         else if (MODE == 2) reinterpret_cast<float*>(out)[(size_t)n * M + m0 + r] = s;
         else reinterpret_cast<bf16*>(out)[(size_t)n * M + m0 + r] = __float2bfloat16_rn(s);
@@ -343,9 +368,12 @@ static int gemv_launch(const void* act, const void* W, void* out, int N, int M, 
     }
     unsigned grid = (unsigned)((units + GV_WARPS - 1) / GV_WARPS);
     size_t smem = 0;
-    if (NORM) {
-        // every block normalises the row once: a few blocks per SM that walk the rows, not one block per 16 rows
-        if ((reinterpret_cast<uintptr_t>(nrm.x) & 15) || (reinterpret_cast<uintptr_t>(nrm.w) & 15)) return -2;
+    // without a norm: the activations are copied into shared memory once per block when they fit, else read from global
+    const bool copy = !NORM && (size_t)N * K * sizeof(bf16) <= 48 * 1024;
+    if (NORM || copy) {
+        // every block makes (or copies) the rows once: a few blocks per SM that walk the rows of W, not one block per
+        // 16 rows
+        if (NORM && ((reinterpret_cast<uintptr_t>(nrm.x) & 15) || (reinterpret_cast<uintptr_t>(nrm.w) & 15))) return -2;
         smem = (size_t)N * K * sizeof(bf16);
         if (smem > 48 * 1024) return -2;
         static int sms = 0;
@@ -358,12 +386,16 @@ static int gemv_launch(const void* act, const void* W, void* out, int N, int M, 
         if (grid > (unsigned)(4 * sms)) grid = (unsigned)(4 * sms);
     }
     cudaError_t le = cudaSuccess;
+#define GV_GO(NT_, PRE_) le = mb_launch(false, gemv_kernel<NT_, MODE, PRE_>, dim3(grid), dim3(GV_WARPS * 32), smem, st, a, w, out, M, K, nrm, bias, rope)
+#define GV_PRE(NT_) do { if (NORM) GV_GO(NT_, 1); else if (copy) GV_GO(NT_, 2); else GV_GO(NT_, 0); } while (0)
     switch (N) {
-        case 1: le = mb_launch(false, gemv_kernel<1, MODE, NORM>, dim3(grid), dim3(GV_WARPS * 32), smem, st, a, w, out, M, K, nrm, bias, rope); break;
-        case 2: le = mb_launch(false, gemv_kernel<2, MODE, NORM>, dim3(grid), dim3(GV_WARPS * 32), smem, st, a, w, out, M, K, nrm, bias, rope); break;
-        case 3: le = mb_launch(false, gemv_kernel<3, MODE, NORM>, dim3(grid), dim3(GV_WARPS * 32), smem, st, a, w, out, M, K, nrm, bias, rope); break;
-        default: le = mb_launch(false, gemv_kernel<4, MODE, NORM>, dim3(grid), dim3(GV_WARPS * 32), smem, st, a, w, out, M, K, nrm, bias, rope); break;
+        case 1: GV_PRE(1); break;
+        case 2: GV_PRE(2); break;
+        case 3: GV_PRE(3); break;
+        default: GV_PRE(4); break;
     }
+#undef GV_PRE
+#undef GV_GO
     return le == cudaSuccess ? 0 : (int)le;
 }
 

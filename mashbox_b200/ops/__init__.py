@@ -261,12 +261,13 @@ def linear_tc5(a, w, out, mode="plain"):
 # the FMA pipe) already costs more than the stream.  GEMV[mode] = the most tokens the engine gives the kernel (0: never);
 # "fused": the forms that normalise the residual stream themselves or add their product into it (see small_fused_supports).
 # A limit of -1 leaves the choice at one token to the width of the product's input: below GEMV_AUTO_WIDTH the
-# matrix-vector kernels, from there on the weight-streaming products (which want a row tile for most SMs and find one
-# in matrices of 4,096 rows and more).  One request, 128 new tokens, through Engine.admit/step (python bench.py
-# --workload 1b-single and the like), matrix-vector / streaming: Llama-3.2-1B shape (width 2,048) 1,187 / 987 tokens/s,
-# Llama-3.2-3B shape (3,072) 539 / 498, Falcon3-1B shape (2,048) 924 / 765; Llama-3.1-8B shape (4,096) 300 / 315.
+# matrix-vector kernels, from there on the weight-streaming products.  One request, 128 new tokens after 32 of prompt,
+# through Engine.admit/step (python bench.py --workload 1b-single and the like), matrix-vector / streaming: Llama-3.2-1B
+# shape (width 2,048) 1,378 / 987 tokens/s, Llama-3.2-3B shape (3,072) 605 / 498, Falcon3-1B shape (2,048) 1,047 / 765,
+# Llama-3.1-8B shape (4,096) 328 / 315 (the same at 8,192 tokens of context: 3.35 ms a step either way).  The
+# advantage shrinks with the width (+40 %, +21 %, +4 %), so the line is drawn between 4,096 and 5,120.
 GEMV = {"swiglu": 1, "plain": 1, "fused": 1}
-GEMV_AUTO_WIDTH = 4096
+GEMV_AUTO_WIDTH = 4608
 
 
 def _gemv_limit(mode, K):
@@ -342,8 +343,8 @@ def configure(options):
     """Engine options that choose between this package's kernels, applied process-wide (the kernels' faces are module
     functions).  pdl (default on): programmatic dependent launch along the chain of kernels of a small step; with it
     the weight-streaming products take steps of one token too when the model is at least GEMV_AUTO_WIDTH wide
-    (measured on the 8B shape at one token per step: 3.41 ms against 3.68 ms for the matrix-vector kernels, which lose
-    0.7 ms when they are launched that way themselves; narrower models stay with the matrix-vector kernels).
+    (narrower models stay with the matrix-vector kernels, which are launched plainly: launched that way themselves
+    they lost 0.7 ms a step on the 8B shape).
     gemv_tokens / stream_tokens: the most tokens of a step the matrix-vector / weight-streaming products take (0: never;
     gemv_tokens unset: by the width)."""
     pdl = bool(options.get("pdl", True))
