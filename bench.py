@@ -613,7 +613,15 @@ def run_kernels(a):
                   "stream_of_normalised_us": chained(lambda i: ops.linear_stream(x, ws[i], y, "plain", sums_in, 1e-5), n_w),
                   "stream_residual_us": chained(lambda i: ops.linear_stream_residual(x, ws[i], hs, None, sums_out, nw_out, scaled_out), n_w)})
         if B <= 4:
+            # the matrix-vector kernels in the forms the engine runs at one token: with the residual add; of the
+            # normalised stream (the norm inside the kernel), for gate/up with SwiGLU
             r["gemv_us"] = chained(lambda i: ops.linear_gemv(x, ws[i], y, "plain"), n_w)
+            r["gemv_residual_us"] = chained(lambda i: ops.linear_gemv_residual(x, ws[i], hs), n_w)
+            if K < 8192 and name != "gate_up":
+                r["gemv_of_normalised_us"] = chained(lambda i: ops.linear_gemv_normed(h, nw, 1e-5, ws[i], y), n_w)
+            if name == "gate_up":
+                act1 = torch.empty(B, F, device=dev, dtype=torch.bfloat16)
+                r["gemv_of_normalised_swiglu_us"] = chained(lambda i: ops.linear_gemv_normed(h, nw, 1e-5, ws[i], act1, "swiglu"), n_w)
         if name == "gate_up":
             act, hh = torch.empty(B, F, device=dev, dtype=torch.bfloat16), torch.empty(B, K, device=dev, dtype=torch.bfloat16)
             r["stream_of_normalised_swiglu_us"] = chained(lambda i: ops.linear_stream(x, ws[i], act, "swiglu", sums_in, 1e-5), n_w)
