@@ -260,21 +260,28 @@ def linear_tc5(a, w, out, mode="plain"):
 # 21.2 / 24.9, fused gate/up + SwiGLU 39.0 / 39.2 + 2.3; at two tokens the arithmetic (bf16 to float conversions on
 # the FMA pipe) already costs more than the stream.  GEMV[mode] = the most tokens the engine gives the kernel (0: never);
 # "fused": the forms that normalise the residual stream themselves or add their product into it (see small_fused_supports).
-# A limit of -1 leaves the choice at one token to the width of the product's input: below GEMV_AUTO_WIDTH the
-# matrix-vector kernels, from there on the weight-streaming products.  One request, 128 new tokens after 32 of prompt,
+# A limit of -1 leaves the choice to the width of the product's input (GEMV_AUTO: the matrix-vector kernels up to that
+# many tokens below that width, else the weight-streaming products).  One request, 128 new tokens after 32 of prompt,
 # through Engine.admit/step (python bench.py --workload 1b-single and the like), matrix-vector / streaming: Llama-3.2-1B
 # shape (width 2,048) 1,378 / 987 tokens/s, Llama-3.2-3B shape (3,072) 605 / 498, Falcon3-1B shape (2,048) 1,047 / 765,
-# Llama-3.1-8B shape (4,096) 328 / 315 (the same at 8,192 tokens of context: 3.35 ms a step either way).  The
-# advantage shrinks with the width (+40 %, +21 %, +4 %), so the line is drawn between 4,096 and 5,120.
+# Llama-3.1-8B shape (4,096) 328 / 315 (the same at 8,192 tokens of context: 3.35 ms a step either way): the advantage
+# shrinks with the width (+40 %, +21 %, +4 %), so the line for one token is drawn between 4,096 and 5,120.  At two
+# tokens (2,048 of context) the 1B shape takes 0.88 / 0.99 ms a step, the 3B shape 1.99 / 2.24, the 8B shape 3.84 /
+# 3.55; at three they are level, at four the streaming products win everywhere.
 GEMV = {"swiglu": 1, "plain": 1, "fused": 1}
-GEMV_AUTO_WIDTH = 4608
+GEMV_AUTO = ((3584, 2), (4608, 1))            # (narrower than, tokens), the first line that applies
 
 
 def _gemv_limit(mode, K):
     v = GEMV[mode]
     if v >= 0:
         return v
-    return 1 if (not PDL["on"] or K < GEMV_AUTO_WIDTH) else 0
+    if not PDL["on"]:
+        return 1
+    for width, tokens in GEMV_AUTO:
+        if K < width:
+            return tokens
+    return 0
 
 
 def gemv_supports(N, K, mode="plain"):
@@ -342,7 +349,7 @@ STREAM = {"tokens": 16}
 def configure(options):
     """Engine options that choose between this package's kernels, applied process-wide (the kernels' faces are module
     functions).  pdl (default on): programmatic dependent launch along the chain of kernels of a small step; with it
-    the weight-streaming products take steps of one token too when the model is at least GEMV_AUTO_WIDTH wide
+    the weight-streaming products take steps of one token too when the model is wide enough (GEMV_AUTO)
     (narrower models stay with the matrix-vector kernels, which are launched plainly: launched that way themselves
     they lost 0.7 ms a step on the 8B shape).
     gemv_tokens / stream_tokens: the most tokens of a step the matrix-vector / weight-streaming products take (0: never;
