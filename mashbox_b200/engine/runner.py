@@ -12,6 +12,7 @@ captured when it comes a second time -- decode batches, and the equal portions a
 least recently captured graph goes when there are MAX_GRAPHS of them.  Models with a part that does not declare itself
 graph_safe run without graphs.
 """
+import gc
 import time
 
 import numpy as np
@@ -203,17 +204,26 @@ class ModelRunner:
         self.capture_stream.wait_stream(main)
         graph = torch.cuda.CUDAGraph()
         before = kernels.COUNTERS["launches"]
-        with torch.cuda.stream(self.capture_stream):
-            graph.capture_begin(capture_error_mode="thread_local")
-            try:
-                logits = self.model.forward(ctx)
-            except BaseException:
+        # No garbage collection while the stream captures: a graph of an engine that is garbage by now (they sit in
+        # reference cycles) would be destroyed in the middle of the capture, which CUDA does not permit and answers by
+        # invalidating the capture.
+        collecting = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.stream(self.capture_stream):
+                graph.capture_begin(capture_error_mode="thread_local")
                 try:
-                    graph.capture_end()
-                except Exception:
-                    pass
-                raise
-            graph.capture_end()
+                    logits = self.model.forward(ctx)
+                except BaseException:
+                    try:
+                        graph.capture_end()
+                    except Exception:
+                        pass
+                    raise
+                graph.capture_end()
+        finally:
+            if collecting:
+                gc.enable()
         captured = kernels.COUNTERS["launches"] - before
         main.wait_stream(self.capture_stream)
         graph.replay()

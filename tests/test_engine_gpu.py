@@ -173,11 +173,14 @@ def test_a_step_that_needs_ids_still_in_flight_waits_for_them(tmp_path_factory):
     assert eng.cache.free_pages() == [eng.cache.num_pages]
 
 
-@pytest.mark.parametrize("seed", [1, 4])
-def test_random_traffic_equals_each_request_alone(tmp_path_factory, seed):
+@pytest.mark.parametrize("seed,slots,pool,budget,count,burst", [(1, 3, 192, 48, 36, 4), (4, 3, 192, 48, 36, 4),
+                                                                 (9, 26, 1600, 96, 70, 30)])
+def test_random_traffic_equals_each_request_alone(tmp_path_factory, seed, slots, pool, budget, count, burst):
     """36 requests of random lengths, samplers, stop tokens and arrival times through an engine with three slots, 192
     tokens of cache and 48 tokens a step (portions, preemptions, a few cancellations, two steps in flight all along):
-    in float32 every answer is the one the request gets alone in a roomy engine, cut at its stop token."""
+    in float32 every answer is the one the request gets alone in a roomy engine, cut at its stop token.  The third case
+    has 26 slots and 70 requests arriving in bursts of up to 30: decode batches of more than 16, which are filled up to
+    the grid of sizes and replayed from graphs."""
     import random
     rng = random.Random(seed)
     folder, roomy = engine(tmp_path_factory.mktemp("m"), "A", "f32", max_tokens=512, max_requests=2)
@@ -195,19 +198,27 @@ def test_random_traffic_equals_each_request_alone(tmp_path_factory, seed):
         return d
 
     reqs = [dict(ids=[rng.randrange(vocab) for _ in range(rng.randint(1, 70))], max_new=rng.randint(1, 36), samp=samp())
-            for _ in range(36)]
+            for _ in range(count)]
     alone = [roomy.generate([q["ids"]], max_new=q["max_new"], samp=[q["samp"]])["ids"][0] for q in reqs]
     for q, a in zip(reqs, alone):
         if rng.random() < 0.35 and a:
             q["stop_ids"] = (a[rng.randrange(len(a))],)
     want = [a[:a.index(q["stop_ids"][0])] if q.get("stop_ids") else a for q, a in zip(reqs, alone)]
     from mashbox_b200.engine.engine import Engine
-    tight = Engine.from_folder(folder, dtype="float32", page_size=H.TINY["A"][2], max_tokens=192, max_requests=3,
-                               max_tokens_per_step=48, chunk=32)
+    tight = Engine.from_folder(folder, dtype="float32", page_size=H.TINY["A"][2], max_tokens=pool, max_requests=slots,
+                               max_tokens_per_step=budget, chunk=32)
+    seen_batches = []
+    inner_prepare = tight.runner.prepare
+
+    def watching_prepare(entries, *a, **k):
+        ctx = inner_prepare(entries, *a, **k)
+        seen_batches.append((len(entries), ctx.S))
+        return ctx
+    tight.runner.prepare = watching_prepare
     rows, pending, cancelled, steps = {}, list(range(len(reqs))), set(), 0
     while pending or tight.busy():
         if pending and (rng.random() < 0.3 or not tight.busy()):
-            n = rng.randint(1, 4)
+            n = rng.randint(1, burst)
             take, pending = pending[:n], pending[n:]
             for i, r in zip(take, tight.admit([reqs[i] for i in take])):
                 rows[i] = r
@@ -229,6 +240,9 @@ def test_random_traffic_equals_each_request_alone(tmp_path_factory, seed):
             assert r.finish == ("stop" if reqs[i].get("stop_ids") else "length")
     tight.cache.check()
     assert tight.cache.free_pages() == [tight.cache.num_pages]
+    if slots > 16:
+        assert any(real > 16 and filled > real for real, filled in seen_batches), "no decode batch was filled up"
+        assert tight.runner.stats["graph_replays"] > 0
 
 
 def test_cancel_through_on_step(tmp_path_factory):
