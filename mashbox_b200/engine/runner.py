@@ -164,11 +164,12 @@ class ModelRunner:
         return ctx
 
     def filled_size(self, S):
-        """the size a decode batch of S sequences is filled up to: itself up to 16 (those steps run other kernels than
-        larger ones), then steps of 4 up to 32, of 8 up to 128, of 16 beyond; never more than the logits buffer holds"""
-        if S <= 16 or not self.options.get("fill_decode_batches", True):
+        """the size a decode batch of S sequences is filled up to: itself up to 4, then steps of 2 up to 8, of 4 up to
+        32 (16 stays a size: up to there a step runs the weight-streaming products, whose time does not depend on the
+        number of tokens), of 8 up to 128, of 16 beyond; never more than the logits buffer holds"""
+        if S <= 4 or not self.options.get("fill_decode_batches", True):
             return S
-        step = 4 if S <= 32 else 8 if S <= 128 else 16
+        step = 2 if S <= 8 else 4 if S <= 32 else 8 if S <= 128 else 16
         return max(S, min(-(-S // step) * step, int(self.options["logit_rows"])))
 
     def patch_token(self, index, token):
