@@ -48,7 +48,7 @@ class ModelRunner:
         self.use_graphs = (bool(engine_config.cuda_graphs) and not self.options.get("no_graphs", False)
                            and getattr(model, "graph_safe", False))
         self.stats = dict(steps=0, tokens=0, graph_replays=0, graph_captures=0, capture_s=0.0)
-        self.capture_stream = None
+        self.capture_stream = self.graph_pool = None
 
     # -------------------------------------------------------------------------------------------- the step
     def step(self, entries):
@@ -202,6 +202,11 @@ class ModelRunner:
         main = torch.cuda.current_stream(self.device)
         if self.capture_stream is None:
             self.capture_stream = torch.cuda.Stream(self.device)
+            # One memory pool for every graph of this runner: what a library allocates while a step is captured (the
+            # workspace of its matrix products) is reserved once, not once per graph.  The graphs are replayed one after
+            # the other on one stream and leave nothing in the pool that anyone reads later (a step's buffers are the
+            # workspace's, made outside captures), so they can share it.
+            self.graph_pool = torch.cuda.graph_pool_handle()
         self.capture_stream.wait_stream(main)
         graph = torch.cuda.CUDAGraph()
         before = kernels.COUNTERS["launches"]
@@ -212,7 +217,7 @@ class ModelRunner:
         gc.disable()
         try:
             with torch.cuda.stream(self.capture_stream):
-                graph.capture_begin(capture_error_mode="thread_local")
+                graph.capture_begin(pool=self.graph_pool, capture_error_mode="thread_local")
                 try:
                     logits = self.model.forward(ctx)
                 except BaseException:
