@@ -25,17 +25,23 @@ DECODE_ROWS, PREFILL_ROWS, KEY_TILE = 16, 64, 64
 def many_splits(blocks, work, slots, head_dim, most=4):
     """Into how many splits (1 to `most`) to cut each of `blocks` decode-form tiles of the TMA attention kernel, `work`
     key tiles in all, when there are more of them than half the `slots` the device has for such blocks.  The model: the
-    blocks run in rounds of `slots`; a round of n blocks of w key tiles takes w * max(n, enough) / bandwidth, `enough`
-    being the number of blocks whose tiles in flight (three or four stages of 64 keys) keep the memory busy, about 19
-    MB in all; every further split costs 2 % (its partial results meet through global memory).  The fewest splits
-    within 1 % of the best."""
-    enough = max(1, int(19.2e6 // ((3 if head_dim > 64 else 4) * 2 * 64 * head_dim * 2)))
+    blocks run in rounds of `slots`; a round of n blocks of w key tiles takes the longer of what the memory needs for
+    them (n w tiles at 6.5 TB/s, but never less than `enough` blocks' worth: that many blocks, with three or four
+    stages of 64 keys in flight each, about 19 MB, keep the memory busy) and what one block needs for itself (7 us to
+    start, meet and finish, half a microsecond a tile); splits cost 4 us and 0.15 us each on top (their partial
+    results meet through global memory).  The fewest splits within 1 % of the best."""
+    tile_bytes = 2 * 64 * head_dim * 2
+    enough = max(1, int(19.2e6 // ((3 if head_dim > 64 else 4) * tile_bytes)))
+    tile_us = tile_bytes / 6.5e6                                 # a tile's share of the memory's time
     costs = []
     for ns in range(1, max(1, most) + 1):
-        n = blocks * ns
+        n, w = blocks * ns, work / (blocks * ns)
         full, rest = divmod(n, slots)
-        rounds = full * slots + (max(rest, enough) if rest else 0)
-        costs.append((work / n) * rounds * (1.0 + 0.02 * (ns - 1)))
+        alone = 7.0 + 0.5 * w                                     # a block by itself
+        t = full * max(slots * w * tile_us, alone)
+        if rest:
+            t += max(max(rest, enough) * w * tile_us, alone)
+        costs.append(t + (4.0 + 0.15 * ns if ns > 1 else 0.0))
     best = min(costs)
     return 1 + next(i for i, c in enumerate(costs) if c <= 1.01 * best)
 

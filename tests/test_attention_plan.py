@@ -108,7 +108,10 @@ def test_many_splits_model():
     # a thin second round (320 blocks on 296 places) is the worst case: cut further
     assert many_splits(320, 320 * 128, 296, 128) == 4
     assert many_splits(160, 160 * 128, 296, 128) == 3
-    assert many_splits(384, 384 * 128, 296, 128) == 2
+    assert many_splits(384, 384 * 128, 296, 128) in (2, 3)          # measured within 1.3 % of each other
+    # short sequences: a block's own start and finish, and the meeting of the splits, outweigh a thin round
+    assert many_splits(160, 160 * 32, 296, 128) == 1
+    assert many_splits(192, 192 * 16, 296, 128) == 1
     # never more than asked for, never fewer than one
     for blocks in range(1, 1200, 7):
         for most in (1, 2, 4):
