@@ -446,6 +446,13 @@ static int stream_launch_th(const void* act, const void* W, void* out, int N, in
     const int tiles = (M + TH - 1) / TH, sms = stream_sms();
     const long long T = (long long)tiles * ((K + SH::KS - 1) / SH::KS);
     long long grid = tiles <= sms && tiles >= (sms * 3 + 4) / 5 ? tiles : sms;    // a block per tile, or equal shares
+    if (tiles < (sms * 3 + 4) / 5 && sms / tiles >= 2) {
+        // few tiles: the same whole number of blocks for every tile (as many as fit), so that the shares are even and
+        // a tile's sharers finish together (a 2,048 x 2,048 matrix, 64 tiles: as 128 blocks of two items 5.5 us, as
+        // 148 blocks of one or two 7.7; with the residual add 6.5 against 9.5)
+        const long long kblocks = T / tiles, per = sms / tiles;
+        grid = tiles * (per < kblocks ? per : kblocks);
+    }
     if (grid > T) grid = T;
     const cudaError_t e = mb_launch(mb_pdl != 0, gemm_stream_kernel<EPI, SCALED, TH>, dim3((unsigned)grid), dim3(S_THREADS),
                                     SH::BYTES, st, wmap, xmap, out, N, M, K, tiles, workspace, counters, nrm, bias, after, err);
