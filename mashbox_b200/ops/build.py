@@ -154,7 +154,8 @@ def prune():
     d = build_dir()
     current = {os.path.basename(library_path(n)) for n in LIBRARIES}
     for f in os.listdir(d):
-        if f.startswith("libmashbox_b200_") and f.endswith(".so") and f not in current:
+        stale_lock = f.endswith(".so.lock") and f[:-5] not in current
+        if f.startswith("libmashbox_b200_") and ((f.endswith(".so") and f not in current) or stale_lock):
             try:
                 os.remove(os.path.join(d, f))
             except OSError:
