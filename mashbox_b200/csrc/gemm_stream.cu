@@ -426,11 +426,41 @@ static int stream_tile_height(int M, int sms, int least) {
     return least;
 }
 
+// How a product is cut: the height of a row tile and the number of blocks.  Of the heights that give no more tiles
+// than SMs and of the numbers of blocks per tile (1 to as many as fit, at most one per k block; the same for every
+// tile, so that a tile's sharers finish together), the pair that this estimate puts first: 4 us, the matrix's bytes
+// at the rate the blocks take them in (60 GB/s a block, 6 TB/s in all), and 1.5 us + 0.5 us per sharer when blocks
+// share a tile (their partial sums meet through global memory, behind whatever else is in flight).  Measured alone
+// (8 tokens, launch to launch in a graph), us: 2,048 x 2,048 as 64 blocks 4.2, as 128 blocks that share 5.5, dealt
+// unevenly over all SMs as before 7.7; 2,048 x 8,192: 12.8 / 10.5 / 11.3; 5,120 x 3,072 as 80 tiles of 64 rows 8.9,
+// unevenly 10.6; 6,144 x 4,096 as 96 tiles of 64 rows 11.3, as 48 tiles of 128 rows shared by three 11.6 -- and inside
+// a model the shared form cost 7 us more than that.  With more tiles than SMs at every height (the output head)
+// stream_tile_height() decides and all SMs take equal shares.
+struct StreamPlan { int th; long long grid; };
+static StreamPlan stream_plan(int M, int K, int sets, int sms, int least) {
+    StreamPlan best{0, 0};
+    double best_t = 0.0;
+    const double bytes = (double)sets * M * K * 2.0;
+    for (int th = least; th <= 128; th *= 2) {                       // at equal cost the lower tile: fewer sharers
+        const long long tiles = (M + th - 1) / th;
+        if (tiles > sms) continue;
+        const long long ks = 16384 / th, kblocks = (K + ks - 1) / ks;
+        for (long long per = 1; per <= kblocks && tiles * per <= sms; per++) {
+            const double blocks = (double)(tiles * per);
+            const double stream = bytes / 6e6 > bytes / (blocks * 60e3) ? bytes / 6e6 : bytes / (blocks * 60e3);
+            const double t = 4.0 + stream + (per > 1 ? 1.5 + 0.5 * (double)per : 0.0);
+            if (best.th == 0 || t < best_t - 1e-9) { best = StreamPlan{th, tiles * per}; best_t = t; }
+        }
+    }
+    if (best.th == 0) best = StreamPlan{stream_tile_height(M, sms, least), sms};
+    return best;
+}
+
 MB_PDL_SWITCH(mb_gemm_stream_set_pdl)
 
 template <int EPI, bool SCALED, int TH>
 static int stream_launch_th(const void* act, const void* W, void* out, int N, int M, int K, float* workspace, int* counters,
-                            StreamNorm nrm, const float* bias, StreamAfter after, int* err, cudaStream_t st) {
+                            StreamNorm nrm, const float* bias, StreamAfter after, int* err, cudaStream_t st, long long grid) {
     using SH = StreamShape<EPI, TH>;
     static_assert(SH::STAGES >= 2, "a ring of at least two stages");
     CUtensorMap wmap, xmap;
@@ -443,16 +473,8 @@ static int stream_launch_th(const void* act, const void* W, void* out, int N, in
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    const int tiles = (M + TH - 1) / TH, sms = stream_sms();
+    const int tiles = (M + TH - 1) / TH;
     const long long T = (long long)tiles * ((K + SH::KS - 1) / SH::KS);
-    long long grid = tiles <= sms && tiles >= (sms * 3 + 4) / 5 ? tiles : sms;    // a block per tile, or equal shares
-    if (tiles < (sms * 3 + 4) / 5 && sms / tiles >= 2) {
-        // few tiles: the same whole number of blocks for every tile (as many as fit), so that the shares are even and
-        // a tile's sharers finish together (a 2,048 x 2,048 matrix, 64 tiles: as 128 blocks of two items 5.5 us, as
-        // 148 blocks of one or two 7.7; with the residual add 6.5 against 9.5)
-        const long long kblocks = T / tiles, per = sms / tiles;
-        grid = tiles * (per < kblocks ? per : kblocks);
-    }
     if (grid > T) grid = T;
     const cudaError_t e = mb_launch(mb_pdl != 0, gemm_stream_kernel<EPI, SCALED, TH>, dim3((unsigned)grid), dim3(S_THREADS),
                                     SH::BYTES, st, wmap, xmap, out, N, M, K, tiles, workspace, counters, nrm, bias, after, err);
@@ -466,10 +488,11 @@ static int stream_launch(const void* act, const void* W, void* out, int N, int M
     if (N > S_NT || K % 8 || K < 8 || !workspace || !counters || (reinterpret_cast<uintptr_t>(W) & 15) ||
         (reinterpret_cast<uintptr_t>(act) & 15) || (SCALED && (!nrm.ssq || (reinterpret_cast<uintptr_t>(nrm.ssq) & 15))))
         return -2;
-    switch (stream_tile_height(M, stream_sms(), 32)) {
-        case 128: return stream_launch_th<EPI, SCALED, 128>(act, W, out, N, M, K, workspace, counters, nrm, bias, after, err, st);
-        case 64: return stream_launch_th<EPI, SCALED, 64>(act, W, out, N, M, K, workspace, counters, nrm, bias, after, err, st);
-        default: return stream_launch_th<EPI, SCALED, 32>(act, W, out, N, M, K, workspace, counters, nrm, bias, after, err, st);
+    const StreamPlan plan = stream_plan(M, K, EPI == 1 ? 2 : 1, stream_sms(), 32);
+    switch (plan.th) {
+        case 128: return stream_launch_th<EPI, SCALED, 128>(act, W, out, N, M, K, workspace, counters, nrm, bias, after, err, st, plan.grid);
+        case 64: return stream_launch_th<EPI, SCALED, 64>(act, W, out, N, M, K, workspace, counters, nrm, bias, after, err, st, plan.grid);
+        default: return stream_launch_th<EPI, SCALED, 32>(act, W, out, N, M, K, workspace, counters, nrm, bias, after, err, st, plan.grid);
     }
 }
 
