@@ -1,10 +1,10 @@
 // bf16 matrix products for decode batches (at most 16 tokens), bound by reading W once:
 // out[n, m] = sum_k act[n, k] * W[m, k].
 //
-// W is cut into row tiles of TH rows (128, 64 or 32: the largest height that still gives most SMs a tile, so that a
-// matrix of 4,096 rows is 128 tiles of 32 rows and no tile is shared) and k blocks of 16,384 / TH, so an item (row
-// tile, k block) is 32 KB of W.  When there are at most as many tiles as SMs the grid is one block per tile.
-// Otherwise the items, row tile major, are dealt in equal shares: block b of G takes [T b / G, T (b + 1) / G), which
+// W is cut into row tiles of TH rows (128, 64 or 32) and k blocks of 16,384 / TH, so an item (row tile, k block) is 32
+// KB of W.  stream_plan() picks the height and the number of blocks: a matrix of 4,096 rows is 128 tiles of 32 rows
+// with a block each and no tile is shared; a matrix with few tiles and long rows gets two or three blocks per tile.
+// In general the items, row tile major, are dealt in equal shares: block b of G takes [T b / G, T (b + 1) / G), which
 // covers the end of one row tile, whole row tiles, and the start of another; a tile that several blocks share is
 // finished by the block that arrives last (a counter per tile counts k blocks; it resets itself): every sharer leaves
 // its partial sums in its own slot of a workspace and the last one adds the slots in the order of the blocks, so the
