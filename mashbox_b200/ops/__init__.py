@@ -266,10 +266,10 @@ def linear_tc5(a, w, out, mode="plain"):
 # shape (width 2,048) 1,378 / 987 tokens/s, Llama-3.2-3B shape (3,072) 605 / 498, Falcon3-1B shape (2,048) 1,047 / 765,
 # Llama-3.1-8B shape (4,096) 328 / 315 (the same at 8,192 tokens of context: 3.35 ms a step either way): the advantage
 # shrinks with the width (+40 %, +21 %, +4 %), so the line for one token is drawn between 4,096 and 5,120.  At two
-# tokens (2,048 of context) the 1B shape takes 0.88 / 0.99 ms a step, the 3B shape 1.99 / 2.24, the 8B shape 3.84 /
+# tokens (2,048 of context) the 1B shape takes 0.88 / 0.91 ms a step, the 3B shape 1.98 / 1.88, the 8B shape 3.84 /
 # 3.55; at three they are level, at four the streaming products win everywhere.
 GEMV = {"swiglu": 1, "plain": 1, "fused": 1}
-GEMV_AUTO = ((3584, 2), (4608, 1))            # (narrower than, tokens), the first line that applies
+GEMV_AUTO = ((2560, 2), (4608, 1))            # (narrower than, tokens), the first line that applies
 
 
 def _gemv_limit(mode, K):
