@@ -219,9 +219,13 @@ class Attention:
         folded = (rot is not None and run.write and N == ctx.S and self.uses_mma(ctx)
                   and ctx.options.get("attention_kernel", "tma") == "tma" and ops.attention_tma_supports(HD, page)
                   and ops.attention_tma_folds_rotation(H // KV) and ctx.options.get("attention_folds_rotation", True)
-                  and not (normed is not None and ops.small_qkv_supports(N, self.D)))
-        if normed is not None and rot is not None and ops.small_qkv_supports(N, self.D):
-            # a step of very few tokens: norm, product, rotation and the cache write in one kernel
+                  and not (normed is not None and ops.small_qkv_supports(N, self.D)
+                           and ctx.options.get("qkv_rope_epilogue", False)))
+        if (normed is not None and rot is not None and ops.small_qkv_supports(N, self.D)
+                and (ctx.options.get("qkv_rope_epilogue", False) or not folded)):
+            # a step of very few tokens: norm, product, rotation and the cache write in one kernel -- where the attention
+            # kernel cannot take the rotation in (when it can, it also fetches the cached keys before this product has
+            # ended: a one-token step of the 8B shape 3.31 against 3.35 ms)
             x, norm = normed
             w, eps = norm.fusable()
             freqs, rd, pairing = rot
