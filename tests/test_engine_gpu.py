@@ -456,3 +456,38 @@ def test_decode_batches_filled_up_to_a_grid_share_graphs_and_change_nothing(tmp_
             assert np.array_equal(a, b)
         for i in (0, live - 1):
             H.check(a[i:i + 1], folder, prompts[i][:fed[i]], mode, f"filled batch of {live}, row {i}", slice(-1, None))
+
+
+def test_many_step_shapes_graphs_are_replaced_and_everything_finishes(tmp_path):
+    """600 requests of random lengths arriving in bursts at an engine with 40 slots: more step shapes than the runner
+    keeps graphs for (64), so graphs are captured, replayed and given up all along; every request ends with exactly
+    the tokens it asked for, and the cache is whole afterwards."""
+    import random
+    from mashbox_b200.engine.engine import Engine
+    rng = random.Random(3)
+    folder = H.make_folder(tmp_path, "C", "bfloat16")
+    vocab = H.TINY["C"][0].vocab
+    eng = Engine.from_folder(folder, dtype="bfloat16", page_size=H.TINY["C"][2], max_tokens=40 * 320, max_requests=40,
+                             max_tokens_per_step=256, chunk=128, max_context=320)
+    reqs = [dict(ids=[rng.randrange(vocab) for _ in range(rng.randint(1, 200))], max_new=rng.randint(1, 100),
+                 samp=None if rng.random() < 0.5 else dict(temperature=0.8, seed=rng.randrange(1 << 30),
+                                                           top_k=rng.choice([0, 20])))
+            for _ in range(600)]
+    pending, rows, steps = list(range(len(reqs))), {}, 0
+    while pending or eng.busy():
+        if pending and (rng.random() < 0.25 or not eng.busy()):
+            n = rng.randint(1, 25)
+            take, pending = pending[:n], pending[n:]
+            for i, r in zip(take, eng.admit([reqs[i] for i in take])):
+                rows[i] = r
+        eng.step()
+        steps += 1
+        assert steps < 100000
+    for i, r in rows.items():
+        assert r.finish == "length" and len(r.generated) == reqs[i]["max_new"] and -1 not in r.generated, (i, r.finish)
+        assert all(0 <= t < vocab for t in r.generated)
+    st = eng.runner.stats
+    assert st["graph_captures"] > eng.runner.MAX_GRAPHS and len(eng.runner.graphs) <= eng.runner.MAX_GRAPHS
+    assert st["graph_replays"] > 0
+    eng.cache.check()
+    assert eng.cache.free_pages() == [eng.cache.num_pages]
