@@ -435,7 +435,10 @@ def test_penalties_and_their_state():
 
 
 @pytest.mark.parametrize("N,M,K", [(1, 4096, 4096), (8, 6144, 4096), (3, 1000, 200), (16, 4096, 14336), (5, 504, 320), (2, 56, 72),
-                                   (8, 5000, 520), (3, 14336, 256), (16, 10008, 136), (2, 28672, 264)])
+                                   (8, 5000, 520), (3, 14336, 256), (16, 10008, 136), (2, 28672, 264),
+                                   # the cuts of few-tile matrices: two and three blocks a tile, tiles of 64 rows
+                                   (8, 2048, 8192), (4, 5120, 3072), (16, 2560, 2560), (3, 1024, 4096), (8, 3072, 8192),
+                                   (8, 2048, 2048)])
 def test_weight_streaming_product(N, M, K):
     """the product for decode batches that streams W by TMA: a block per row tile where that leaves at most a tile per
     SM (tiles of 32, 48, 64, 112 or 128 rows, the last one of a matrix cut short), else equal shares per SM, row tiles
@@ -573,7 +576,8 @@ def test_qkv_product_with_rotation_and_cache_write_in_its_epilogue(pairing, HD, 
     assert torch.equal(three[:, :H * HD], one[:, :H * HD])
 
 
-@pytest.mark.parametrize("N,M,K", [(8, 6144, 4096), (16, 56, 72), (3, 1000, 2504), (1, 4096, 4096), (5, 264, 14336), (8, 4096, 4096)])
+@pytest.mark.parametrize("N,M,K", [(8, 6144, 4096), (16, 56, 72), (3, 1000, 2504), (1, 4096, 4096), (5, 264, 14336), (8, 4096, 4096),
+                                   (8, 2048, 8192), (4, 3072, 8192), (16, 1024, 4096), (8, 2048, 2048)])
 def test_streaming_products_that_add_to_the_stream_and_take_the_norm_in(N, M, K):
     """the folded forms of a step of at most 16 tokens: the product that ends a sublayer adds into the float32 stream and
     leaves what the norm after it needs (sums of squares by 32 columns, rows times the norm's weight in bf16); the
